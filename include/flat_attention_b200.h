@@ -1,0 +1,420 @@
+/*
+ * flat_attention_b200.h — C ABI of the B200 (sm_100a) fused-attention backend.
+ *
+ * This is the boundary a Rust `Cuda*` backend would bind (one `extern "C"` block, plain
+ * pointers and sizes).  Every entry point names the FLAT-ATTENTION interface it stands in
+ * for (`file:line` in that project).  Conventions kept from the reference backends:
+ *
+ *  - all validation happens before any launch; the result is a typed status, never an
+ *    abort and never a CPU result (src/lib.rs:362, src/numerical.rs:150-153);
+ *  - `flat_*` calls that launch work are "encode"-style: they enqueue on the context's
+ *    CUDA stream and return without synchronising (src/wgpu_decode.rs:1-8,
+ *    src/wgpu_paged_kv_cache.rs:8-9); only flat_synchronize / flat_download block;
+ *  - buffers may be larger than required, too-small buffers are rejected with the exact
+ *    byte counts (src/wgpu_forward_grouped.rs:565-579);
+ *  - outputs are packed `[O | LSE]` in one buffer, O first (src/wgpu_forward_grouped.rs:34-42).
+ *    f32 mode: LSE starts at element q_elements.  bf16 mode: O is bf16, LSE is f32 at byte
+ *    offset 2*q_elements (the 16-bit packing of src/wgpu_f16_backend.rs:273-277).
+ */
+#ifndef FLAT_ATTENTION_B200_H
+#define FLAT_ATTENTION_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes -------------------------------------------------------------------- */
+/* 1..9 mirror FlatAttentionError (src/lib.rs:363-386) and api::v1::ApiError
+ * (src/api.rs:203-222); the other blocks mirror the per-component error enums. */
+typedef enum flat_status {
+    FLAT_OK = 0,
+    FLAT_ERR_ZERO_DIMENSION = 1,
+    FLAT_ERR_SHAPE_OVERFLOW = 2,
+    FLAT_ERR_INVALID_HEAD_GROUPING = 3,
+    FLAT_ERR_INVALID_ROTARY_HEAD_DIM = 4,
+    FLAT_ERR_INVALID_ROTARY_THETA = 5,
+    FLAT_ERR_POSITION_OVERFLOW = 6,
+    FLAT_ERR_LENGTH_MISMATCH = 7,
+    FLAT_ERR_INVALID_SCALE = 8,
+    FLAT_ERR_NON_FINITE_INPUT = 9,
+    /* backend errors (src/wgpu_backend.rs:39-63, src/wgpu_forward_grouped.rs:104-125) */
+    FLAT_ERR_UNSUPPORTED_HEAD_DIM = 20,
+    FLAT_ERR_INDEX_SPACE_EXCEEDED = 21,
+    FLAT_ERR_BUFFER_TOO_SMALL = 22,
+    FLAT_ERR_UNAVAILABLE = 23,      /* no CUDA device / not an sm_100 device */
+    FLAT_ERR_EXECUTION = 24,        /* a CUDA call failed; detail carries the CUDA message */
+    FLAT_ERR_DISPATCH_LIMIT = 25,
+    FLAT_ERR_UNSUPPORTED_DTYPE = 26,
+    FLAT_ERR_NULL_POINTER = 27,
+    FLAT_ERR_MISALIGNED_BUFFER = 28,
+    FLAT_ERR_UNSUPPORTED_SHAPE = 29, /* shape valid for the contract, not for this kernel */
+    /* decode errors (src/wgpu_decode.rs:104-142, src/wgpu_paged_decode.rs:27-71) */
+    FLAT_ERR_EMPTY_CACHE = 30,
+    FLAT_ERR_INVALID_CACHE_LENGTH = 31,
+    FLAT_ERR_INVALID_QUERY_LEN = 32,
+    FLAT_ERR_CAUSAL_VISIBILITY_MISMATCH = 33,
+    FLAT_ERR_EMPTY_TABLE = 34,
+    FLAT_ERR_PAGE_OUT_OF_RANGE = 35,
+    FLAT_ERR_PAGE_SHARED = 36,
+    FLAT_ERR_INVALID_THETA = 37,
+    /* paged-KV metadata errors (src/paged_kv.rs:37-43) and cache errors
+     * (src/wgpu_kv_cache.rs:21-38, src/wgpu_paged_kv_cache.rs:16-33) */
+    FLAT_ERR_CAPACITY_OVERFLOW = 40,
+    FLAT_ERR_CAPACITY_EXCEEDED = 41,
+    FLAT_ERR_GENERATION_OVERFLOW = 42,
+    /* chunked prefill (src/chunked_projection_prefill.rs:23-27) */
+    FLAT_ERR_ZERO_QUERY_CHUNK_SIZE = 50,
+    /* a bounded device-side wait expired; the kernel returned early and the context is
+     * still usable (outputs of that launch are undefined) */
+    FLAT_ERR_DEVICE_WAIT_TIMEOUT = 60
+} flat_status;
+
+/* Storage/arithmetic mode.  F32: f32 I/O, f32 SIMT arithmetic (parity mode, <=1e-4).
+ * BF16: bf16 Q/K/V/dO/O, f32 LSE, tcgen05 tensor-core arithmetic with f32 accumulation. */
+typedef enum flat_dtype { FLAT_F32 = 0, FLAT_BF16 = 1 } flat_dtype;
+
+/* HEAD_MAJOR: Q/O [B,Hq,Nq,D], K/V [B,Hkv,Nkv,D] (src/grouped.rs:11-16).
+ * PROJECTION: Q/O [B*Nq, Hq*D], K/V [B*Nkv, Hkv*D] (src/projection_grouped.rs:3-8).
+ * LSE is [B,Hq,Nq] in both. */
+typedef enum flat_layout { FLAT_LAYOUT_HEAD_MAJOR = 0, FLAT_LAYOUT_PROJECTION = 1 } flat_layout;
+
+/* api::v1::AttentionShape (src/api.rs:24-33); for equal-length calls query_len == kv_len
+ * and query_position_offset == 0. */
+typedef struct flat_attention_shape {
+    uint64_t batch;
+    uint64_t q_heads;
+    uint64_t kv_heads;
+    uint64_t query_len;
+    uint64_t kv_len;
+    uint64_t head_dim;
+    uint64_t query_position_offset; /* causal domain: row q sits at offset + q */
+} flat_attention_shape;
+
+/* FlatAttentionConfig (src/lib.rs:248-269). has_softmax_scale == 0 -> 1/sqrt(head_dim). */
+typedef struct flat_attention_config {
+    int32_t causal;
+    int32_t has_softmax_scale;
+    float softmax_scale;
+} flat_attention_config;
+
+/* AsymmetricRotaryEmbeddingConfig (src/projection_asymmetric.rs:18-23) plus the
+ * `rotate_k` switch of encode_pre_rotated_k (src/wgpu_external_asymmetric.rs:203-211):
+ * rotate_k == 0 means K in memory is already rotated and only Q is rotated in-kernel. */
+typedef struct flat_rotary_config {
+    float theta;
+    int32_t rotate_k;
+    uint64_t query_position_offset;
+    uint64_t kv_position_offset;
+} flat_rotary_config;
+
+/* A device allocation: the wgpu::Buffer analogue (pointer + size in bytes). */
+typedef struct flat_buffer {
+    void *ptr;
+    uint64_t bytes;
+} flat_buffer;
+
+/* GroupedForwardLayout / ExternalProjectionLayout (src/wgpu_forward_grouped.rs:23-42). */
+typedef struct flat_forward_layout {
+    uint64_t q_elements;
+    uint64_t kv_elements;
+    uint64_t lse_elements;
+    uint64_t q_bytes;
+    uint64_t kv_bytes;
+    uint64_t lse_byte_offset; /* where LSE starts inside the packed output */
+    uint64_t combined_bytes;  /* size of the packed [O | LSE] buffer */
+} flat_forward_layout;
+
+/* VariableLengthSequenceMetadata (src/wgpu_external_variable.rs:21-33). */
+typedef struct flat_varlen_sequence {
+    uint32_t active_query_len;
+    uint32_t active_kv_len;
+    uint32_t causal_query_offset;
+    uint32_t query_rope_offset;
+} flat_varlen_sequence;
+
+/* PagedKvTelemetry (src/paged_kv.rs:27-35). */
+typedef struct flat_paged_kv_telemetry {
+    uint64_t live_tokens;
+    uint64_t capacity_tokens;
+    uint64_t mapped_pages;
+    uint64_t free_pages;
+    uint64_t internal_fragmentation_tokens;
+    uint64_t generation;
+} flat_paged_kv_telemetry;
+
+/* PagedKvAddress (src/paged_kv.rs:20-25). */
+typedef struct flat_paged_kv_address {
+    uint64_t physical_page;
+    uint64_t offset_in_page;
+    uint64_t generation;
+} flat_paged_kv_address;
+
+/* GroupedBackwardRecomputeLayout (src/wgpu_backward_grouped.rs:17-56): packed input
+ * Q|K|V|dO|O|LSE and packed output dQ|dK|dV, offsets in bytes. */
+typedef struct flat_backward_layout {
+    uint64_t q_elements;
+    uint64_t kv_elements;
+    uint64_t lse_elements;
+    uint64_t q_offset, k_offset, v_offset, d_out_offset, out_offset, lse_offset;
+    uint64_t input_bytes;
+    uint64_t dq_offset, dk_offset, dv_offset;
+    uint64_t output_bytes;
+} flat_backward_layout;
+
+typedef struct flat_ctx flat_ctx;
+typedef struct flat_paged_kv_table flat_paged_kv_table;
+typedef struct flat_paged_kv_cache flat_paged_kv_cache;
+typedef struct flat_resident_kv_cache flat_resident_kv_cache;
+
+/* ---- context ------------------------------------------------------------------------- */
+
+/* WgpuFlatAttention::new (src/wgpu_backend.rs:177-255): bind to one device.  `stream` is a
+ * cudaStream_t (NULL = legacy default stream); the caller owns it, like the wgpu queue. */
+int32_t flat_ctx_create(int32_t device, void *stream, flat_ctx **out);
+void flat_ctx_destroy(flat_ctx *ctx);
+/* Replace the stream later launches are enqueued on. */
+int32_t flat_ctx_set_stream(flat_ctx *ctx, void *stream);
+const char *flat_status_str(int32_t status);
+/* Human-readable detail of the last error on this context (tensor name, actual/expected
+ * sizes, CUDA message): the payload of the reference's error variants. */
+const char *flat_last_error_detail(const flat_ctx *ctx);
+/* Pre-size the context's device scratch (split-KV partials, rotated-operand staging,
+ * backward accumulators) so later encode calls do not allocate. */
+int32_t flat_ctx_reserve_workspace(flat_ctx *ctx, uint64_t bytes);
+uint64_t flat_ctx_workspace_bytes(const flat_ctx *ctx);
+/* Number of kernel launches this context has enqueued since creation. */
+uint64_t flat_ctx_launch_count(const flat_ctx *ctx);
+/* Reads the device status word written by bounded waits (FLAT_OK or
+ * FLAT_ERR_DEVICE_WAIT_TIMEOUT); synchronises the stream. */
+int32_t flat_ctx_device_status(flat_ctx *ctx);
+
+/* WgpuFlatAttention::upload / download_attention (src/wgpu_backend.rs:465-482,588-608):
+ * explicit host<->device copies on the context stream; download blocks. */
+int32_t flat_upload(flat_ctx *ctx, flat_buffer dst, const void *host_src, uint64_t bytes);
+int32_t flat_download(flat_ctx *ctx, void *host_dst, flat_buffer src, uint64_t bytes);
+int32_t flat_synchronize(flat_ctx *ctx);
+
+/* ---- forward ------------------------------------------------------------------------- */
+
+/* *Pipeline::layout (src/wgpu_forward_grouped.rs:306-334, src/wgpu_external.rs:153-173):
+ * pure, allocation-free. */
+int32_t flat_forward_layout_for(int32_t dtype, const flat_attention_shape *shape,
+                                flat_forward_layout *out);
+
+/* WgpuFlatAttention::forward_resident (src/wgpu_backend.rs:484-586): MHA, head-major;
+ * requires q_heads == kv_heads and query_len == kv_len. */
+int32_t flat_forward_mha(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
+                         const flat_attention_config *config, flat_buffer q, flat_buffer k,
+                         flat_buffer v, flat_buffer out_and_lse);
+
+/* WgpuGroupedForwardPipeline::encode (src/wgpu_forward_grouped.rs:531-539): GQA/MQA,
+ * head-major, equal length. */
+int32_t flat_forward_grouped(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
+                             const flat_attention_config *config, flat_buffer q, flat_buffer k,
+                             flat_buffer v, flat_buffer out_and_lse);
+
+/* Head-major rectangular GQA without RoPE: forward_reference_grouped_asymmetric
+ * (src/asymmetric_grouped.rs:230-304). */
+int32_t flat_forward_grouped_asymmetric(flat_ctx *ctx, int32_t dtype,
+                                        const flat_attention_shape *shape,
+                                        const flat_attention_config *config, flat_buffer q,
+                                        flat_buffer k, flat_buffer v, flat_buffer out_and_lse);
+
+/* WgpuRotaryGroupedAttention::forward_resident (src/wgpu_rotary_grouped_backend.rs:163-271):
+ * head-major GQA with fused RoPE; rotary->query_position_offset == kv_position_offset. */
+int32_t flat_forward_grouped_rope(flat_ctx *ctx, int32_t dtype,
+                                  const flat_attention_shape *shape,
+                                  const flat_attention_config *config,
+                                  const flat_rotary_config *rotary, flat_buffer q, flat_buffer k,
+                                  flat_buffer v, flat_buffer out_and_lse);
+
+/* ExternalProjectionRotaryGroupedPipeline::encode (src/wgpu_external.rs:198-211):
+ * projection layout, equal length, fused RoPE. */
+int32_t flat_forward_projection_rope(flat_ctx *ctx, int32_t dtype,
+                                     const flat_attention_shape *shape,
+                                     const flat_attention_config *config,
+                                     const flat_rotary_config *rotary, flat_buffer q,
+                                     flat_buffer k, flat_buffer v, flat_buffer out_and_lse);
+
+/* ExternalAsymmetricProjectionRotaryGroupedPipeline::encode / encode_pre_rotated_k
+ * (src/wgpu_external_asymmetric.rs:192-211): rectangular projection layout, three position
+ * domains, optional pre-rotated K. */
+int32_t flat_forward_projection_rope_asymmetric(flat_ctx *ctx, int32_t dtype,
+                                                const flat_attention_shape *shape,
+                                                const flat_attention_config *config,
+                                                const flat_rotary_config *rotary, flat_buffer q,
+                                                flat_buffer k, flat_buffer v,
+                                                flat_buffer out_and_lse);
+
+/* ExternalVariableProjectionRotaryGroupedPipeline::encode
+ * (src/wgpu_external_variable.rs:190-223): padded variable-length batch; `sequences` is a
+ * HOST array of shape->batch entries (validated, then copied to the device); padded query
+ * rows get O = 0 and LSE = -inf.  rotary->query_position_offset is ignored (per-sequence). */
+int32_t flat_forward_projection_rope_varlen(flat_ctx *ctx, int32_t dtype,
+                                            const flat_attention_shape *shape,
+                                            const flat_attention_config *config,
+                                            const flat_rotary_config *rotary,
+                                            const flat_varlen_sequence *sequences,
+                                            uint64_t sequence_count, flat_buffer q,
+                                            flat_buffer k, flat_buffer v,
+                                            flat_buffer out_and_lse);
+
+/* ---- paged-KV metadata (host only) --------------------------------------------------- */
+
+/* PagedKvTable::new / append / address / telemetry / reset (src/paged_kv.rs:84-188). */
+int32_t flat_paged_kv_table_create(uint64_t page_size, uint64_t physical_pages,
+                                   flat_paged_kv_table **out);
+void flat_paged_kv_table_destroy(flat_paged_kv_table *table);
+int32_t flat_paged_kv_table_append(flat_paged_kv_table *table, uint64_t tokens);
+/* returns FLAT_OK and fills *out, or FLAT_ERR_EMPTY_TABLE when the reference returns None */
+int32_t flat_paged_kv_table_address(const flat_paged_kv_table *table, uint64_t logical_token,
+                                    flat_paged_kv_address *out);
+int32_t flat_paged_kv_table_telemetry(const flat_paged_kv_table *table,
+                                      flat_paged_kv_telemetry *out);
+int32_t flat_paged_kv_table_reset(flat_paged_kv_table *table);
+uint64_t flat_paged_kv_table_len(const flat_paged_kv_table *table);
+uint64_t flat_paged_kv_table_generation(const flat_paged_kv_table *table);
+/* WgpuPagedKvTable::from_table (src/wgpu_paged_decode.rs:162-198): flatten the logical ->
+ * physical map into u32 entries; *count receives mapped_pages (entries may be NULL to query). */
+int32_t flat_paged_kv_table_export(const flat_paged_kv_table *table, uint32_t *entries,
+                                   uint64_t capacity, uint64_t *count);
+
+/* ---- KV caches ----------------------------------------------------------------------- */
+
+/* WgpuPagedKvCache::new (src/wgpu_paged_kv_cache.rs:99-146): owns K and V
+ * [physical_pages*page_size, kv_heads*head_dim] in device memory. */
+int32_t flat_paged_kv_cache_create(flat_ctx *ctx, int32_t dtype, uint64_t page_size,
+                                   uint64_t physical_pages, uint64_t kv_heads,
+                                   uint64_t head_dim, flat_paged_kv_cache **out);
+void flat_paged_kv_cache_destroy(flat_paged_kv_cache *cache);
+/* WgpuPagedKvCache::record_append (src/wgpu_paged_kv_cache.rs:206-279): sources are
+ * [append_len, kv_heads*head_dim], K already rotated; metadata commits only if every copy
+ * was enqueued; *new_len receives the live length. */
+int32_t flat_paged_kv_cache_append(flat_paged_kv_cache *cache, flat_buffer k_source,
+                                   flat_buffer v_source, uint64_t append_len,
+                                   uint64_t *new_len);
+/* Same append with RoPE fused into the copy: K rows are raw projections and are rotated
+ * at positions kv_position_offset + old_len + i while being written (V copied as is). */
+int32_t flat_paged_kv_cache_append_rotating(flat_paged_kv_cache *cache, flat_buffer k_source,
+                                            flat_buffer v_source, uint64_t append_len,
+                                            float theta, uint64_t kv_position_offset,
+                                            uint64_t *new_len);
+int32_t flat_paged_kv_cache_reset(flat_paged_kv_cache *cache);
+uint64_t flat_paged_kv_cache_len(const flat_paged_kv_cache *cache);
+uint64_t flat_paged_kv_cache_generation(const flat_paged_kv_cache *cache);
+flat_buffer flat_paged_kv_cache_k_buffer(const flat_paged_kv_cache *cache);
+flat_buffer flat_paged_kv_cache_v_buffer(const flat_paged_kv_cache *cache);
+const flat_paged_kv_table *flat_paged_kv_cache_table(const flat_paged_kv_cache *cache);
+
+/* WgpuResidentKvCache (src/wgpu_kv_cache.rs:104-262): [batch, capacity, kv_heads*head_dim]. */
+int32_t flat_resident_kv_cache_create(flat_ctx *ctx, int32_t dtype, uint64_t batch,
+                                      uint64_t kv_heads, uint64_t capacity, uint64_t head_dim,
+                                      flat_resident_kv_cache **out);
+void flat_resident_kv_cache_destroy(flat_resident_kv_cache *cache);
+/* sources are [batch, append_len, kv_heads*head_dim] (src/wgpu_kv_cache.rs:212-262) */
+int32_t flat_resident_kv_cache_append(flat_resident_kv_cache *cache, flat_buffer k_source,
+                                      flat_buffer v_source, uint64_t append_len,
+                                      uint64_t *new_len);
+void flat_resident_kv_cache_reset(flat_resident_kv_cache *cache);
+uint64_t flat_resident_kv_cache_len(const flat_resident_kv_cache *cache);
+uint64_t flat_resident_kv_cache_capacity(const flat_resident_kv_cache *cache);
+flat_buffer flat_resident_kv_cache_k_buffer(const flat_resident_kv_cache *cache);
+flat_buffer flat_resident_kv_cache_v_buffer(const flat_resident_kv_cache *cache);
+
+/* ---- decode -------------------------------------------------------------------------- */
+
+/* WgpuResidentDecodePipeline::encode_external_pre_rotated_k (src/wgpu_decode.rs:263-322,
+ * 419-435): q_len = 1 per batch row over [batch, kv_capacity, kv_heads*head_dim] with live
+ * prefix kv_len; Q [batch, q_heads*head_dim] is raw and rotated at q_rope_position, K is
+ * pre-rotated.  Output packed [O(batch*q_heads*head_dim) | LSE(batch*q_heads)]. */
+int32_t flat_decode_resident(flat_ctx *ctx, int32_t dtype, uint64_t batch, uint64_t q_heads,
+                             uint64_t kv_heads, uint64_t head_dim, uint64_t kv_len,
+                             uint64_t kv_capacity, const flat_attention_config *config,
+                             float theta, uint64_t q_rope_position, flat_buffer q,
+                             flat_buffer k, flat_buffer v, flat_buffer out_and_lse);
+
+/* WgpuPagedDecodePipeline::encode (src/wgpu_paged_decode.rs:300-436): one sequence, page
+ * table taken from a PagedKvTable.  K/V physical layout
+ * [physical_pages, page_size, kv_heads*head_dim]; output [O(q_heads*head_dim) | LSE(q_heads)]. */
+int32_t flat_decode_paged(flat_ctx *ctx, int32_t dtype, const flat_paged_kv_table *table,
+                          uint64_t q_heads, uint64_t kv_heads, uint64_t head_dim,
+                          const flat_attention_config *config, float theta,
+                          uint64_t q_rope_position, flat_buffer q, flat_buffer k, flat_buffer v,
+                          flat_buffer out_and_lse);
+
+/* Batched generalisation of the same kernel: num_seqs independent sequences sharing one
+ * physical pool.  page_tables is a DEVICE array [num_seqs, max_pages_per_seq] of int32,
+ * context_lens / q_rope_positions are DEVICE arrays [num_seqs] of int32.  host_context_lens
+ * (and host_page_tables, optional) let the call validate before launch: every used entry
+ * < physical_pages, no page shared between sequences, causal visibility per sequence.
+ * Q is [num_seqs, q_heads*head_dim]; output [O(num_seqs*q_heads*head_dim) | LSE(num_seqs*q_heads)].
+ * kv_splits = 0 lets the library choose the split along KV. */
+int32_t flat_decode_paged_batched(flat_ctx *ctx, int32_t dtype, uint64_t num_seqs,
+                                  uint64_t q_heads, uint64_t kv_heads, uint64_t head_dim,
+                                  uint64_t page_size, uint64_t physical_pages,
+                                  uint64_t max_pages_per_seq, const int32_t *page_tables_dev,
+                                  const int32_t *context_lens_dev,
+                                  const int32_t *q_rope_positions_dev,
+                                  const int32_t *host_page_tables,
+                                  const int32_t *host_context_lens,
+                                  const int32_t *host_q_rope_positions,
+                                  const flat_attention_config *config, float theta,
+                                  uint32_t kv_splits, flat_buffer q, flat_buffer k,
+                                  flat_buffer v, flat_buffer out_and_lse);
+
+/* Split-KV merge over `parts` partial results laid out [parts, rows, head_dim] (O, f32,
+ * each normalised within its part) and [parts, rows] (LSE, f32):
+ * LSE = log(sum_i exp(LSE_i)), O = sum_i exp(LSE_i - LSE) O_i.  This is the consumer of the
+ * all-gathered per-GPU partials of single-sequence long-context decode; the reference has
+ * no counterpart (it never splits KV).  Output packed [O | LSE] in `dtype`. */
+int32_t flat_splitkv_merge(flat_ctx *ctx, int32_t dtype, uint64_t parts, uint64_t rows,
+                           uint64_t head_dim, flat_buffer partial_o, flat_buffer partial_lse,
+                           flat_buffer out_and_lse);
+
+/* ---- chunked prefill ----------------------------------------------------------------- */
+
+/* WgpuChunkedProjectionPrefillPipeline::encode (src/wgpu_chunked_prefill.rs:156-299):
+ * projection-layout prefill with Q/O/LSE processed in query chunks of query_chunk_size;
+ * result identical to the contiguous call (src/chunked_projection_prefill.rs:63-169). */
+int32_t flat_chunked_prefill(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
+                             const flat_attention_config *config,
+                             const flat_rotary_config *rotary, uint64_t query_chunk_size,
+                             flat_buffer q, flat_buffer k, flat_buffer v,
+                             flat_buffer out_and_lse);
+
+/* One prefill chunk against the growing paged cache (chunked prefill composed with
+ * WgpuPagedKvCache::record_append, src/wgpu_paged_kv_cache.rs:206-279): the chunk's K rows
+ * (raw) are rotated at their absolute positions and appended with V, then the chunk's
+ * queries [chunk_len, q_heads*head_dim] attend causally to the whole cache through the page
+ * table with query_position_offset = old cache length.  Output packed
+ * [O(chunk_len*q_heads*head_dim) | LSE(q_heads*chunk_len)]. */
+int32_t flat_chunked_prefill_paged(flat_ctx *ctx, flat_paged_kv_cache *cache, uint64_t q_heads,
+                                   uint64_t chunk_len, const flat_attention_config *config,
+                                   float theta, uint64_t position_offset, flat_buffer q_chunk,
+                                   flat_buffer k_chunk, flat_buffer v_chunk,
+                                   flat_buffer out_and_lse);
+
+/* ---- backward ------------------------------------------------------------------------ */
+
+/* GroupedBackwardRecomputePipeline::layout (src/wgpu_backward_grouped.rs:181-215). */
+int32_t flat_backward_layout_for(int32_t dtype, const flat_attention_shape *shape,
+                                 flat_backward_layout *out);
+
+/* WgpuGroupedBackwardRecomputePipeline::encode (src/wgpu_backward_grouped.rs:318-326) and
+ * WgpuBackwardRecomputePipeline::encode (src/wgpu_backward.rs:286-308; the q_heads ==
+ * kv_heads case): head-major, equal length, inputs Q,K,V,dO,O,LSE packed per the layout,
+ * outputs dQ|dK|dV with dK/dV reduced over each KV head's query-head group. */
+int32_t flat_backward_grouped(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
+                              const flat_attention_config *config, flat_buffer packed_inputs,
+                              flat_buffer packed_grads);
+int32_t flat_backward_mha(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
+                          const flat_attention_config *config, flat_buffer packed_inputs,
+                          flat_buffer packed_grads);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLAT_ATTENTION_B200_H */
