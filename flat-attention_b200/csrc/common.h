@@ -1,0 +1,150 @@
+// Internal declarations shared by the host layer (abi.cu) and the kernel translation units.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <vector>
+
+#include "../../include/flat_attention_b200.h"
+
+namespace flat {
+
+constexpr int kMaxHeadDim = 128;  // WGSL_MAX_HEAD_DIM, src/lib.rs:60
+
+// Device status word written by bounded waits.
+struct DeviceStatus {
+    int code;    // FLAT_OK or FLAT_ERR_DEVICE_WAIT_TIMEOUT
+    int where;   // which wait gave up (kernel-specific tag)
+};
+
+}  // namespace flat
+
+struct flat_ctx {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    int sm_count = 0;
+    int cc_major = 0, cc_minor = 0;
+    void *workspace = nullptr;
+    uint64_t workspace_bytes = 0;
+    flat::DeviceStatus *dev_status = nullptr;  // device memory
+    uint64_t launches = 0;
+    std::string detail;
+};
+
+namespace flat {
+
+// printf-style error recording; returns `status` so call sites can `return fail(...)`.
+int fail(flat_ctx *ctx, int status, const char *fmt, ...);
+
+inline bool mul_ok(uint64_t a, uint64_t b, uint64_t *out) { return !__builtin_mul_overflow(a, b, out); }
+inline bool add_ok(uint64_t a, uint64_t b, uint64_t *out) { return !__builtin_add_overflow(a, b, out); }
+
+inline size_t dtype_size(int dtype) { return dtype == FLAT_BF16 ? 2 : 4; }
+
+// Grows (never shrinks) the context scratch; synchronises the stream when it reallocates, so it
+// must be called before anything of the current call is copied into the scratch.
+int ensure_workspace(flat_ctx *ctx, uint64_t bytes);
+// Scratch convention: the first kWorkspaceMeta bytes hold small host-provided tables of the
+// current call (variable-length metadata, a single-sequence page table); kernel scratch (split-KV
+// partials, rotated operands, backward accumulators) starts behind it.
+constexpr uint64_t kWorkspaceMeta = 1 << 16;
+inline char *scratch_ptr(flat_ctx *ctx) { return static_cast<char *>(ctx->workspace) + kWorkspaceMeta; }
+
+#define FLAT_CUDA_OK(ctx, expr)                                                            \
+    do {                                                                                   \
+        cudaError_t e__ = (expr);                                                          \
+        if (e__ != cudaSuccess)                                                            \
+            return ::flat::fail((ctx), FLAT_ERR_EXECUTION, "%s: %s", #expr, cudaGetErrorString(e__)); \
+    } while (0)
+
+// ---- forward ---------------------------------------------------------------------------------
+// One parameter block serves every forward flavour: layouts are element strides, RoPE is two
+// switches plus three position domains, variable-length batches and paged K/V are optional
+// pointers.  (The reference kernels' uniform blocks: src/wgpu_external_asymmetric.rs:319-339,
+// src/wgpu_external_variable.rs:148-171.)
+struct FwdParams {
+    const void *q, *k, *v;
+    void *o;
+    float *lse;
+    int64_t q_bs, q_hs, q_rs;     // Q element strides: batch, head, row
+    int64_t kv_bs, kv_hs, kv_rs;  // K/V element strides (ignored for paged K/V except kv_hs)
+    int64_t o_bs, o_hs, o_rs;
+    int64_t lse_hs;               // LSE elements between consecutive (batch, q_head) rows
+    int batch, q_heads, kv_heads, q_len, kv_len, head_dim, group;
+    int causal;
+    int64_t causal_off;
+    float scale;
+    int rope_q, rope_k;
+    int64_t q_rope_off, k_rope_off;
+    const flat_varlen_sequence *varlen;  // device, [batch] or null
+    const int32_t *page_table;           // device, [batch, max_pages] or null
+    int page_size, max_pages;
+    int64_t page_row_stride;             // elements per physical row (kv_heads*head_dim)
+    float inv_freq[kMaxHeadDim / 2];     // theta^(-2j/D), host-computed in f32
+};
+
+// Generic SIMT forward (f32 arithmetic; T = float or __nv_bfloat16 storage).
+int launch_forward_simt(flat_ctx *ctx, int dtype, const FwdParams &p);
+// tcgen05 forward for bf16, head_dim 64/128; returns FLAT_ERR_UNSUPPORTED_SHAPE when the shape
+// does not fit it (the caller then uses the SIMT kernel).
+bool forward_sm100_supported(const FwdParams &p);
+uint64_t forward_sm100_workspace_bytes(const FwdParams &p);
+int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p);
+
+// ---- decode ----------------------------------------------------------------------------------
+struct DecodeParams {
+    const void *q;       // [num_seqs, q_heads*head_dim]
+    const void *k, *v;   // paged: [pages, page_size, kv_heads*head_dim]; resident: [batch, capacity, ...]
+    void *o;             // [num_seqs, q_heads*head_dim]
+    float *lse;          // [num_seqs, q_heads]
+    int num_seqs, q_heads, kv_heads, head_dim, group;
+    int page_size, max_pages;            // page_size == 0 -> resident (contiguous) addressing
+    const int32_t *page_table;           // device [num_seqs, max_pages]
+    const int32_t *context_lens;         // device [num_seqs] or null (-> uniform_len)
+    const int32_t *q_rope_positions;     // device [num_seqs] or null (-> uniform_q_pos)
+    int uniform_len;
+    int64_t uniform_q_pos;
+    int64_t seq_stride_rows;             // resident: capacity (rows per batch element)
+    float scale;
+    int rope_q;
+    float inv_freq[kMaxHeadDim / 2];
+    int kv_splits;                       // >= 1
+    float *partial_o;                    // [splits, num_seqs*q_heads, head_dim] f32 (splits > 1)
+    float *partial_lse;                  // [splits, num_seqs*q_heads]
+    int chunk_tokens;                    // tokens per split chunk (splits > 1)
+};
+uint64_t decode_workspace_bytes(const DecodeParams &p);
+bool decode_fast_path_ok(int dtype, int head_dim, int group);
+int launch_decode(flat_ctx *ctx, int dtype, const DecodeParams &p);
+int launch_splitkv_merge(flat_ctx *ctx, int dtype, int parts, int64_t rows, int head_dim,
+                         const float *partial_o, const float *partial_lse, void *o, float *lse);
+
+// ---- KV cache --------------------------------------------------------------------------------
+// Copies `rows` source rows of `row_elems` elements to destination rows dst_rows[i] (device
+// array of int64), optionally rotating each head_dim-wide head slice at positions pos0 + i.
+int launch_append_rows(flat_ctx *ctx, int dtype, const void *k_src, const void *v_src, void *k_dst,
+                       void *v_dst, int64_t rows, int row_elems, int head_dim,
+                       const int32_t *page_table, int page_size, int64_t first_logical,
+                       int64_t dst_row0, int rotate, int64_t pos0, const float *inv_freq);
+
+// ---- backward --------------------------------------------------------------------------------
+struct BwdParams {
+    const void *q, *k, *v, *d_out, *out;
+    const float *lse;
+    void *dq, *dk, *dv;
+    int batch, q_heads, kv_heads, seq_len, head_dim, group;
+    int causal;
+    float scale;
+};
+int launch_backward_simt(flat_ctx *ctx, int dtype, const BwdParams &p);
+bool backward_sm100_supported(const BwdParams &p);
+uint64_t backward_sm100_workspace_bytes(const BwdParams &p);
+int launch_backward_sm100(flat_ctx *ctx, const BwdParams &p);
+
+}  // namespace flat
