@@ -170,7 +170,7 @@ def test_paged_cache_append_reset_reuse_then_decode():
         assert gen == 0
         assert np.array_equal(K[page * ps + offset].numpy(), k_all[t]) and np.array_equal(V[page * ps + offset].numpy(), v_all[t])
     with pytest.raises(fa.FlatAttentionError) as e:
-        cache.record_append(dev(k_all), dev(v_all), 7)
+        cache.record_append(dev(ramp(7 * W, 0.3)), dev(ramp(7 * W, 0.4)), 7)
     assert e.value.kind == "CapacityExceeded" and len(cache) == 6
     cache.reset()
     assert len(cache) == 0 and cache.generation() == 1 and cache.table().address(0) is None
