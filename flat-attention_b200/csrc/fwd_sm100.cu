@@ -1,6 +1,615 @@
+// tcgen05 forward: causal / non-causal online-softmax attention for bf16 storage, head_dim 64 or
+// 128, GQA by head mapping, RoPE, rectangular shapes, K/V contiguous or read through a page table.
+//
+// One CTA owns 256 consecutive query rows of one (batch, q_head) as two 128-row tiles that
+// ping-pong on the tensor core.  Warp roles (384 threads):
+//   warps 0-3  softmax of Q tile 0 : thread t owns query row t (TMEM lane t), no shuffles
+//   warps 4-7  softmax of Q tile 1
+//   warp  8    TMA producer        : Q tiles once, then K_j, V_j through an mbarrier ring
+//   warp  9    MMA issuer          : one thread issues every tcgen05.mma and tcgen05.commit
+// Per KV tile j and Q tile w:  S_w = Q_w K_j^T (SS MMA, f32 in TMEM)  ->  softmax warps read S_w
+// from TMEM, track the running max (rescaling O_w in TMEM only when the max grows by more than
+// 2^8), write P_w = exp2(S_w*c - m) as bf16 over S_w  ->  O_w += P_w V_j (A operand from TMEM).
+// The N x N matrix never leaves TMEM.  Tensor-core order S0 S1 | PV0 S0' PV1 S1' | ... keeps the
+// pipe busy with one tile's MMAs while the other tile is in softmax.
+//
+// RoPE: the rotation is applied by a prologue kernel that writes rotated Q and K as fp16 into
+// context scratch; fp16 keeps the rounding of the rotated operands eight times smaller than bf16
+// would, which the 2e-3 LSE tolerance needs.  When the cache already holds rotated bf16 K
+// (rotate_k = 0) only Q is rotated; tcgen05.mma kind::f16 takes A and B of one format only, so
+// rotated Q is then written as two bf16 tensors hi + lo (lo = bf16(q - hi)) and S = Q_hi K^T +
+// Q_lo K^T costs one extra QK MMA pass.
+// Semantics: Appendix of the forward contract (src/projection_asymmetric.rs:97-238): key k is
+// visible to local row q iff !causal || k <= query_position_offset + q; LSE = max + ln(sum).
+#include <cuda.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+
 #include "common.h"
+#include "sm100_ptx.cuh"
+
 namespace flat {
-bool forward_sm100_supported(const FwdParams &) { return false; }
-uint64_t forward_sm100_workspace_bytes(const FwdParams &) { return 0; }
-int launch_forward_sm100(flat_ctx *ctx, const FwdParams &) { return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE, "not built"); }
+namespace {
+
+using namespace sm100;
+
+constexpr int kTileRows = 128;
+constexpr int kThreads = 384;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+constexpr float kRescaleThreshold = 8.0f;  // log2 domain
+
+struct KernelParams {
+    CUtensorMap map_q, map_q_lo, map_k, map_v;
+    void *o;
+    float *lse;
+    int64_t o_bs, o_hs, o_rs, lse_hs;
+    int batch, q_heads, kv_heads, q_len, kv_len, group;
+    int causal;
+    long long causal_off;
+    float scale_log2;
+    uint32_t idesc_qk, idesc_pv;
+    const int32_t *page_table;
+    int page_size, max_pages, physical_pages;
+    int q_blocks;
+    DeviceStatus *status;
+    float *debug_s;
+};
+
+// SPLIT: Q arrives as bf16 hi + lo parts (two smem tiles per Q tile).
+template <int D, bool SPLIT> struct Cfg {
+    static constexpr int kBoxes = D / 64;                  // 64-element (128-byte) column boxes per row
+    static constexpr int kBoxBytes = kTileRows * 128;      // 128 rows x 128 B
+    static constexpr int kTileBytes = kBoxes * kBoxBytes;  // one Q / K / V tile
+    static constexpr int kQParts = SPLIT ? 2 : 1;
+    static constexpr int kStages = D == 128 ? (SPLIT ? 3 : 4) : 8;  // K/V ring entries
+    static constexpr int kBars = 2 + 2 * kStages + 6;
+    static constexpr int kSmemBytes = (2 * kQParts + kStages) * kTileBytes + kBars * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ void record_timeout(const KernelParams &p, int where) {
+    if (p.status) {
+        p.status->code = FLAT_ERR_DEVICE_WAIT_TIMEOUT;
+        p.status->where = where;
+    }
 }
+
+template <int D, bool SPLIT>
+__global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_constant__ KernelParams p) {
+    using C = Cfg<D, SPLIT>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *q_s = smem;
+    uint8_t *kv_s = smem + 2 * C::kQParts * C::kTileBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(kv_s + C::kStages * C::kTileBytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + C::kBars);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const uint32_t bar0 = smem_u32(bars);
+    auto q_full = [&](int w) { return bar0 + 8u * w; };
+    auto kv_full = [&](int s) { return bar0 + 8u * (2 + s); };
+    auto kv_empty = [&](int s) { return bar0 + 8u * (2 + C::kStages + s); };
+    auto s_full = [&](int w) { return bar0 + 8u * (2 + 2 * C::kStages + w); };
+    auto p_full = [&](int w) { return bar0 + 8u * (4 + 2 * C::kStages + w); };
+    auto o_final = [&](int w) { return bar0 + 8u * (6 + 2 * C::kStages + w); };
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    // block -> (query block, batch, head); late (long) query blocks first
+    const int total_bh = p.batch * p.q_heads;
+    const int lin = blockIdx.x;
+    const int qb = p.q_blocks - 1 - lin / total_bh;
+    const int bh = lin % total_bh;
+    const int b = bh / p.q_heads;
+    const int h = bh % p.q_heads;
+    const int kvh = h / p.group;
+    const int r0 = qb * 2 * kTileRows;
+
+    int n_tiles[2];
+    bool active[2];
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+        const int first = r0 + w * kTileRows;
+        active[w] = first < p.q_len;
+        long long visible = p.kv_len;
+        if (p.causal) {
+            const long long last_row = min(first + kTileRows - 1, p.q_len - 1);
+            visible = min((long long)p.kv_len, p.causal_off + last_row + 1);
+        }
+        n_tiles[w] = active[w] ? (int)((visible + kTileRows - 1) / kTileRows) : 0;
+    }
+    const int n_max = max(n_tiles[0], n_tiles[1]);
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int w = 0; w < 2; ++w) {
+            mbar_init(q_full(w), 1);
+            mbar_init(s_full(w), 1);
+            mbar_init(p_full(w), 4);
+            mbar_init(o_final(w), 1);
+        }
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(kv_full(s), 1);
+            mbar_init(kv_empty(s), 1);
+        }
+        mbar_fence_init();
+        fence_proxy_async();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t col_s[2] = {0u, 128u};
+    const uint32_t col_o[2] = {256u, 256u + D};
+
+    if (warp == kProducerWarp) {
+        // ================= TMA producer =================
+        if (lane == 0) {
+            tma_prefetch_desc(&p.map_q);
+            if (SPLIT) tma_prefetch_desc(&p.map_q_lo);
+            tma_prefetch_desc(&p.map_k);
+            tma_prefetch_desc(&p.map_v);
+            for (int w = 0; w < 2; ++w) {
+                if (!active[w]) continue;
+                mbar_expect_tx(q_full(w), C::kQParts * C::kTileBytes);
+                for (int part = 0; part < C::kQParts; ++part)
+                    for (int kb = 0; kb < C::kBoxes; ++kb)
+                        tma_load_4d(smem_u32(q_s + (w * C::kQParts + part) * C::kTileBytes + kb * C::kBoxBytes),
+                                    part ? &p.map_q_lo : &p.map_q, kb * 64, r0 + w * kTileRows, h, b, q_full(w));
+            }
+            bool ok = true;
+            for (int i = 0; ok && i < 2 * n_max; ++i) {
+                const int s = i % C::kStages;
+                const uint32_t phase = (i / C::kStages) & 1;
+                if (!mbar_wait(kv_empty(s), phase ^ 1, abort_flag)) {
+                    record_timeout(p, 100 + s);
+                    ok = false;
+                    break;
+                }
+                const int j = i >> 1;
+                const CUtensorMap *map = (i & 1) ? &p.map_v : &p.map_k;
+                const uint32_t dst = smem_u32(kv_s + s * C::kTileBytes);
+                mbar_expect_tx(kv_full(s), C::kTileBytes);
+                if (p.page_table) {
+                    const int pages_per_tile = kTileRows / p.page_size;
+                    for (int pg = 0; pg < pages_per_tile; ++pg) {
+                        const int tok = j * kTileRows + pg * p.page_size;
+                        const int page = tok < p.kv_len ? p.page_table[(long long)b * p.max_pages + tok / p.page_size]
+                                                        : p.physical_pages;  // out of range: zero fill
+                        for (int kb = 0; kb < C::kBoxes; ++kb)
+                            tma_load_4d(dst + kb * C::kBoxBytes + pg * p.page_size * 128, map, kb * 64, 0, kvh, page,
+                                        kv_full(s));
+                    }
+                } else {
+                    for (int kb = 0; kb < C::kBoxes; ++kb)
+                        tma_load_4d(dst + kb * C::kBoxBytes, map, kb * 64, j * kTileRows, kvh, b, kv_full(s));
+                }
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ================= MMA issuer =================
+        if (lane == 0) {
+            bool ok = true;
+            auto wait = [&](uint32_t bar, uint32_t parity, int where) {
+                if (!ok) return;
+                if (!mbar_wait(bar, parity, abort_flag)) {
+                    record_timeout(p, where);
+                    ok = false;
+                }
+            };
+            auto issue_s = [&](int w, int stage) {
+                const uint32_t b0 = smem_u32(kv_s + stage * C::kTileBytes);
+#pragma unroll
+                for (int part = 0; part < C::kQParts; ++part) {
+                    const uint32_t a0 = smem_u32(q_s + (w * C::kQParts + part) * C::kTileBytes);
+#pragma unroll
+                    for (int kk = 0; kk < D / 16; ++kk) {
+                        const uint32_t off = (kk / 4) * C::kBoxBytes + (kk % 4) * 32;
+                        mma_ss(tmem_base + col_s[w], make_smem_desc(a0 + off, 0, 1024),
+                               make_smem_desc(b0 + off, 0, 1024), p.idesc_qk, (part > 0 || kk > 0));
+                    }
+                }
+            };
+            auto issue_pv = [&](int w, int stage, int j) {
+                const uint32_t b0 = smem_u32(kv_s + stage * C::kTileBytes);
+#pragma unroll
+                for (int kk = 0; kk < kTileRows / 16; ++kk)
+                    mma_ts(tmem_base + col_o[w], tmem_base + col_s[w] + kk * 8,
+                           make_smem_desc(b0 + kk * 16 * 128, C::kBoxBytes, 1024), p.idesc_pv, (j > 0 || kk > 0));
+            };
+            auto stage_of = [&](int i) { return i % C::kStages; };
+            auto phase_of = [&](int i) { return (uint32_t)((i / C::kStages) & 1); };
+
+            for (int w = 0; w < 2; ++w)
+                if (active[w]) wait(q_full(w), 0, 200 + w);
+            // prologue: S_w(0)
+            wait(kv_full(stage_of(0)), phase_of(0), 210);
+            if (ok) {
+                tc_fence_after();
+                for (int w = 0; w < 2; ++w) {
+                    if (n_tiles[w] > 0) {
+                        issue_s(w, stage_of(0));
+                        tc_commit(s_full(w));
+                    }
+                }
+                tc_commit(kv_empty(stage_of(0)));
+            }
+            for (int j = 0; ok && j < n_max; ++j) {
+                const int iv = 2 * j + 1, ik = 2 * j + 2;
+                wait(kv_full(stage_of(iv)), phase_of(iv), 220);
+                bool k_ready = false;
+                for (int w = 0; w < 2 && ok; ++w) {
+                    if (j >= n_tiles[w]) continue;
+                    wait(p_full(w), j & 1, 230 + w);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_pv(w, stage_of(iv), j);
+                    if (w == 1 || j >= n_tiles[1]) tc_commit(kv_empty(stage_of(iv)));  // last reader of V_j
+                    if (j + 1 < n_tiles[w]) {
+                        if (!k_ready) {
+                            wait(kv_full(stage_of(ik)), phase_of(ik), 240);
+                            if (!ok) break;
+                            tc_fence_after();
+                            k_ready = true;
+                        }
+                        issue_s(w, stage_of(ik));
+                        tc_commit(s_full(w));
+                        if (w == 1 || j + 1 >= n_tiles[1]) tc_commit(kv_empty(stage_of(ik)));  // last reader of K_{j+1}
+                    } else {
+                        tc_commit(o_final(w));
+                    }
+                }
+            }
+        }
+    } else if (warp < 8) {
+        // ================= softmax + epilogue =================
+        const int w = warp >> 2;
+        if (active[w]) {
+            const int lane_base = (warp & 3) * 32;
+            const int row_in_tile = lane_base + lane;
+            const int row = r0 + w * kTileRows + row_in_tile;
+            const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16);
+            const uint32_t t_s = t_lane + col_s[w];
+            const uint32_t t_o = t_lane + col_o[w];
+            long long lim = (long long)p.kv_len - 1;  // last visible key of this row
+            if (p.causal) lim = min(lim, p.causal_off + row);
+            float m = -INFINITY, l = 0.f;
+            bool ok = true;
+            const int n = n_tiles[w];
+            for (int j = 0; j < n; ++j) {
+                if (!mbar_wait(s_full(w), j & 1, abort_flag)) {
+                    record_timeout(p, 300 + w);
+                    ok = false;
+                    break;
+                }
+                tc_fence_after();
+                const int key0 = j * kTileRows;
+                const bool need_mask = (long long)key0 + kTileRows - 1 > lim;
+                const int vis = (int)min((long long)kTileRows, lim - key0 + 1);  // visible columns (may be <= 0)
+                uint32_t r[32];
+                // pass 1: row maximum of the raw scores
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    tmem_ld32(t_s + c * 32, r);
+                    tc_wait_ld();
+                    if (D == 128 && p.debug_s && lin == 0 && w == 0 && j == 0) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) p.debug_s[row_in_tile * 128 + c * 32 + i] = __uint_as_float(r[i]);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        float v = __uint_as_float(r[i]);
+                        if (need_mask && c * 32 + i >= vis) v = -INFINITY;
+                        mx = fmaxf(mx, v);
+                    }
+                }
+                const float m_cand = fmaxf(m, mx * p.scale_log2);
+                const bool grow = (m_cand - m) > kRescaleThreshold;
+                float alpha = 1.0f;
+                if (grow) {
+                    alpha = ex2(m - m_cand);
+                    m = m_cand;
+                }
+                if (j > 0 && __any_sync(0xffffffffu, grow)) {
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        tmem_ld32(t_o + c * 32, r);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+                        tmem_st32(t_o + c * 32, r);
+                    }
+                }
+                l *= alpha;
+                // pass 2: P = exp2(S*c - m) as bf16, written over S
+                const float neg_m = -m;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    tmem_ld32(t_s + c * 32, r);
+                    tc_wait_ld();
+                    uint32_t pk[16];
+#pragma unroll
+                    for (int i = 0; i < 32; i += 2) {
+                        float p0 = ex2(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
+                        float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
+                        if (need_mask) {
+                            if (c * 32 + i >= vis) p0 = 0.f;
+                            if (c * 32 + i + 1 >= vis) p1 = 0.f;
+                        }
+                        l += p0 + p1;
+                        __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                        pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                    }
+                    tmem_st16(t_s + c * 16, pk);
+                }
+                tc_wait_st();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(p_full(w));
+            }
+            if (ok) {
+                if (!mbar_wait(o_final(w), 0, abort_flag)) {
+                    record_timeout(p, 310 + w);
+                    ok = false;
+                }
+            }
+            if (ok) {
+                tc_fence_after();
+                const float inv = 1.0f / l;
+                const bool store = row < p.q_len;
+                __nv_bfloat16 *op = reinterpret_cast<__nv_bfloat16 *>(p.o) + (long long)b * p.o_bs + (long long)h * p.o_hs +
+                                    (long long)row * p.o_rs;
+                uint32_t r[32];
+#pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    tmem_ld32(t_o + c * 32, r);
+                    tc_wait_ld();
+                    if (store) {
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            __nv_bfloat162 h2 =
+                                __floats2bfloat162_rn(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                            pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                        }
+                        uint4 *dst = reinterpret_cast<uint4 *>(op + c * 32);
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4)
+                            dst[q4] = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+                    }
+                }
+                if (store) p.lse[((long long)b * p.q_heads + h) * p.lse_hs + row] = (m + log2f(l)) * kLn2;
+            }
+        }
+    }
+
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let copies in flight land before the CTA exits
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// Rotation prologue: x (bf16, strided) -> y (fp16, compact [B, H, N, D]) rotated at pos_off + row
+// with interleaved pairs (src/rotary_grouped.rs:36-50).  One thread moves 8 elements (16 bytes).
+struct InvFreq {
+    float f[kMaxHeadDim / 2];
+};
+
+// y_lo == nullptr: y receives fp16.  Otherwise y / y_lo receive the bf16 hi / lo parts.
+__global__ void __launch_bounds__(256) rotate_to_f16_kernel(const __nv_bfloat16 *__restrict__ x, void *__restrict__ y,
+                                                            void *__restrict__ y_lo, int heads, int rows, int head_dim,
+                                                            int64_t bs, int64_t hs, int64_t rs, int64_t total_vec,
+                                                            int64_t pos_off, InvFreq inv_freq) {
+    const int vec_per_row = head_dim / 8;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec; i += (int64_t)gridDim.x * blockDim.x) {
+        const int v = (int)(i % vec_per_row);
+        const int64_t rowi = i / vec_per_row;
+        const int n = (int)(rowi % rows);
+        const int64_t bh = rowi / rows;
+        const int hh = (int)(bh % heads);
+        const int64_t bb = bh / heads;
+        const uint4 raw = *reinterpret_cast<const uint4 *>(x + bb * bs + hh * hs + (int64_t)n * rs + v * 8);
+        const __nv_bfloat162 *in = reinterpret_cast<const __nv_bfloat162 *>(&raw);
+        uint32_t out[4], out_lo[4];
+        const float pos = (float)(pos_off + n);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(in[e]);
+            const float angle = __fmul_rn(pos, inv_freq.f[v * 4 + e]);
+            float s, c;
+            sincosf(angle, &s, &c);
+            const float re = f.x * c - f.y * s, ro = f.x * s + f.y * c;
+            if (y_lo) {
+                const __nv_bfloat162 hi = __floats2bfloat162_rn(re, ro);
+                const float2 hf = __bfloat1622float2(hi);
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(re - hf.x, ro - hf.y);
+                out[e] = *reinterpret_cast<const uint32_t *>(&hi);
+                out_lo[e] = *reinterpret_cast<const uint32_t *>(&lo);
+            } else {
+                const __half2 hh2 = __floats2half2_rn(re, ro);
+                out[e] = *reinterpret_cast<const uint32_t *>(&hh2);
+            }
+        }
+        const int64_t off = (rowi * head_dim + v * 8) * 2;
+        *reinterpret_cast<uint4 *>(static_cast<char *>(y) + off) = make_uint4(out[0], out[1], out[2], out[3]);
+        if (y_lo)
+            *reinterpret_cast<uint4 *>(static_cast<char *>(y_lo) + off) = make_uint4(out_lo[0], out_lo[1], out_lo[2], out_lo[3]);
+    }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+    static EncodeFn fn = [] {
+        void *sym = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            sym = nullptr;
+        return reinterpret_cast<EncodeFn>(sym);
+    }();
+    return fn;
+}
+
+// 4-D map over (d, row, head, batch) with a (64, box_rows, 1, 1) box and 128-byte swizzle.
+int make_map(flat_ctx *ctx, CUtensorMap *map, bool f16, const void *base, uint64_t head_dim, uint64_t rows,
+             uint64_t heads, uint64_t batch, int64_t rs, int64_t hs, int64_t bs, uint32_t box_rows) {
+    EncodeFn fn = encode_fn();
+    if (!fn) return fail(ctx, FLAT_ERR_UNAVAILABLE, "cuTensorMapEncodeTiled is not available from this driver");
+    cuuint64_t dims[4] = {head_dim, rows, heads, batch};
+    cuuint64_t strides[3] = {(cuuint64_t)rs * 2, (cuuint64_t)hs * 2, (cuuint64_t)bs * 2};
+    for (int i = 0; i < 3; ++i)
+        if (strides[i] == 0) strides[i] = 16;  // extent-1 dimensions still need a legal stride
+    cuuint32_t box[4] = {64, box_rows, 1, 1};
+    cuuint32_t estr[4] = {1, 1, 1, 1};
+    CUresult r = fn(map, f16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                    const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail(ctx, FLAT_ERR_EXECUTION, "cuTensorMapEncodeTiled failed with %d", (int)r);
+    return FLAT_OK;
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+bool forward_sm100_supported(const FwdParams &p) {
+    if (p.head_dim != 64 && p.head_dim != 128) return false;
+    if (p.varlen) return false;
+    if (p.q_len < 32 || p.kv_len < 32) return false;  // tiny shapes: the generic kernel is the better fit
+    if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.o)) return false;
+    const int64_t strides[] = {p.q_bs, p.q_hs, p.q_rs, p.kv_bs, p.kv_hs, p.kv_rs, p.o_bs, p.o_hs, p.o_rs};
+    for (int64_t s : strides)
+        if (s % 8 != 0) return false;
+    if (p.page_table) {
+        if (p.rope_k) return false;  // the paged cache holds rotated K
+        if (p.batch != 1) return false;
+        const int ps = p.page_size;
+        if (!(ps == 8 || ps == 16 || ps == 32 || ps == 64 || ps == 128)) return false;
+    }
+    if (p.rope_k && !p.rope_q) return false;
+    return true;
+}
+
+uint64_t forward_sm100_workspace_bytes(const FwdParams &p) {
+    uint64_t bytes = 0;
+    if (p.rope_q) bytes += (uint64_t)p.batch * p.q_heads * p.q_len * p.head_dim * 2 * (p.rope_k ? 1 : 2);
+    bytes = (bytes + 255) & ~uint64_t(255);
+    if (p.rope_k) bytes += (uint64_t)p.batch * p.kv_heads * p.kv_len * p.head_dim * 2;
+    return bytes;
+}
+
+int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
+    int st = ensure_workspace(ctx, kWorkspaceMeta + forward_sm100_workspace_bytes(p) + 128 * 128 * 4);
+    if (st) return st;
+    const int D = p.head_dim;
+    const void *q_ptr = p.q, *k_ptr = p.k;
+    int64_t q_rs = p.q_rs, q_hs = p.q_hs, q_bs = p.q_bs;
+    int64_t k_rs = p.kv_rs, k_hs = p.kv_hs, k_bs = p.kv_bs;
+    bool q_f16 = false, k_f16 = false;
+    char *scratch = scratch_ptr(ctx);
+    const bool split = p.rope_q && !p.rope_k;
+    const void *q_lo_ptr = nullptr;
+    if (p.rope_q) {
+        InvFreq f;
+        std::memcpy(f.f, p.inv_freq, sizeof f.f);
+        const uint64_t q_bytes = (uint64_t)p.batch * p.q_heads * p.q_len * D * 2;
+        void *rq = scratch;
+        void *rq_lo = split ? scratch + q_bytes : nullptr;
+        const int64_t vecs = (int64_t)p.batch * p.q_heads * p.q_len * (D / 8);
+        int blocks = (int)std::min<int64_t>((vecs + 255) / 256, (int64_t)ctx->sm_count * 16);
+        rotate_to_f16_kernel<<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const __nv_bfloat16 *>(p.q), rq, rq_lo,
+                                                              p.q_heads, p.q_len, D, p.q_bs, p.q_hs, p.q_rs, vecs,
+                                                              p.q_rope_off, f);
+        ctx->launches += 1;
+        q_ptr = rq;
+        q_lo_ptr = rq_lo;
+        q_rs = D; q_hs = (int64_t)p.q_len * D; q_bs = q_hs * p.q_heads;
+        q_f16 = !split;
+        if (p.rope_k) {
+            uint64_t off = (q_bytes + 255) & ~uint64_t(255);
+            void *rk = scratch + off;
+            const int64_t kvecs = (int64_t)p.batch * p.kv_heads * p.kv_len * (D / 8);
+            blocks = (int)std::min<int64_t>((kvecs + 255) / 256, (int64_t)ctx->sm_count * 16);
+            rotate_to_f16_kernel<<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const __nv_bfloat16 *>(p.k), rk, nullptr,
+                                                                  p.kv_heads, p.kv_len, D, p.kv_bs, p.kv_hs, p.kv_rs, kvecs,
+                                                                  p.k_rope_off, f);
+            ctx->launches += 1;
+            k_ptr = rk;
+            k_rs = D; k_hs = (int64_t)p.kv_len * D; k_bs = k_hs * p.kv_heads;
+            k_f16 = true;
+        }
+    }
+
+    KernelParams kp{};
+    if ((st = make_map(ctx, &kp.map_q, q_f16, q_ptr, D, p.q_len, p.q_heads, p.batch, q_rs, q_hs, q_bs, kTileRows))) return st;
+    if (split && (st = make_map(ctx, &kp.map_q_lo, false, q_lo_ptr, D, p.q_len, p.q_heads, p.batch, q_rs, q_hs, q_bs, kTileRows)))
+        return st;
+    if (p.page_table) {
+        // physical layout [pages, page_size, kv_heads*D]: dims (d, token in page, head, page)
+        const int64_t row = p.page_row_stride;
+        if ((st = make_map(ctx, &kp.map_k, false, p.k, D, p.page_size, p.kv_heads, p.max_pages, row, p.kv_hs,
+                           row * p.page_size, p.page_size))) return st;
+        if ((st = make_map(ctx, &kp.map_v, false, p.v, D, p.page_size, p.kv_heads, p.max_pages, row, p.kv_hs,
+                           row * p.page_size, p.page_size))) return st;
+    } else {
+        if ((st = make_map(ctx, &kp.map_k, k_f16, k_ptr, D, p.kv_len, p.kv_heads, p.batch, k_rs, k_hs, k_bs, kTileRows))) return st;
+        if ((st = make_map(ctx, &kp.map_v, false, p.v, D, p.kv_len, p.kv_heads, p.batch, p.kv_rs, p.kv_hs, p.kv_bs, kTileRows))) return st;
+    }
+    kp.o = p.o;
+    kp.lse = p.lse;
+    kp.o_bs = p.o_bs; kp.o_hs = p.o_hs; kp.o_rs = p.o_rs; kp.lse_hs = p.lse_hs;
+    kp.batch = p.batch; kp.q_heads = p.q_heads; kp.kv_heads = p.kv_heads; kp.q_len = p.q_len; kp.kv_len = p.kv_len;
+    kp.group = p.group;
+    kp.causal = p.causal;
+    kp.causal_off = p.causal_off;
+    kp.scale_log2 = p.scale * kLog2e;
+    kp.idesc_qk = make_idesc(q_f16 ? kFmtF16 : kFmtBF16, k_f16 ? kFmtF16 : kFmtBF16, 0, 0, 128, 128);
+    kp.idesc_pv = make_idesc(kFmtBF16, kFmtBF16, 0, 1, 128, (uint32_t)D);
+    kp.page_table = p.page_table;
+    kp.page_size = p.page_size;
+    kp.max_pages = p.max_pages;
+    kp.physical_pages = p.max_pages;
+    kp.q_blocks = (p.q_len + 2 * kTileRows - 1) / (2 * kTileRows);
+    kp.status = ctx->dev_status;
+    kp.debug_s = nullptr;
+    const char *dbg = getenv("FLAT_SM100_DEBUG_S");
+    if (dbg && dbg[0] == '1')
+        kp.debug_s = reinterpret_cast<float *>(scratch + ((forward_sm100_workspace_bytes(p) + 255) & ~uint64_t(255)));
+
+    const long long grid = (long long)kp.q_blocks * p.batch * p.q_heads;
+    if (grid > 2147483647LL) return fail(ctx, FLAT_ERR_DISPATCH_LIMIT, "forward grid of %lld blocks is too large", grid);
+    auto run = [&](auto kernel, int smem_bytes) -> int {
+        FLAT_CUDA_OK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        kernel<<<(unsigned)grid, kThreads, smem_bytes, ctx->stream>>>(kp);
+        return FLAT_OK;
+    };
+    if (D == 128) st = split ? run(fwd_sm100_kernel<128, true>, Cfg<128, true>::kSmemBytes)
+                             : run(fwd_sm100_kernel<128, false>, Cfg<128, false>::kSmemBytes);
+    else st = split ? run(fwd_sm100_kernel<64, true>, Cfg<64, true>::kSmemBytes)
+                    : run(fwd_sm100_kernel<64, false>, Cfg<64, false>::kSmemBytes);
+    if (st) return st;
+    ctx->launches += 1;
+    FLAT_CUDA_OK(ctx, cudaGetLastError());
+    return FLAT_OK;
+}
+
+}  // namespace flat

@@ -1,0 +1,119 @@
+"""bf16 tensor-core forward (tcgen05) against the CPU oracle evaluated on the de-quantised bf16
+inputs (policy of docs/m8-precision.md:74-85): max-abs error <= 2e-2 on O and <= 2e-3 on LSE.
+RoPE cases use the materialise-then-grouped oracle route, bit-identical to the fused oracle
+(tests/rotary_grouped.rs:48-143)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import binding as ob
+from tests.gpu_util import bf16_round, ctx, fa, run_forward
+
+pytestmark = pytest.mark.gpu
+O_TOL, LSE_TOL = 2e-2, 2e-3
+
+
+def randn(n, seed):
+    return bf16_round(torch.randn(n, generator=torch.Generator().manual_seed(seed)).numpy())
+
+
+def check(o, l, eo, el, what=""):
+    eo, el = np.asarray(eo).reshape(-1), np.asarray(el).reshape(-1)
+    assert np.isfinite(o).all() and np.isfinite(l).all(), what
+    assert np.abs(o - eo).max() <= O_TOL, (what, float(np.abs(o - eo).max()))
+    assert np.abs(l - el).max() <= LSE_TOL, (what, float(np.abs(l - el).max()))
+
+
+SHAPES = [(1, 4, 2, 256, 128), (2, 2, 2, 128, 128), (1, 4, 1, 200, 128), (1, 2, 2, 333, 64), (1, 8, 2, 512, 64),
+          (1, 2, 1, 640, 128), (1, 4, 4, 40, 128)]
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,N,D", SHAPES)
+@pytest.mark.parametrize("causal", [False, True])
+def test_grouped_bf16(B, Hq, Hkv, N, D, causal):
+    q, k, v = randn(B * Hq * N * D, 1), randn(B * Hkv * N * D, 2), randn(B * Hkv * N * D, 3)
+    o, l = run_forward("grouped", fa.BF16, fa.shape(B, Hq, Hkv, N, N, D), fa.config(causal), q, k, v)
+    eo, el = ob.forward_reference_grouped(q, k, v, B, Hq, Hkv, N, D, causal)
+    check(o, l, eo, el)
+    assert ctx().device_status() == 0
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,N,D,theta,off", [(1, 4, 2, 256, 128, 5e5, 0), (1, 2, 1, 300, 64, 1e4, 11),
+                                                    (2, 4, 4, 160, 128, 5e5, 4000)])
+def test_grouped_rope_bf16(B, Hq, Hkv, N, D, theta, off):
+    q, k, v = randn(B * Hq * N * D, 1), randn(B * Hkv * N * D, 2), randn(B * Hkv * N * D, 3)
+    for causal in (True, False):
+        o, l = run_forward("grouped_rope", fa.BF16, fa.shape(B, Hq, Hkv, N, N, D), fa.config(causal), q, k, v,
+                           rot=fa.rotary(theta, off))
+        rq = ob.rotate_rows(q, D, np.tile(np.arange(N, dtype=np.uint64) + off, B * Hq), theta)
+        rk = ob.rotate_rows(k, D, np.tile(np.arange(N, dtype=np.uint64) + off, B * Hkv), theta)
+        eo, el = ob.forward_reference_grouped(rq, rk, v, B, Hq, Hkv, N, D, causal)
+        check(o, l, eo, el)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Nq,Nkv,D,causal,coff,qr,kr,rotate_k", [
+    (1, 4, 2, 256, 256, 128, True, 0, 7, 7, True),
+    (2, 4, 2, 100, 300, 128, True, 200, 200, 0, True),
+    (1, 8, 2, 130, 517, 64, True, 387, 400, 13, True),
+    (1, 4, 1, 64, 400, 128, False, 0, 50, 3, True),
+    (1, 4, 2, 128, 384, 128, True, 256, 256, 0, False),   # pre-rotated K: fp16 Q x bf16 K
+])
+def test_projection_rope_asymmetric_bf16(B, Hq, Hkv, Nq, Nkv, D, causal, coff, qr, kr, rotate_k):
+    theta = 5e5
+    q, k, v = randn(B * Nq * Hq * D, 1), randn(B * Nkv * Hkv * D, 2), randn(B * Nkv * Hkv * D, 3)
+    kpos = np.repeat(np.tile(np.arange(Nkv, dtype=np.uint64) + kr, B), Hkv)
+    qpos = np.repeat(np.tile(np.arange(Nq, dtype=np.uint64) + qr, B), Hq)
+    k_in = k
+    if not rotate_k:  # the cache convention: K rotated once, stored in bf16
+        k_in = bf16_round(ob.rotate_rows(k, D, kpos, theta))
+        rk = k_in
+    else:
+        rk = ob.rotate_rows(k, D, kpos, theta)
+    rq = ob.rotate_rows(q, D, qpos, theta)
+    o, l = run_forward("projection_rope_asymmetric", fa.BF16, fa.shape(B, Hq, Hkv, Nq, Nkv, D, coff), fa.config(causal),
+                       q, k_in, v, rot=fa.rotary(theta, qr, kr, rotate_k=rotate_k))
+    rows = [(b, h, r) for b in range(B) for h in range(Hq) for r in range(Nq)]
+    eo, el = ob.forward_rows(rq, rk, v, ob._shape(B, Hq, Hkv, Nq, Nkv, D, coff), ob.PROJECTION, rows, causal, threads=8)
+    o = o.reshape(B, Nq, Hq, D).transpose(0, 2, 1, 3).reshape(-1)
+    check(o, l, eo, el)
+    assert ctx().device_status() == 0
+
+
+def test_config2_llama8b_prefill_sampled_rows():
+    """B=4, Hq=32, Hkv=8, N=4096, D=128, causal, RoPE theta 5e5: oracle on sampled
+    (batch, q_head, row) triples including tile and sequence boundaries; V = 1 gives O = 1."""
+    B, Hq, Hkv, N, D, theta = 4, 32, 8, 4096, 128, 5e5
+    g = torch.Generator().manual_seed(1)
+    q = torch.randn(B, Hq, N, D, generator=torch.Generator().manual_seed(1)).bfloat16()
+    k = torch.randn(B, Hkv, N, D, generator=torch.Generator().manual_seed(2)).bfloat16()
+    v = torch.randn(B, Hkv, N, D, generator=torch.Generator().manual_seed(3)).bfloat16()
+    c = ctx()
+    shp = fa.shape(B, Hq, Hkv, N, N, D)
+    out = c.create_output_buffer(fa.BF16, shp)
+    dq, dk, dv = q.cuda(), k.cuda(), v.cuda()
+    c.forward_grouped_rope(fa.BF16, shp, fa.config(True), fa.rotary(theta, 0), dq, dk, dv, out)
+    o, l = c.split_output(out, fa.BF16, shp)
+    o, l = o.float().cpu().numpy(), l.cpu().numpy()
+    assert c.device_status() == 0
+    rng = np.random.default_rng(0)
+    rows = {(0, 0, 0), (0, 0, 1), (0, 0, 127), (0, 0, 128), (3, 31, 4095), (1, 5, 255), (1, 5, 256), (2, 17, 2047)}
+    while len(rows) < 72:
+        rows.add((int(rng.integers(B)), int(rng.integers(Hq)), int(rng.integers(N))))
+    rows = sorted(rows)
+    qf, kf, vf = q.float().numpy(), k.float().numpy(), v.float().numpy()
+    pos_k = np.tile(np.arange(N, dtype=np.uint64), B * Hkv)
+    rk = ob.rotate_rows(kf, D, pos_k, theta)
+    rq = qf.copy().reshape(B, Hq, N, D)
+    for (b, h, r) in rows:  # only the sampled query rows need rotating
+        rq[b, h, r] = ob.rotate_rows(qf.reshape(B, Hq, N, D)[b, h, r], D, [r], theta)
+    eo, el = ob.forward_rows(rq, rk, vf, ob._shape(B, Hq, Hkv, N, N, D), ob.HEAD_MAJOR, rows, True, threads=8)
+    ao = np.stack([o[b, h, r] for (b, h, r) in rows])
+    al = np.array([l[b, h, r] for (b, h, r) in rows])
+    assert np.abs(ao - eo).max() <= O_TOL, float(np.abs(ao - eo).max())
+    assert np.abs(al - el).max() <= LSE_TOL, float(np.abs(al - el).max())
+    # size-independent properties on the whole output
+    assert np.isfinite(o).all() and np.isfinite(l).all()
+    c.forward_grouped_rope(fa.BF16, shp, fa.config(True), fa.rotary(theta, 0), dq, dk, torch.ones_like(dv), out)
+    o1, l1 = c.split_output(out, fa.BF16, shp)
+    assert (o1.float() - 1.0).abs().max().item() <= 8e-3
+    assert torch.equal(l1.cpu(), torch.from_numpy(l))  # LSE does not depend on V; runs are bitwise repeatable
