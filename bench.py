@@ -1,0 +1,374 @@
+"""Benchmark of the fused-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+Headline workload (one "step"): the Llama-3-8B-shaped prefill of the reference's config list — GQA
+with fused RoPE, B=4, Hq=32, Hkv=8, N=4096, D=128, causal, bf16, theta=5e5 — on synthetic seeded
+N(0,1) inputs.  `value` is attention TFLOP/s (4*B*Hq*N^2*D/2 flop per step) with inputs resident in
+HBM; `e2e` is the same metric through the public call with pinned HOST buffers (H2D of Q/K/V and D2H
+of the packed [O|LSE] inside the timed region).  With N GPUs every rank runs its own batch (weak
+scaling, no collective on the data path) and `value` is the whole-job aggregate.  The paged-decode
+half of the metric (64 sequences, ctx U[512,8192], page 16) is reported in the `decode` object as
+HBM GB/s, the backward and chunked-prefill configs in `backward` / `chunked_prefill`.
+
+`--impl reference` times the reference's own CPU implementation of the path: its scalar oracle,
+restated in C++ under oracle/ (no Rust toolchain exists on these machines), on all host threads,
+each step a bounded sample of query rows of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+C2 = dict(B=4, Hq=32, Hkv=8, N=4096, D=128, theta=500000.0)
+C3 = dict(S=64, Hq=32, Hkv=8, D=128, page=16, lo=512, hi=8192, theta=500000.0)
+C5 = dict(B=2, Hq=32, Hkv=8, N=8192, D=128)
+
+
+def prefill_flops(c):
+    return 4 * c["B"] * c["Hq"] * c["N"] * c["N"] * c["D"] // 2
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], bf16_sustained=d.get("bf16_tflops_sustained"),
+                    source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons through NVML (read-only) while the timed region runs."""
+
+    def __init__(self, device_index, period_s=0.004):
+        self.idx, self.period = device_index, period_s
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._err = None
+
+    def _run(self):
+        try:
+            import pynvml as nv
+            nv.nvmlInit()
+            h = nv.nvmlDeviceGetHandleByIndex(self.idx)
+            self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+            names = {"hw_slowdown": nv.nvmlClocksThrottleReasonHwSlowdown,
+                     "hw_thermal_slowdown": nv.nvmlClocksThrottleReasonHwThermalSlowdown,
+                     "sw_thermal_slowdown": nv.nvmlClocksThrottleReasonSwThermalSlowdown,
+                     "sw_power_cap": nv.nvmlClocksThrottleReasonSwPowerCap}
+            while not self._stop.is_set():
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for name, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+                time.sleep(self.period)
+        except Exception as e:  # NVML missing: report it, never fail the bench
+            self._err = repr(e)
+
+    def start(self):
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+        time.sleep(0.02)
+
+    def stop(self):
+        self._stop.set()
+        if self._thread:
+            self._thread.join(timeout=2)
+        sm = sorted(self.samples)
+        out = {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": self.max_mhz, "samples": len(sm),
+               "reasons": sorted(self.reasons)}
+        if self._err:
+            out["error"] = self._err
+        return out
+
+
+def make_c2_inputs(torch, rank):
+    c = C2
+    q = torch.randn(c["B"], c["Hq"], c["N"], c["D"], generator=torch.Generator().manual_seed(1 + 1000 * rank)).bfloat16()
+    k = torch.randn(c["B"], c["Hkv"], c["N"], c["D"], generator=torch.Generator().manual_seed(2 + 1000 * rank)).bfloat16()
+    v = torch.randn(c["B"], c["Hkv"], c["N"], c["D"], generator=torch.Generator().manual_seed(3 + 1000 * rank)).bfloat16()
+    return q, k, v
+
+
+def oracle_rows_c2(ob, np, q, k, v, rows, threads):
+    """Oracle O/LSE on sampled (b, h, row) of the C2 workload: RoPE materialised with the oracle
+    formula, then the grouped oracle (bit-identical route to the fused oracle)."""
+    c = C2
+    B, Hq, Hkv, N, D, theta = c["B"], c["Hq"], c["Hkv"], c["N"], c["D"], c["theta"]
+    qf, kf, vf = q.float().numpy(), k.float().numpy(), v.float().numpy()
+    rk = ob.rotate_rows(kf, D, np.tile(np.arange(N, dtype=np.uint64), B * Hkv), theta)
+    rq = qf.reshape(B, Hq, N, D).copy()
+    for (b, h, r) in rows:
+        rq[b, h, r] = ob.rotate_rows(rq[b, h, r], D, [r], theta)
+    t0 = time.perf_counter()
+    eo, el = ob.forward_rows(rq, rk, vf, ob._shape(B, Hq, Hkv, N, N, D), ob.HEAD_MAJOR, rows, True, threads=threads)
+    return eo, el, time.perf_counter() - t0
+
+
+def sample_rows(np, count, seed):
+    c = C2
+    rng = np.random.default_rng(seed)
+    return [(int(rng.integers(c["B"])), int(rng.integers(c["Hq"])), int(rng.integers(c["N"]))) for _ in range(count)]
+
+
+def rows_flops(rows):
+    return sum(4 * C2["D"] * (r + 1) for (_, _, r) in rows)
+
+
+def run_reference(args, rank, world):
+    """Reference arm: the scalar CPU oracle (C++ restatement) on all host threads."""
+    if rank != 0:
+        return
+    import numpy as np
+    import torch
+    from oracle import binding as ob
+    ob.build()
+    threads = os.cpu_count() or 1
+    q, k, v = make_c2_inputs(torch, 0)
+    per_step = 256 * threads
+    warm = sample_rows(np, 64, 99)
+    for _ in range(max(args.warmup, 1)):
+        oracle_rows_c2(ob, np, q, k, v, warm, threads)
+    total_flops, total_t = 0, 0.0
+    for s in range(args.steps):
+        rows = sample_rows(np, per_step, 100 + s)
+        _, _, dt = oracle_rows_c2(ob, np, q, k, v, rows, threads)
+        total_flops += rows_flops(rows)
+        total_t += dt
+    tflops = total_flops / total_t / 1e12
+    line = {
+        "impl": "reference", "metric": "prefill_attention_tflops", "value": tflops, "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total_t / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "C2 GQA+RoPE causal prefill B=4 Hq=32 Hkv=8 N=4096 D=128 bf16-quantised inputs",
+                   "sample": f"{per_step} random (batch, q_head, row) query rows per step"},
+        "cpu_baseline": {"value": tflops, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                         "sample": f"{per_step} query rows per step, {args.steps} steps, oracle restated in C++ "
+                                   "(no Rust toolchain on this machine)"},
+        "e2e": {"value": tflops, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def timed_region(torch, dist, world, fn, steps):
+    """barrier + synchronize, K steps between CUDA events, max over ranks (milliseconds)."""
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        fn()
+    stop.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(stop)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+        dist.barrier()
+    return ms
+
+
+def bench_decode(torch, np, fa, ctx, peaks, steps, warmup):
+    """Config 3: batched paged decode, HBM GB/s of the algorithmic bytes."""
+    c = C3
+    S, Hq, Hkv, D, ps = c["S"], c["Hq"], c["Hkv"], c["D"], c["page"]
+    rng = np.random.default_rng(5)
+    lens = (c["lo"] + rng.integers(0, c["hi"] - c["lo"] + 1, S)).astype(np.int32)
+    pages_per = (lens + ps - 1) // ps
+    pool = int(pages_per.sum()) + 64
+    perm = np.random.default_rng(6).permutation(pool).astype(np.int32)
+    maxp = int(pages_per.max())
+    tables = np.zeros((S, maxp), np.int32)
+    at = 0
+    for s in range(S):
+        tables[s, :pages_per[s]] = perm[at:at + pages_per[s]]
+        at += pages_per[s]
+    g = torch.Generator(device="cuda").manual_seed(7)
+    K = torch.randn(pool * ps, Hkv * D, generator=g, device="cuda", dtype=torch.float32).bfloat16()
+    V = torch.randn(pool * ps, Hkv * D, generator=g, device="cuda", dtype=torch.float32).bfloat16()
+    Q = torch.randn(S, Hq * D, generator=g, device="cuda", dtype=torch.float32).bfloat16()
+    qpos = (lens - 1).astype(np.int32)
+    d_tab, d_len, d_pos = torch.from_numpy(tables).cuda(), torch.from_numpy(lens).cuda(), torch.from_numpy(qpos).cuda()
+    out = ctx.empty_bytes(S * Hq * D * 2 + S * Hq * 4)
+    cfg = fa.config(True)
+
+    def step():
+        ctx.decode_paged_batched(fa.BF16, S, Hq, Hkv, D, ps, pool, maxp, d_tab, d_len, d_pos, tables, lens, qpos, cfg,
+                                 c["theta"], Q, K, V, out)
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warmup):
+        step()
+    ctx.set_kernel_timing(True)
+    ctx.take_kernel_time()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(steps):
+        flush.zero_()  # K/V of one step fit in L2 only partly; flush so every step streams from HBM
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step()
+        e1.record()
+        torch.cuda.synchronize()
+        total += e0.elapsed_time(e1)
+    kms, kn = ctx.take_kernel_time()
+    ctx.set_kernel_timing(False)
+    kv_bytes = int(lens.sum()) * Hkv * D * 2 * 2
+    other = S * Hq * D * 2 * 2 + S * Hq * 4 + int(pages_per.sum()) * 4
+    alg = kv_bytes + other
+    ms = total / steps
+    kernel_ms = kms / max(kn, 1)
+    return {
+        "metric": "paged_decode_hbm_gbs", "value": alg / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms,
+        "algorithmic_bytes": alg, "sequences": S, "context_tokens": int(lens.sum()),
+        "roofline": {"bound": "hbm", "achieved": alg / (kernel_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": alg / (kernel_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": None,
+                     "kernel": "decode_kernel", "kernel_ms": kernel_ms, "peak_source": peaks["source"]},
+        "l2": "flushed between steps (256 MiB write)",
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--skip-extras", action="store_true", help="only the headline prefill workload")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    fa = load_package()
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    peaks = load_peaks()
+    ctx = fa.Context(local_rank)
+    c = C2
+    B, Hq, Hkv, N, D, theta = c["B"], c["Hq"], c["Hkv"], c["N"], c["D"], c["theta"]
+    shp = fa.shape(B, Hq, Hkv, N, N, D)
+    cfg, rot = fa.config(True), fa.rotary(theta, 0)
+    q, k, v = make_c2_inputs(torch, rank)
+    hq, hk, hv = q.pin_memory(), k.pin_memory(), v.pin_memory()
+    dq, dk, dv = hq.cuda(non_blocking=True), hk.cuda(non_blocking=True), hv.cuda(non_blocking=True)
+    out = ctx.create_output_buffer(fa.BF16, shp)
+    host_out = torch.empty(out.numel(), dtype=torch.uint8).pin_memory()
+    flops = prefill_flops(c)
+
+    def step():
+        ctx.forward_grouped_rope(fa.BF16, shp, cfg, rot, dq, dk, dv, out)
+
+    def step_e2e():
+        a, b_, c_ = hq.cuda(non_blocking=True), hk.cuda(non_blocking=True), hv.cuda(non_blocking=True)
+        ctx.forward_grouped_rope(fa.BF16, shp, cfg, rot, a, b_, c_, out)
+        host_out.copy_(out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()  # the caller reads the result
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+
+    # parity gate before timing (reference bench protocol): a few sampled rows against the oracle
+    parity = None
+    if rank == 0:
+        from oracle import binding as ob
+        rows = [(0, 0, 0), (0, 0, 129), (B - 1, Hq - 1, N - 1)] + sample_rows(np, 13, 3)
+        eo, el, _ = oracle_rows_c2(ob, np, q, k, v, rows, min(8, os.cpu_count() or 1))
+        o, l = ctx.split_output(out, fa.BF16, shp)
+        ao = np.stack([o[b, h, r].float().cpu().numpy() for (b, h, r) in rows])
+        al = np.array([float(l[b, h, r]) for (b, h, r) in rows])
+        parity = {"rows": len(rows), "max_abs_o": float(np.abs(ao - eo).max()), "max_abs_lse": float(np.abs(al - el).max())}
+        parity["ok"] = parity["max_abs_o"] <= 2e-2 and parity["max_abs_lse"] <= 2e-3
+
+    sampler = ClockSampler(local_rank)
+    launches0 = ctx.launch_count()
+    ctx.set_kernel_timing(True)
+    ctx.take_kernel_time()
+    if rank == 0:
+        sampler.start()
+    ms = timed_region(torch, dist, world, step, args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    kernel_ms, kernel_n = ctx.take_kernel_time()
+    ctx.set_kernel_timing(False)
+    launches = ctx.launch_count() - launches0
+
+    for _ in range(2):
+        step_e2e()
+    ms_e2e = timed_region(torch, dist, world, step_e2e, max(3, min(args.steps, 10)))
+    e2e_steps = max(3, min(args.steps, 10))
+    status = ctx.device_status()
+
+    ms_per_step = ms / args.steps
+    value = world * flops / (ms_per_step * 1e-3) / 1e12
+    kms = kernel_ms / max(kernel_n, 1)
+    # the step is short and the GPU is idle between bench phases: the burst peak is the denominator
+    peak = peaks["bf16_tflops"]
+    line = {
+        "metric": "prefill_attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "C2 GQA+RoPE causal prefill (Llama-3-8B shape): B=4 per GPU, Hq=32, Hkv=8, N=4096, D=128, "
+                               "bf16, theta=5e5, O + f32 LSE", "flop_per_step_per_gpu": flops,
+                   "inputs": "seeded N(0,1) rounded to bf16; 192 MiB of Q/K/V + 160 MiB rotated operands per step "
+                             "exceed the 126 MB L2", "sharding": "independent batches per rank, no collective"},
+        "e2e": {"value": world * flops / (ms_e2e / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": int(hq.numel() + hk.numel() + hv.numel()) * 2, "d2h_bytes_per_step": int(out.numel()),
+                "ms_per_step": ms_e2e / e2e_steps},
+        "gpu_launches": int(launches),
+        "roofline": {"bound": "tensor", "achieved": flops / (kms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                     "frac": flops / (kms * 1e-3) / 1e12 / peak, "traffic": None, "kernel": "fwd_sm100_kernel<128,false>",
+                     "kernel_ms": kms, "peak_source": peaks["source"] + " (burst cuBLAS bf16)"},
+        "clocks": clocks,
+        "parity": parity,
+        "device_status": status,
+    }
+    if rank == 0 and world == 1:
+        from oracle import binding as ob
+        rows = sample_rows(np, 40000, 11)
+        _, _, dt = oracle_rows_c2(ob, np, q, k, v, rows, 1)
+        line["cpu_baseline"] = {"value": rows_flops(rows) / dt / 1e12, "unit": "TFLOP/s", "cores": 1, "kind": "port",
+                                "sample": "40000 random (batch, q_head, row) query rows of the same workload, scalar oracle "
+                                          "restated in C++, %.1f s" % dt}
+        if not args.skip_extras:
+            line["decode"] = bench_decode(torch, np, fa, ctx, peaks, max(5, min(args.steps, 20)), args.warmup)
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

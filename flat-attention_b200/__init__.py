@@ -233,6 +233,15 @@ class Context:
     def reserve_workspace(self, nbytes: int):
         self.check(lib().flat_ctx_reserve_workspace(self.h, C.c_uint64(nbytes)))
 
+    def set_kernel_timing(self, enabled: bool):
+        self.check(lib().flat_ctx_set_kernel_timing(self.h, C.c_int32(int(enabled))))
+
+    def take_kernel_time(self):
+        """(summed milliseconds, launches) of the dominant kernels timed since the last call."""
+        ms, n = C.c_double(), C.c_uint64()
+        self.check(lib().flat_ctx_take_kernel_time(self.h, C.byref(ms), C.byref(n)))
+        return ms.value, n.value
+
     def device_status(self) -> int:
         return int(lib().flat_ctx_device_status(self.h))
 

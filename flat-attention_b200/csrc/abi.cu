@@ -438,6 +438,10 @@ void flat_ctx_destroy(flat_ctx *ctx) {
     if (!ctx) return;
     cudaSetDevice(ctx->device);
     cudaStreamSynchronize(ctx->stream);
+    for (auto &pr : ctx->timed) {
+        cudaEventDestroy(pr.first);
+        cudaEventDestroy(pr.second);
+    }
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     delete ctx;
@@ -507,6 +511,28 @@ int32_t flat_ctx_device_status(flat_ctx *ctx) {
         cudaMemset(ctx->dev_status, 0, sizeof(DeviceStatus));
     }
     return h.code;
+}
+
+int32_t flat_ctx_set_kernel_timing(flat_ctx *ctx, int32_t enabled) {
+    if (!ctx) return FLAT_ERR_NULL_POINTER;
+    ctx->timing = enabled != 0;
+    return FLAT_OK;
+}
+
+int32_t flat_ctx_take_kernel_time(flat_ctx *ctx, double *total_ms, uint64_t *timed_launches) {
+    if (!ctx || !total_ms || !timed_launches) return FLAT_ERR_NULL_POINTER;
+    FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    double sum = 0.0;
+    for (auto &pr : ctx->timed) {
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, pr.first, pr.second) == cudaSuccess) sum += ms;
+        cudaEventDestroy(pr.first);
+        cudaEventDestroy(pr.second);
+    }
+    *total_ms = sum;
+    *timed_launches = ctx->timed.size();
+    ctx->timed.clear();
+    return FLAT_OK;
 }
 
 int32_t flat_upload(flat_ctx *ctx, flat_buffer dst, const void *host_src, uint64_t bytes) {

@@ -9,6 +9,7 @@
 #include <cstdint>
 #include <cstdio>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "../../include/flat_attention_b200.h"
@@ -35,6 +36,9 @@ struct flat_ctx {
     flat::DeviceStatus *dev_status = nullptr;  // device memory
     uint64_t launches = 0;
     std::string detail;
+    // optional timing of the dominant kernel of each call (CUDA events on the launch stream)
+    bool timing = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;
 };
 
 namespace flat {
@@ -44,6 +48,25 @@ int fail(flat_ctx *ctx, int status, const char *fmt, ...);
 
 inline bool mul_ok(uint64_t a, uint64_t b, uint64_t *out) { return !__builtin_mul_overflow(a, b, out); }
 inline bool add_ok(uint64_t a, uint64_t b, uint64_t *out) { return !__builtin_add_overflow(a, b, out); }
+
+// Brackets the dominant kernel of a call with CUDA events when timing is enabled.
+struct KernelTimer {
+    flat_ctx *ctx;
+    cudaEvent_t start = nullptr, stop = nullptr;
+    explicit KernelTimer(flat_ctx *c) : ctx(c) {
+        if (!ctx->timing) return;
+        if (cudaEventCreate(&start) != cudaSuccess || cudaEventCreate(&stop) != cudaSuccess) {
+            start = stop = nullptr;
+            return;
+        }
+        cudaEventRecord(start, ctx->stream);
+    }
+    ~KernelTimer() {
+        if (!start) return;
+        cudaEventRecord(stop, ctx->stream);
+        ctx->timed.emplace_back(start, stop);
+    }
+};
 
 inline size_t dtype_size(int dtype) { return dtype == FLAT_BF16 ? 2 : 4; }
 

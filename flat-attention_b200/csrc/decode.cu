@@ -275,7 +275,10 @@ template <typename T, int LPR, int G>
 int launch_lg(flat_ctx *ctx, const DecodeParams &p) {
     int warps = p.kv_heads < 8 ? p.kv_heads : 8;
     dim3 grid(p.kv_splits, (p.kv_heads + warps - 1) / warps, p.num_seqs);
-    decode_kernel<T, LPR, G><<<grid, warps * 32, 0, ctx->stream>>>(p);
+    {
+        KernelTimer timer(ctx);
+        decode_kernel<T, LPR, G><<<grid, warps * 32, 0, ctx->stream>>>(p);
+    }
     ctx->launches += 1;
     FLAT_CUDA_OK(ctx, cudaGetLastError());
     if (p.kv_splits > 1) {

@@ -599,6 +599,7 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     if (grid > 2147483647LL) return fail(ctx, FLAT_ERR_DISPATCH_LIMIT, "forward grid of %lld blocks is too large", grid);
     auto run = [&](auto kernel, int smem_bytes) -> int {
         FLAT_CUDA_OK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        KernelTimer timer(ctx);
         kernel<<<(unsigned)grid, kThreads, smem_bytes, ctx->stream>>>(kp);
         return FLAT_OK;
     };

@@ -191,6 +191,13 @@ uint64_t flat_ctx_launch_count(const flat_ctx *ctx);
  * FLAT_ERR_DEVICE_WAIT_TIMEOUT); synchronises the stream. */
 int32_t flat_ctx_device_status(flat_ctx *ctx);
 
+/* Kernel timing for benchmarks (the reference benches time encode+submit+poll on the host,
+ * examples/m15_decode_bench.rs:181-203; here the dominant kernel of each call is bracketed with
+ * CUDA events on the context stream).  take: synchronises, returns the summed duration in
+ * milliseconds and the number of timed launches since the last take, and clears the record. */
+int32_t flat_ctx_set_kernel_timing(flat_ctx *ctx, int32_t enabled);
+int32_t flat_ctx_take_kernel_time(flat_ctx *ctx, double *total_ms, uint64_t *timed_launches);
+
 /* WgpuFlatAttention::upload / download_attention (src/wgpu_backend.rs:465-482,588-608):
  * explicit host<->device copies on the context stream; download blocks. */
 int32_t flat_upload(flat_ctx *ctx, flat_buffer dst, const void *host_src, uint64_t bytes);
