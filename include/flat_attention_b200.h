@@ -372,6 +372,31 @@ int32_t flat_decode_paged_batched(flat_ctx *ctx, int32_t dtype, uint64_t num_seq
                                   uint32_t kv_splits, flat_buffer q, flat_buffer k,
                                   flat_buffer v, flat_buffer out_and_lse);
 
+/* The same batched split-KV decode for callers that cannot allocate device memory when the
+ * call is made (a latency-critical serving loop where an allocation would stall the device, a
+ * plug-in under a framework allocator that forbids side allocations, or a process whose memory
+ * budget was fixed at start-up).  It has no
+ * counterpart in the reference.  The per-chunk (O, LSE) partials live in an 8 MiB array that
+ * is part of the library image (every GPU that loads the library holds it until exit) instead
+ * of the growable context workspace; the call issues no cudaMalloc / cudaFree.
+ *  - limit: kv_splits * num_seqs * q_heads * (head_dim + 1) * 4 bytes <= 8 MiB with at least two
+ *    chunks, head_dim a multiple of 16 bytes and a query-head group of 1, 2, 4 or 8; anything
+ *    else is refused with FLAT_ERR_UNSUPPORTED_SHAPE and a message giving both sizes.
+ *    kv_splits = 0 picks a split that fits.
+ *  - the first call on a device looks the array's device address up once
+ *    (cudaGetSymbolAddress); make that first call before any stream capture.
+ *  - all calls on a device share the array and it keeps the previous call's partials; nothing
+ *    in it needs clearing (every live chunk is written before it is read), but two calls that
+ *    overlap on the GPU (different streams) race on it.
+ *  - page-sharing between sequences is not checked here (that check needs host memory). */
+int32_t flat_decode_paged_batched_static_scratch(
+    flat_ctx *ctx, int32_t dtype, uint64_t num_seqs, uint64_t q_heads, uint64_t kv_heads,
+    uint64_t head_dim, uint64_t page_size, uint64_t physical_pages, uint64_t max_pages_per_seq,
+    const int32_t *page_tables_dev, const int32_t *context_lens_dev,
+    const int32_t *q_rope_positions_dev, const int32_t *host_context_lens,
+    const int32_t *host_q_rope_positions, const flat_attention_config *config, float theta,
+    uint32_t kv_splits, flat_buffer q, flat_buffer k, flat_buffer v, flat_buffer out_and_lse);
+
 /* Split-KV merge over `parts` partial results laid out [parts, rows, head_dim] (O, f32,
  * each normalised within its part) and [parts, rows] (LSE, f32):
  * LSE = log(sum_i exp(LSE_i)), O = sum_i exp(LSE_i - LSE) O_i.  This is the consumer of the
