@@ -332,13 +332,48 @@ int validate_decode_geometry(flat_ctx *ctx, uint64_t q_heads, uint64_t kv_heads,
     return FLAT_OK;
 }
 
-// Chooses the split along KV for the streaming decode kernel so that the grid fills the machine
-// about four times over; returns the scratch bytes the launch needs (behind the metadata region).
-uint64_t plan_decode(flat_ctx *ctx, int dtype, DecodeParams &p, uint64_t total_tokens_hint, int max_len_hint,
-                     uint32_t kv_splits) {
+// Chooses the split along KV for the streaming decode kernels and returns the scratch bytes the
+// launch needs (behind the metadata region).  With kv_splits == 0 and the tensor-core decode
+// available the work is balanced: sequences padded to 16 tokens are laid end to end and cut into
+// equal spans, one per resident CTA (two per SM); `offsets` receives the start of every sequence
+// on that line (num_seqs + 1 entries) and has to be copied to the metadata region by the caller.
+// Otherwise every sequence is cut into kv_splits chunks of equal token count.
+constexpr uint64_t kSeqOffsetsAt = 48 << 10;  // byte offset of the sequence offsets inside the metadata region
+
+uint64_t plan_decode(flat_ctx *ctx, int dtype, DecodeParams &p, const int32_t *host_lens, uint64_t total_tokens_hint,
+                     int max_len_hint, uint32_t kv_splits, std::vector<int32_t> *offsets) {
     p.kv_splits = 1;
     p.chunk_tokens = 0;
+    p.balanced = 0;
     if (!decode_fast_path_ok(dtype, p.head_dim, p.group)) return 0;
+    if (kv_splits == 0 && offsets && decode_mma_supported(dtype, p) &&
+        (uint64_t)(p.num_seqs + 1) * sizeof(int32_t) <= kWorkspaceMeta - kSeqOffsetsAt) {
+        offsets->resize(p.num_seqs + 1);
+        int64_t at = 0;
+        int max16 = 0;
+        for (int s = 0; s < p.num_seqs; ++s) {
+            (*offsets)[s] = (int32_t)at;
+            const int len = host_lens ? host_lens[s] : p.uniform_len;
+            const int len16 = (len + 15) / 16 * 16;
+            at += len16;
+            if (len16 > max16) max16 = len16;
+        }
+        if (at < 0x7fffffff) {
+            (*offsets)[p.num_seqs] = (int32_t)at;
+            const int64_t head_blocks = (p.kv_heads + 7) / 8;
+            int64_t ctas = (int64_t)ctx->sm_count * 2 / head_blocks;
+            if (ctas < 1) ctas = 1;
+            int64_t span = (at + ctas - 1) / ctas;
+            span = (span + 15) / 16 * 16;
+            if (span < 64) span = 64;
+            ctas = (at + span - 1) / span;
+            p.balanced = 1;
+            p.span_tokens = (int)span;
+            p.num_ctas = (int)ctas;
+            p.kv_splits = (int)((max16 + span - 1) / span + 1);  // slots per sequence
+            return decode_workspace_bytes(p);
+        }
+    }
     int splits = 1, chunk = 0;
     if (kv_splits > 1) {
         splits = (int)kv_splits;
@@ -362,6 +397,16 @@ uint64_t plan_decode(flat_ctx *ctx, int dtype, DecodeParams &p, uint64_t total_t
         p.chunk_tokens = chunk;
     }
     return decode_workspace_bytes(p);
+}
+
+// Copies the sequence offsets of a balanced plan into the metadata region (after ensure_workspace).
+int upload_decode_plan(flat_ctx *ctx, DecodeParams &p, const std::vector<int32_t> &offsets) {
+    if (!p.balanced) return FLAT_OK;
+    char *dst = static_cast<char *>(ctx->workspace) + kSeqOffsetsAt;
+    FLAT_CUDA_OK(ctx, cudaMemcpyAsync(dst, offsets.data(), offsets.size() * sizeof(int32_t), cudaMemcpyHostToDevice,
+                                      ctx->stream));
+    p.seq_offsets = reinterpret_cast<const int32_t *>(dst);
+    return FLAT_OK;
 }
 
 // Runs the streaming decode kernel, or the generic forward kernel (q_len = 1) for head
@@ -927,8 +972,10 @@ int32_t flat_decode_resident(flat_ctx *ctx, int32_t dtype, uint64_t batch, uint6
     p.scale = scale;
     p.rope_q = 1;
     fill_inv_freq(theta, p.head_dim, p.inv_freq);
-    const uint64_t scratch = plan_decode(ctx, dtype, p, batch * kv_len, (int)kv_len, 0);
+    std::vector<int32_t> offsets;
+    const uint64_t scratch = plan_decode(ctx, dtype, p, nullptr, batch * kv_len, (int)kv_len, 0, &offsets);
     if ((st = ensure_workspace(ctx, kWorkspaceMeta + scratch))) return st;
+    if ((st = upload_decode_plan(ctx, p, offsets))) return st;
     return run_decode(ctx, dtype, p);
 }
 
@@ -975,9 +1022,9 @@ int32_t flat_decode_paged(flat_ctx *ctx, int32_t dtype, const flat_paged_kv_tabl
     if ((st = check_buffer(ctx, "K", k, kv_bytes))) return st;
     if ((st = check_buffer(ctx, "V", v, kv_bytes))) return st;
     if ((st = check_buffer(ctx, "O|LSE", out_and_lse, lse_off + q_heads * 4))) return st;
-    if (mapped * sizeof(int32_t) > kWorkspaceMeta)
+    if (mapped * sizeof(int32_t) > kSeqOffsetsAt)
         return fail(ctx, FLAT_ERR_DISPATCH_LIMIT, "single-sequence paged decode maps %llu pages, maximum is %llu",
-                    (unsigned long long)mapped, (unsigned long long)(kWorkspaceMeta / 4));
+                    (unsigned long long)mapped, (unsigned long long)(kSeqOffsetsAt / 4));
     DecodeParams p{};
     p.q = q.ptr; p.k = k.ptr; p.v = v.ptr; p.o = out_and_lse.ptr;
     p.lse = reinterpret_cast<float *>(static_cast<char *>(out_and_lse.ptr) + lse_off);
@@ -990,11 +1037,13 @@ int32_t flat_decode_paged(flat_ctx *ctx, int32_t dtype, const flat_paged_kv_tabl
     p.scale = scale;
     p.rope_q = 1;
     fill_inv_freq(theta, p.head_dim, p.inv_freq);
-    const uint64_t scratch = plan_decode(ctx, dtype, p, table->live_tokens, (int)table->live_tokens, 0);
+    std::vector<int32_t> offsets;
+    const uint64_t scratch = plan_decode(ctx, dtype, p, nullptr, table->live_tokens, (int)table->live_tokens, 0, &offsets);
     if ((st = ensure_workspace(ctx, kWorkspaceMeta + scratch))) return st;
     FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ctx->workspace, entries.data(), mapped * sizeof(int32_t), cudaMemcpyHostToDevice,
                                       ctx->stream));
     p.page_table = static_cast<const int32_t *>(ctx->workspace);
+    if ((st = upload_decode_plan(ctx, p, offsets))) return st;
     return run_decode(ctx, dtype, p);
 }
 
@@ -1078,8 +1127,10 @@ int32_t flat_decode_paged_batched(flat_ctx *ctx, int32_t dtype, uint64_t num_seq
     p.scale = scale;
     p.rope_q = 1;
     fill_inv_freq(theta, p.head_dim, p.inv_freq);
-    const uint64_t scratch = plan_decode(ctx, dtype, p, total, max_len, kv_splits);
+    std::vector<int32_t> offsets;
+    const uint64_t scratch = plan_decode(ctx, dtype, p, host_context_lens, total, max_len, kv_splits, &offsets);
     if ((st = ensure_workspace(ctx, kWorkspaceMeta + scratch))) return st;
+    if ((st = upload_decode_plan(ctx, p, offsets))) return st;
     return run_decode(ctx, dtype, p);
 }
 

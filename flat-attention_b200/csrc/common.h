@@ -141,10 +141,22 @@ struct DecodeParams {
     float *partial_o;                    // [splits, num_seqs*q_heads, head_dim] f32 (splits > 1)
     float *partial_lse;                  // [splits, num_seqs*q_heads]
     int chunk_tokens;                    // tokens per split chunk (splits > 1)
+    // Balanced mode (tensor-core decode only): sequences, each padded to a multiple of 16 tokens,
+    // are laid end to end and CTA i streams tokens [i*span, (i+1)*span) of that line, whatever
+    // sequences they belong to.  seq_offsets[s] is where sequence s starts (device, num_seqs+1
+    // entries).  Partial slot of (sequence, CTA) = CTA index - first CTA touching the sequence;
+    // kv_splits then holds the maximum number of slots per sequence.
+    int balanced;
+    int span_tokens;
+    int num_ctas;
+    const int32_t *seq_offsets;
 };
 uint64_t decode_workspace_bytes(const DecodeParams &p);
 bool decode_fast_path_ok(int dtype, int head_dim, int group);
 int launch_decode(flat_ctx *ctx, int dtype, const DecodeParams &p);
+// bf16 tensor-core decode (mma.sync), head_dim 64/128, group <= 8, pages of a multiple of 16 tokens
+bool decode_mma_supported(int dtype, const DecodeParams &p);
+int launch_decode_mma(flat_ctx *ctx, const DecodeParams &p);
 int launch_splitkv_merge(flat_ctx *ctx, int dtype, int parts, int64_t rows, int head_dim,
                          const float *partial_o, const float *partial_lse, void *o, float *lse);
 

@@ -243,12 +243,18 @@ __global__ void __launch_bounds__(128) merge_kernel(int parts, int64_t rows, int
                                                     const float *__restrict__ partial_o,
                                                     const float *__restrict__ partial_lse, T *__restrict__ o,
                                                     float *__restrict__ lse, const int32_t *context_lens,
-                                                    int uniform_len, int chunk_tokens, int rows_per_seq) {
+                                                    int uniform_len, int chunk_tokens, int rows_per_seq,
+                                                    const int32_t *seq_offsets, int span_tokens) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
     int live = parts;
-    if (chunk_tokens > 0) {
+    if (seq_offsets) {
+        // balanced mode: one slot per CTA that touched the sequence; a single slot was written as the final result
+        const int seq = (int)(row / rows_per_seq);
+        live = (seq_offsets[seq + 1] - 1) / span_tokens - seq_offsets[seq] / span_tokens + 1;
+        if (live <= 1) return;
+    } else if (chunk_tokens > 0) {
         int len = context_lens ? context_lens[row / rows_per_seq] : uniform_len;
         live = min(parts, (len + chunk_tokens - 1) / chunk_tokens);
     }
@@ -273,6 +279,19 @@ __global__ void __launch_bounds__(128) merge_kernel(int parts, int64_t rows, int
     if (lane == 0) lse[row] = total;
 }
 
+template <typename T>
+int merge_chunks(flat_ctx *ctx, const DecodeParams &p) {
+    if (p.kv_splits <= 1) return FLAT_OK;
+    int64_t rows = (int64_t)p.num_seqs * p.q_heads;
+    int blocks = (int)((rows + 3) / 4);
+    merge_kernel<T><<<blocks, 128, 0, ctx->stream>>>(p.kv_splits, rows, p.head_dim, p.partial_o, p.partial_lse, (T *)p.o,
+                                                      p.lse, p.context_lens, p.uniform_len, p.chunk_tokens, p.q_heads,
+                                                      p.balanced ? p.seq_offsets : nullptr, p.span_tokens);
+    ctx->launches += 1;
+    FLAT_CUDA_OK(ctx, cudaGetLastError());
+    return FLAT_OK;
+}
+
 template <typename T, int LPR, int G>
 int launch_lg(flat_ctx *ctx, const DecodeParams &p) {
     int warps = p.kv_heads < 8 ? p.kv_heads : 8;
@@ -283,16 +302,7 @@ int launch_lg(flat_ctx *ctx, const DecodeParams &p) {
     }
     ctx->launches += 1;
     FLAT_CUDA_OK(ctx, cudaGetLastError());
-    if (p.kv_splits > 1) {
-        int64_t rows = (int64_t)p.num_seqs * p.q_heads;
-        int blocks = (int)((rows + 3) / 4);
-        merge_kernel<T><<<blocks, 128, 0, ctx->stream>>>(p.kv_splits, rows, p.head_dim, p.partial_o, p.partial_lse,
-                                                          (T *)p.o, p.lse, p.context_lens, p.uniform_len,
-                                                          p.chunk_tokens, p.q_heads);
-        ctx->launches += 1;
-        FLAT_CUDA_OK(ctx, cudaGetLastError());
-    }
-    return FLAT_OK;
+    return merge_chunks<T>(ctx, p);
 }
 
 template <typename T, int LPR>
@@ -334,6 +344,12 @@ bool decode_fast_path_ok(int dtype, int head_dim, int group) {
 
 int launch_decode(flat_ctx *ctx, int dtype, const DecodeParams &p) {
     if (p.num_seqs > 65535) return fail(ctx, FLAT_ERR_DISPATCH_LIMIT, "decode batch %d exceeds 65535", p.num_seqs);
+    if (decode_mma_supported(dtype, p)) {
+        launch_decode_mma(ctx, p);
+        ctx->launches += 1;
+        FLAT_CUDA_OK(ctx, cudaGetLastError());
+        return merge_chunks<__nv_bfloat16>(ctx, p);
+    }
     int st = dtype == FLAT_BF16 ? launch_t<__nv_bfloat16>(ctx, p) : launch_t<float>(ctx, p);
     return st;
 }
@@ -343,10 +359,10 @@ int launch_splitkv_merge(flat_ctx *ctx, int dtype, int parts, int64_t rows, int 
     int blocks = (int)((rows + 3) / 4);
     if (dtype == FLAT_BF16)
         merge_kernel<__nv_bfloat16><<<blocks, 128, 0, ctx->stream>>>(parts, rows, head_dim, partial_o, partial_lse,
-                                                                      (__nv_bfloat16 *)o, lse, nullptr, 0, 0, 1);
+                                                                      (__nv_bfloat16 *)o, lse, nullptr, 0, 0, 1, nullptr, 0);
     else
         merge_kernel<float><<<blocks, 128, 0, ctx->stream>>>(parts, rows, head_dim, partial_o, partial_lse, (float *)o,
-                                                             lse, nullptr, 0, 0, 1);
+                                                             lse, nullptr, 0, 0, 1, nullptr, 0);
     ctx->launches += 1;
     FLAT_CUDA_OK(ctx, cudaGetLastError());
     return FLAT_OK;
