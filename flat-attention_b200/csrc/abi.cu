@@ -761,6 +761,10 @@ int32_t flat_paged_kv_cache_create(flat_ctx *ctx, int32_t dtype, uint64_t page_s
     cudaError_t e = cudaMalloc(&c->k, bytes);
     if (e == cudaSuccess) e = cudaMalloc(&c->v, bytes);
     if (e == cudaSuccess) e = cudaMalloc(reinterpret_cast<void **>(&c->dev_table), physical_pages * sizeof(int32_t));
+    // Rows of a mapped page that were never appended reach the tensor core with probability 0;
+    // they must hold finite values (0 * NaN is NaN), so the storage starts zeroed.
+    if (e == cudaSuccess) e = cudaMemsetAsync(c->k, 0, bytes, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(c->v, 0, bytes, ctx->stream);
     if (e != cudaSuccess) {
         cudaGetLastError();
         flat_paged_kv_cache_destroy(c);
@@ -870,6 +874,8 @@ int32_t flat_resident_kv_cache_create(flat_ctx *ctx, int32_t dtype, uint64_t bat
     c->head_dim = head_dim; c->tensor_bytes = bytes;
     cudaError_t e = cudaMalloc(&c->k, bytes);
     if (e == cudaSuccess) e = cudaMalloc(&c->v, bytes);
+    if (e == cudaSuccess) e = cudaMemsetAsync(c->k, 0, bytes, ctx->stream);
+    if (e == cudaSuccess) e = cudaMemsetAsync(c->v, 0, bytes, ctx->stream);
     if (e != cudaSuccess) {
         cudaGetLastError();
         flat_resident_kv_cache_destroy(c);

@@ -13,12 +13,15 @@
 // The N x N matrix never leaves TMEM.  Tensor-core order S0 S1 | PV0 S0' PV1 S1' | ... keeps the
 // pipe busy with one tile's MMAs while the other tile is in softmax.
 //
-// RoPE: the rotation is applied by a prologue kernel that writes rotated Q and K as fp16 into
-// context scratch; fp16 keeps the rounding of the rotated operands eight times smaller than bf16
-// would, which the 2e-3 LSE tolerance needs.  When the cache already holds rotated bf16 K
-// (rotate_k = 0) only Q is rotated; tcgen05.mma kind::f16 takes A and B of one format only, so
-// rotated Q is then written as two bf16 tensors hi + lo (lo = bf16(q - hi)) and S = Q_hi K^T +
-// Q_lo K^T costs one extra QK MMA pass.
+// RoPE: Q is rotated inside this kernel.  The raw bf16 Q tile lands in shared memory by TMA, the
+// softmax thread that owns a row rotates it in place with a (cos, sin) table of the call's
+// positions and hands the tile to the MMA warp; rotated operands are stored as fp16, which keeps
+// their rounding eight times smaller than bf16 would (the 2e-3 LSE tolerance needs that).  K is
+// rotated once per call by a small prologue kernel into fp16 scratch (every K tile is read by
+// many CTAs, so rotating it in-kernel would repeat the work 32 times).  When the cache already
+// holds rotated bf16 K (rotate_k = 0) only Q is rotated; tcgen05.mma kind::f16 takes A and B of
+// one format only, so rotated Q is then written as two bf16 tiles hi + lo (lo = bf16(q - hi)) and
+// S = Q_hi K^T + Q_lo K^T costs one extra QK MMA pass.
 // Semantics: Appendix of the forward contract (src/projection_asymmetric.rs:97-238): key k is
 // visible to local row q iff !causal || k <= query_position_offset + q; LSE = max + ln(sum).
 #include <cuda.h>
@@ -45,7 +48,7 @@ constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 
 struct KernelParams {
-    CUtensorMap map_q, map_q_lo, map_k, map_v;
+    CUtensorMap map_q, map_k, map_v;
     void *o;
     float *lse;
     int64_t o_bs, o_hs, o_rs, lse_hs;
@@ -58,7 +61,7 @@ struct KernelParams {
     int page_size, max_pages, physical_pages;
     int q_blocks;
     DeviceStatus *status;
-    float *debug_s;
+    const float2 *rope_q_table;  // (cos, sin) of row r, pair j at [r * D/2 + j]; null = Q is used as loaded
 };
 
 // SPLIT: Q arrives as bf16 hi + lo parts (two smem tiles per Q tile).
@@ -68,7 +71,7 @@ template <int D, bool SPLIT> struct Cfg {
     static constexpr int kTileBytes = kBoxes * kBoxBytes;  // one Q / K / V tile
     static constexpr int kQParts = SPLIT ? 2 : 1;
     static constexpr int kStages = D == 128 ? (SPLIT ? 3 : 4) : 8;  // K/V ring entries
-    static constexpr int kBars = 2 + 2 * kStages + 6;
+    static constexpr int kBars = 2 + 2 * kStages + 8;
     static constexpr int kSmemBytes = (2 * kQParts + kStages) * kTileBytes + kBars * 8 + 16 + 1024;
 };
 
@@ -97,6 +100,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     auto s_full = [&](int w) { return bar0 + 8u * (2 + 2 * C::kStages + w); };
     auto p_full = [&](int w) { return bar0 + 8u * (4 + 2 * C::kStages + w); };
     auto o_final = [&](int w) { return bar0 + 8u * (6 + 2 * C::kStages + w); };
+    auto q_ready = [&](int w) { return bar0 + 8u * (8 + 2 * C::kStages + w); };
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -133,6 +137,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             mbar_init(s_full(w), 1);
             mbar_init(p_full(w), 4);
             mbar_init(o_final(w), 1);
+            mbar_init(q_ready(w), 4);
         }
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(kv_full(s), 1);
@@ -156,16 +161,14 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
         // ================= TMA producer =================
         if (lane == 0) {
             tma_prefetch_desc(&p.map_q);
-            if (SPLIT) tma_prefetch_desc(&p.map_q_lo);
             tma_prefetch_desc(&p.map_k);
             tma_prefetch_desc(&p.map_v);
             for (int w = 0; w < 2; ++w) {
                 if (!active[w]) continue;
-                mbar_expect_tx(q_full(w), C::kQParts * C::kTileBytes);
-                for (int part = 0; part < C::kQParts; ++part)
-                    for (int kb = 0; kb < C::kBoxes; ++kb)
-                        tma_load_4d(smem_u32(q_s + (w * C::kQParts + part) * C::kTileBytes + kb * C::kBoxBytes),
-                                    part ? &p.map_q_lo : &p.map_q, kb * 64, r0 + w * kTileRows, h, b, q_full(w));
+                mbar_expect_tx(q_full(w), C::kTileBytes);
+                for (int kb = 0; kb < C::kBoxes; ++kb)
+                    tma_load_4d(smem_u32(q_s + w * C::kQParts * C::kTileBytes + kb * C::kBoxBytes), &p.map_q, kb * 64,
+                                r0 + w * kTileRows, h, b, q_full(w));
             }
             bool ok = true;
             for (int i = 0; ok && i < 2 * n_max; ++i) {
@@ -231,7 +234,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             auto phase_of = [&](int i) { return (uint32_t)((i / C::kStages) & 1); };
 
             for (int w = 0; w < 2; ++w)
-                if (active[w]) wait(q_full(w), 0, 200 + w);
+                if (active[w]) wait(p.rope_q_table ? q_ready(w) : q_full(w), 0, 200 + w);
             // prologue: S_w(0)
             wait(kv_full(stage_of(0)), phase_of(0), 210);
             if (ok) {
@@ -281,12 +284,67 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16);
             const uint32_t t_s = t_lane + col_s[w];
             const uint32_t t_o = t_lane + col_o[w];
+            bool ok = true;
+
+            if (p.rope_q_table) {
+                // rotate this thread's Q row in place (fp16), or into bf16 hi / lo tiles
+                if (!mbar_wait(q_full(w), 0, abort_flag)) {
+                    record_timeout(p, 290 + w);
+                    ok = false;
+                }
+                if (ok && row < p.q_len) {
+                    uint8_t *tile = q_s + w * C::kQParts * C::kTileBytes;
+                    const float4 *tab = reinterpret_cast<const float4 *>(p.rope_q_table + (long long)row * (D / 2));
+#pragma unroll 4
+                    for (int ch = 0; ch < D / 8; ++ch) {  // 16-byte chunks of the row: 8 elements, 4 pairs
+                        const int off = (ch >> 3) * C::kBoxBytes + row_in_tile * 128 + (((ch & 7) ^ (row_in_tile & 7)) << 4);
+                        const uint4 raw = *reinterpret_cast<const uint4 *>(tile + off);
+                        const float4 cs0 = __ldg(tab + 2 * ch), cs1 = __ldg(tab + 2 * ch + 1);  // (c, s, c, s) x 2
+                        const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+                        const float cc[4] = {cs0.x, cs0.z, cs1.x, cs1.z}, ss[4] = {cs0.y, cs0.w, cs1.y, cs1.w};
+                        uint32_t hi[4], lo[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float x = __uint_as_float(in[e] << 16), y = __uint_as_float(in[e] & 0xffff0000u);
+                            const float rx = x * cc[e] - y * ss[e], ry = x * ss[e] + y * cc[e];
+                            if (SPLIT) {
+                                const __nv_bfloat162 h2 = __floats2bfloat162_rn(rx, ry);
+                                const float2 hf = __bfloat1622float2(h2);
+                                const __nv_bfloat162 l2 = __floats2bfloat162_rn(rx - hf.x, ry - hf.y);
+                                hi[e] = *reinterpret_cast<const uint32_t *>(&h2);
+                                lo[e] = *reinterpret_cast<const uint32_t *>(&l2);
+                            } else {
+                                const __half2 h2 = __floats2half2_rn(rx, ry);
+                                hi[e] = *reinterpret_cast<const uint32_t *>(&h2);
+                            }
+                        }
+                        *reinterpret_cast<uint4 *>(tile + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                        if (SPLIT) *reinterpret_cast<uint4 *>(tile + C::kTileBytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    }
+                } else if (ok && SPLIT) {
+                    // rows past q_len were zero-filled by TMA in the hi tile; the lo tile has to be zero too
+                    uint8_t *tile = q_s + (w * C::kQParts + 1) * C::kTileBytes;
+                    for (int ch = 0; ch < D / 8; ++ch)
+                        *reinterpret_cast<uint4 *>(tile + (ch >> 3) * C::kBoxBytes + row_in_tile * 128 + ((ch & 7) << 4)) =
+                            make_uint4(0, 0, 0, 0);
+                }
+                fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(q_ready(w));
+            }
+
             long long lim = (long long)p.kv_len - 1;  // last visible key of this row
             if (p.causal) lim = min(lim, p.causal_off + row);
+            // first row of this Q tile: tiles whose last key is visible to it need no mask for any row
+            long long lim_first = (long long)p.kv_len - 1;
+            if (p.causal) lim_first = min(lim_first, p.causal_off + (long long)(r0 + w * kTileRows));
             float m = -INFINITY, l = 0.f;
-            bool ok = true;
             const int n = n_tiles[w];
-            for (int j = 0; j < n; ++j) {
+            const float c_log2 = p.scale_log2;
+            uint64_t c2;
+            asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(c_log2));
+
+            for (int j = 0; ok && j < n; ++j) {
                 if (!mbar_wait(s_full(w), j & 1, abort_flag)) {
                     record_timeout(p, 300 + w);
                     ok = false;
@@ -294,27 +352,31 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                 }
                 tc_fence_after();
                 const int key0 = j * kTileRows;
-                const bool need_mask = (long long)key0 + kTileRows - 1 > lim;
-                const int vis = (int)min((long long)kTileRows, lim - key0 + 1);  // visible columns (may be <= 0)
+                const bool tile_masked = (long long)key0 + kTileRows - 1 > lim_first;  // uniform over the Q tile
+                const int vis = (int)min((long long)kTileRows, lim - key0 + 1);        // visible columns of this row
                 uint32_t r[32];
                 // pass 1: row maximum of the raw scores
                 float mx = -INFINITY;
+                if (tile_masked) {
 #pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    tmem_ld32(t_s + c * 32, r);
-                    tc_wait_ld();
-                    if (D == 128 && p.debug_s && lin == 0 && w == 0 && j == 0) {
+                    for (int c = 0; c < 4; ++c) {
+                        tmem_ld32(t_s + c * 32, r);
+                        tc_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) p.debug_s[row_in_tile * 128 + c * 32 + i] = __uint_as_float(r[i]);
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i < vis) mx = fmaxf(mx, __uint_as_float(r[i]));
                     }
+                } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        float v = __uint_as_float(r[i]);
-                        if (need_mask && c * 32 + i >= vis) v = -INFINITY;
-                        mx = fmaxf(mx, v);
+                    for (int c = 0; c < 4; ++c) {
+                        tmem_ld32(t_s + c * 32, r);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2)
+                            asm("max.f32 %0, %0, %1, %2;" : "+f"(mx) : "f"(__uint_as_float(r[i])), "f"(__uint_as_float(r[i + 1])));
                     }
                 }
-                const float m_cand = fmaxf(m, mx * p.scale_log2);
+                const float m_cand = fmaxf(m, mx * c_log2);
                 const bool grow = (m_cand - m) > kRescaleThreshold;
                 float alpha = 1.0f;
                 if (grow) {
@@ -332,8 +394,12 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     }
                 }
                 l *= alpha;
-                // pass 2: P = exp2(S*c - m) as bf16, written over S
-                const float neg_m = -m;
+                // pass 2: P = exp2(S*c - m) as bf16, written over S; two scores per packed f32x2 FMA
+                uint64_t nm2, sum2 = 0;
+                {
+                    const float neg_m = -m;
+                    asm("mov.b64 %0, {%1, %1};" : "=l"(nm2) : "f"(neg_m));
+                }
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
                     tmem_ld32(t_s + c * 32, r);
@@ -341,17 +407,28 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        float p0 = ex2(fmaf(__uint_as_float(r[i]), p.scale_log2, neg_m));
-                        float p1 = ex2(fmaf(__uint_as_float(r[i + 1]), p.scale_log2, neg_m));
-                        if (need_mask) {
+                        uint64_t s2, t2;
+                        asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(r[i]), "r"(r[i + 1]));
+                        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(t2) : "l"(s2), "l"(c2), "l"(nm2));
+                        float t0, t1;
+                        asm("mov.b64 {%0, %1}, %2;" : "=f"(t0), "=f"(t1) : "l"(t2));
+                        float p0 = ex2(t0), p1 = ex2(t1);
+                        if (tile_masked) {
                             if (c * 32 + i >= vis) p0 = 0.f;
                             if (c * 32 + i + 1 >= vis) p1 = 0.f;
                         }
-                        l += p0 + p1;
+                        uint64_t p2;
+                        asm("mov.b64 %0, {%1, %2};" : "=l"(p2) : "f"(p0), "f"(p1));
+                        asm("add.rn.f32x2 %0, %0, %1;" : "+l"(sum2) : "l"(p2));
                         __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
                         pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                     }
                     tmem_st16(t_s + c * 16, pk);
+                }
+                {
+                    float s0, s1;
+                    asm("mov.b64 {%0, %1}, %2;" : "=f"(s0), "=f"(s1) : "l"(sum2));
+                    l += s0 + s1;
                 }
                 tc_wait_st();
                 tc_fence_before();
@@ -405,17 +482,31 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     }
 }
 
-// Rotation prologue: x (bf16, strided) -> y (fp16, compact [B, H, N, D]) rotated at pos_off + row
-// with interleaved pairs (src/rotary_grouped.rs:36-50).  One thread moves 8 elements (16 bytes).
+// (cos, sin) of every (row, pair) of a call: angle = f32(pos_off + row) * inv_freq[pair], the same
+// f32 product the oracle forms (src/rotary_grouped.rs:44-48); sincosf is within 2 ulp of libm.
 struct InvFreq {
     float f[kMaxHeadDim / 2];
 };
 
-// y_lo == nullptr: y receives fp16.  Otherwise y / y_lo receive the bf16 hi / lo parts.
-__global__ void __launch_bounds__(256) rotate_to_f16_kernel(const __nv_bfloat16 *__restrict__ x, void *__restrict__ y,
-                                                            void *__restrict__ y_lo, int heads, int rows, int head_dim,
-                                                            int64_t bs, int64_t hs, int64_t rs, int64_t total_vec,
-                                                            int64_t pos_off, InvFreq inv_freq) {
+__global__ void __launch_bounds__(256) rope_table_kernel(float2 *__restrict__ table, int rows, int half_dim,
+                                                         int64_t pos_off, InvFreq inv_freq) {
+    const int64_t total = (int64_t)rows * half_dim;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int pair = (int)(i % half_dim);
+        const int64_t row = i / half_dim;
+        const float angle = __fmul_rn((float)(pos_off + row), inv_freq.f[pair]);
+        float s, c;
+        sincosf(angle, &s, &c);
+        table[i] = make_float2(c, s);
+    }
+}
+
+// K rotation prologue: x (bf16, strided) -> y (fp16, compact [B, H, N, D]) with interleaved pairs
+// (src/rotary_grouped.rs:36-50).  One thread moves 8 elements (16 bytes).
+__global__ void __launch_bounds__(256) rotate_to_f16_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ y,
+                                                            const float2 *__restrict__ table, int heads, int rows,
+                                                            int head_dim, int64_t bs, int64_t hs, int64_t rs,
+                                                            int64_t total_vec) {
     const int vec_per_row = head_dim / 8;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total_vec; i += (int64_t)gridDim.x * blockDim.x) {
         const int v = (int)(i % vec_per_row);
@@ -425,31 +516,18 @@ __global__ void __launch_bounds__(256) rotate_to_f16_kernel(const __nv_bfloat16 
         const int hh = (int)(bh % heads);
         const int64_t bb = bh / heads;
         const uint4 raw = *reinterpret_cast<const uint4 *>(x + bb * bs + hh * hs + (int64_t)n * rs + v * 8);
-        const __nv_bfloat162 *in = reinterpret_cast<const __nv_bfloat162 *>(&raw);
-        uint32_t out[4], out_lo[4];
-        const float pos = (float)(pos_off + n);
+        const float4 *tab = reinterpret_cast<const float4 *>(table + (int64_t)n * (head_dim / 2) + v * 4);
+        const float4 cs0 = __ldg(tab), cs1 = __ldg(tab + 1);
+        const float cc[4] = {cs0.x, cs0.z, cs1.x, cs1.z}, ss[4] = {cs0.y, cs0.w, cs1.y, cs1.w};
+        const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint32_t out[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const float2 f = __bfloat1622float2(in[e]);
-            const float angle = __fmul_rn(pos, inv_freq.f[v * 4 + e]);
-            float s, c;
-            sincosf(angle, &s, &c);
-            const float re = f.x * c - f.y * s, ro = f.x * s + f.y * c;
-            if (y_lo) {
-                const __nv_bfloat162 hi = __floats2bfloat162_rn(re, ro);
-                const float2 hf = __bfloat1622float2(hi);
-                const __nv_bfloat162 lo = __floats2bfloat162_rn(re - hf.x, ro - hf.y);
-                out[e] = *reinterpret_cast<const uint32_t *>(&hi);
-                out_lo[e] = *reinterpret_cast<const uint32_t *>(&lo);
-            } else {
-                const __half2 hh2 = __floats2half2_rn(re, ro);
-                out[e] = *reinterpret_cast<const uint32_t *>(&hh2);
-            }
+            const float fx = __uint_as_float(in[e] << 16), fy = __uint_as_float(in[e] & 0xffff0000u);
+            const __half2 h2 = __floats2half2_rn(fx * cc[e] - fy * ss[e], fx * ss[e] + fy * cc[e]);
+            out[e] = *reinterpret_cast<const uint32_t *>(&h2);
         }
-        const int64_t off = (rowi * head_dim + v * 8) * 2;
-        *reinterpret_cast<uint4 *>(static_cast<char *>(y) + off) = make_uint4(out[0], out[1], out[2], out[3]);
-        if (y_lo)
-            *reinterpret_cast<uint4 *>(static_cast<char *>(y_lo) + off) = make_uint4(out_lo[0], out_lo[1], out_lo[2], out_lo[3]);
+        *reinterpret_cast<uint4 *>(y + rowi * head_dim + v * 8) = make_uint4(out[0], out[1], out[2], out[3]);
     }
 }
 
@@ -509,50 +587,49 @@ bool forward_sm100_supported(const FwdParams &p) {
     return true;
 }
 
+// scratch: [rotated fp16 K (rope_k)] [Q (cos, sin) table (rope_q)] [K (cos, sin) table (rope_k)]
 uint64_t forward_sm100_workspace_bytes(const FwdParams &p) {
     uint64_t bytes = 0;
-    if (p.rope_q) bytes += (uint64_t)p.batch * p.q_heads * p.q_len * p.head_dim * 2 * (p.rope_k ? 1 : 2);
-    bytes = (bytes + 255) & ~uint64_t(255);
-    if (p.rope_k) bytes += (uint64_t)p.batch * p.kv_heads * p.kv_len * p.head_dim * 2;
+    if (p.rope_k) bytes += ((uint64_t)p.batch * p.kv_heads * p.kv_len * p.head_dim * 2 + 255) & ~uint64_t(255);
+    if (p.rope_q) bytes += ((uint64_t)p.q_len * (p.head_dim / 2) * sizeof(float2) + 255) & ~uint64_t(255);
+    if (p.rope_k) bytes += ((uint64_t)p.kv_len * (p.head_dim / 2) * sizeof(float2) + 255) & ~uint64_t(255);
     return bytes;
 }
 
 int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
-    int st = ensure_workspace(ctx, kWorkspaceMeta + forward_sm100_workspace_bytes(p) + 128 * 128 * 4);
+    int st = ensure_workspace(ctx, kWorkspaceMeta + forward_sm100_workspace_bytes(p));
     if (st) return st;
     const int D = p.head_dim;
-    const void *q_ptr = p.q, *k_ptr = p.k;
-    int64_t q_rs = p.q_rs, q_hs = p.q_hs, q_bs = p.q_bs;
+    const void *k_ptr = p.k;
     int64_t k_rs = p.kv_rs, k_hs = p.kv_hs, k_bs = p.kv_bs;
-    bool q_f16 = false, k_f16 = false;
+    bool k_f16 = false;
+    const bool split = p.rope_q && !p.rope_k;  // Q rotated against a cache of already rotated bf16 K
+    const bool q_f16 = p.rope_q && !split;
     char *scratch = scratch_ptr(ctx);
-    const bool split = p.rope_q && !p.rope_k;
-    const void *q_lo_ptr = nullptr;
+    const float2 *q_table = nullptr;
     if (p.rope_q) {
         InvFreq f;
         std::memcpy(f.f, p.inv_freq, sizeof f.f);
-        const uint64_t q_bytes = (uint64_t)p.batch * p.q_heads * p.q_len * D * 2;
-        void *rq = scratch;
-        void *rq_lo = split ? scratch + q_bytes : nullptr;
-        const int64_t vecs = (int64_t)p.batch * p.q_heads * p.q_len * (D / 8);
-        int blocks = (int)std::min<int64_t>((vecs + 255) / 256, (int64_t)ctx->sm_count * 16);
-        rotate_to_f16_kernel<<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const __nv_bfloat16 *>(p.q), rq, rq_lo,
-                                                              p.q_heads, p.q_len, D, p.q_bs, p.q_hs, p.q_rs, vecs,
-                                                              p.q_rope_off, f);
+        uint64_t off = 0;
+        __half *rk = reinterpret_cast<__half *>(scratch);
+        if (p.rope_k) off += ((uint64_t)p.batch * p.kv_heads * p.kv_len * D * 2 + 255) & ~uint64_t(255);
+        float2 *qt = reinterpret_cast<float2 *>(scratch + off);
+        off += ((uint64_t)p.q_len * (D / 2) * sizeof(float2) + 255) & ~uint64_t(255);
+        float2 *kt = reinterpret_cast<float2 *>(scratch + off);
+        const int64_t qn = (int64_t)p.q_len * (D / 2);
+        rope_table_kernel<<<(int)std::min<int64_t>((qn + 255) / 256, 4096), 256, 0, ctx->stream>>>(qt, p.q_len, D / 2,
+                                                                                                  p.q_rope_off, f);
         ctx->launches += 1;
-        q_ptr = rq;
-        q_lo_ptr = rq_lo;
-        q_rs = D; q_hs = (int64_t)p.q_len * D; q_bs = q_hs * p.q_heads;
-        q_f16 = !split;
+        q_table = qt;
         if (p.rope_k) {
-            uint64_t off = (q_bytes + 255) & ~uint64_t(255);
-            void *rk = scratch + off;
+            const int64_t kn = (int64_t)p.kv_len * (D / 2);
+            rope_table_kernel<<<(int)std::min<int64_t>((kn + 255) / 256, 4096), 256, 0, ctx->stream>>>(kt, p.kv_len, D / 2,
+                                                                                                      p.k_rope_off, f);
             const int64_t kvecs = (int64_t)p.batch * p.kv_heads * p.kv_len * (D / 8);
-            blocks = (int)std::min<int64_t>((kvecs + 255) / 256, (int64_t)ctx->sm_count * 16);
-            rotate_to_f16_kernel<<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const __nv_bfloat16 *>(p.k), rk, nullptr,
-                                                                  p.kv_heads, p.kv_len, D, p.kv_bs, p.kv_hs, p.kv_rs, kvecs,
-                                                                  p.k_rope_off, f);
-            ctx->launches += 1;
+            const int blocks = (int)std::min<int64_t>((kvecs + 255) / 256, (int64_t)ctx->sm_count * 16);
+            rotate_to_f16_kernel<<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const __nv_bfloat16 *>(p.k), rk, kt,
+                                                                  p.kv_heads, p.kv_len, D, p.kv_bs, p.kv_hs, p.kv_rs, kvecs);
+            ctx->launches += 2;
             k_ptr = rk;
             k_rs = D; k_hs = (int64_t)p.kv_len * D; k_bs = k_hs * p.kv_heads;
             k_f16 = true;
@@ -560,9 +637,8 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     }
 
     KernelParams kp{};
-    if ((st = make_map(ctx, &kp.map_q, q_f16, q_ptr, D, p.q_len, p.q_heads, p.batch, q_rs, q_hs, q_bs, kTileRows))) return st;
-    if (split && (st = make_map(ctx, &kp.map_q_lo, false, q_lo_ptr, D, p.q_len, p.q_heads, p.batch, q_rs, q_hs, q_bs, kTileRows)))
-        return st;
+    // Q always arrives as the caller's bf16 tensor; rotation (if any) happens in shared memory
+    if ((st = make_map(ctx, &kp.map_q, false, p.q, D, p.q_len, p.q_heads, p.batch, p.q_rs, p.q_hs, p.q_bs, kTileRows))) return st;
     if (p.page_table) {
         // physical layout [pages, page_size, kv_heads*D]: dims (d, token in page, head, page)
         const int64_t row = p.page_row_stride;
@@ -590,10 +666,7 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     kp.physical_pages = p.max_pages;
     kp.q_blocks = (p.q_len + 2 * kTileRows - 1) / (2 * kTileRows);
     kp.status = ctx->dev_status;
-    kp.debug_s = nullptr;
-    const char *dbg = getenv("FLAT_SM100_DEBUG_S");
-    if (dbg && dbg[0] == '1')
-        kp.debug_s = reinterpret_cast<float *>(scratch + ((forward_sm100_workspace_bytes(p) + 255) & ~uint64_t(255)));
+    kp.rope_q_table = q_table;
 
     const long long grid = (long long)kp.q_blocks * p.batch * p.q_heads;
     if (grid > 2147483647LL) return fail(ctx, FLAT_ERR_DISPATCH_LIMIT, "forward grid of %lld blocks is too large", grid);
