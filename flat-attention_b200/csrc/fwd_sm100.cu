@@ -47,6 +47,17 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 
+// Debug timeline (compiled in with -DFLAT_TRACE): clock64 stamps of CTA 0, written to the buffer whose
+// address is given in the environment variable FLAT_TRACE_PTR.  Layout [role 0..2][iteration 0..63][slot 0..7].
+#ifdef FLAT_TRACE
+#define TRACE(role, it, slot)                                                                          \
+    do {                                                                                               \
+        if (p.trace && blockIdx.x == 0 && (it) < 64) p.trace[((role) * 64 + (it)) * 8 + (slot)] = clock64(); \
+    } while (0)
+#else
+#define TRACE(role, it, slot) do { } while (0)
+#endif
+
 struct KernelParams {
     CUtensorMap map_q, map_k, map_v;
     void *o;
@@ -62,6 +73,7 @@ struct KernelParams {
     int q_blocks;
     DeviceStatus *status;
     const float2 *rope_q_table;  // (cos, sin) of row r, pair j at [r * D/2 + j]; null = Q is used as loaded
+    long long *trace;
 };
 
 // SPLIT: Q arrives as bf16 hi + lo parts (two smem tiles per Q tile).
@@ -157,6 +169,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     const uint32_t col_s[2] = {0u, 128u};
     const uint32_t col_o[2] = {256u, 256u + D};
 
+    // Register rebalancing: a softmax thread holds a whole 128-column score row in registers.
+    if (warp >= 8) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == kProducerWarp) {
         // ================= TMA producer =================
         if (lane == 0) {
@@ -255,8 +270,10 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     if (j >= n_tiles[w]) continue;
                     wait(p_full(w), j & 1, 230 + w);
                     if (!ok) break;
+                    TRACE(2, j, w * 4 + 0);
                     tc_fence_after();
                     issue_pv(w, stage_of(iv), j);
+                    TRACE(2, j, w * 4 + 1);
                     if (w == 1 || j >= n_tiles[1]) tc_commit(kv_empty(stage_of(iv)));  // last reader of V_j
                     if (j + 1 < n_tiles[w]) {
                         if (!k_ready) {
@@ -267,6 +284,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                         }
                         issue_s(w, stage_of(ik));
                         tc_commit(s_full(w));
+                        TRACE(2, j, w * 4 + 2);
                         if (w == 1 || j + 1 >= n_tiles[1]) tc_commit(kv_empty(stage_of(ik)));  // last reader of K_{j+1}
                     } else {
                         tc_commit(o_final(w));
@@ -274,8 +292,10 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                 }
             }
         }
-    } else if (warp < 8) {
+    }
+    } else {
         // ================= softmax + epilogue =================
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int w = warp >> 2;
         if (active[w]) {
             const int lane_base = (warp & 3) * 32;
@@ -344,6 +364,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             uint64_t c2;
             asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(c_log2));
 
+            // Online softmax, log2 domain, one thread per row; the whole 128-column score row sits in
+            // registers.  O in TMEM is rescaled only when the running max grew by more than 2^8.
             for (int j = 0; ok && j < n; ++j) {
                 if (!mbar_wait(s_full(w), j & 1, abort_flag)) {
                     record_timeout(p, 300 + w);
@@ -351,32 +373,27 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     break;
                 }
                 tc_fence_after();
+                if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 0);
                 const int key0 = j * kTileRows;
                 const bool tile_masked = (long long)key0 + kTileRows - 1 > lim_first;  // uniform over the Q tile
                 const int vis = (int)min((long long)kTileRows, lim - key0 + 1);        // visible columns of this row
-                uint32_t r[32];
-                // pass 1: row maximum of the raw scores
-                float mx = -INFINITY;
+                uint32_t r[128];  // four loads in flight, one wait
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, r + c * 32);
+                tc_wait_ld();
+                if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 1);
                 if (tile_masked) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        tmem_ld32(t_s + c * 32, r);
-                        tc_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i)
-                            if (c * 32 + i < vis) mx = fmaxf(mx, __uint_as_float(r[i]));
-                    }
-                } else {
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        tmem_ld32(t_s + c * 32, r);
-                        tc_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2)
-                            asm("max.f32 %0, %0, %1, %2;" : "+f"(mx) : "f"(__uint_as_float(r[i])), "f"(__uint_as_float(r[i + 1])));
-                    }
+                    for (int i = 0; i < 128; ++i)
+                        if (i >= vis) r[i] = 0xff800000u;  // -inf: exp2 gives exactly 0
                 }
-                const float m_cand = fmaxf(m, mx * c_log2);
+                float mx = -INFINITY, mx1 = -INFINITY;  // two chains for instruction-level parallelism
+#pragma unroll
+                for (int i = 0; i < 128; i += 4) {
+                    asm("max.f32 %0, %0, %1, %2;" : "+f"(mx) : "f"(__uint_as_float(r[i])), "f"(__uint_as_float(r[i + 1])));
+                    asm("max.f32 %0, %0, %1, %2;" : "+f"(mx1) : "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3])));
+                }
+                const float m_cand = fmaxf(m, fmaxf(mx, mx1) * c_log2);
                 const bool grow = (m_cand - m) > kRescaleThreshold;
                 float alpha = 1.0f;
                 if (grow) {
@@ -384,56 +401,55 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     m = m_cand;
                 }
                 if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                    uint32_t o[32];
 #pragma unroll
                     for (int c = 0; c < D / 32; ++c) {
-                        tmem_ld32(t_o + c * 32, r);
+                        tmem_ld32(t_o + c * 32, o);
                         tc_wait_ld();
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-                        tmem_st32(t_o + c * 32, r);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st32(t_o + c * 32, o);
                     }
                 }
                 l *= alpha;
-                // pass 2: P = exp2(S*c - m) as bf16, written over S; two scores per packed f32x2 FMA
-                uint64_t nm2, sum2 = 0;
+                if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 2);
+                // P = exp2(S*c - m) as bf16, written over S; two scores per packed f32x2 FMA
+                uint64_t nm2, sum2 = 0, sum3 = 0;
                 {
                     const float neg_m = -m;
                     asm("mov.b64 %0, {%1, %1};" : "=l"(nm2) : "f"(neg_m));
                 }
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    tmem_ld32(t_s + c * 32, r);
-                    tc_wait_ld();
                     uint32_t pk[16];
 #pragma unroll
                     for (int i = 0; i < 32; i += 2) {
-                        uint64_t s2, t2;
-                        asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(r[i]), "r"(r[i + 1]));
+                        uint64_t s2, t2, p2;
+                        asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(r[c * 32 + i]), "r"(r[c * 32 + i + 1]));
                         asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(t2) : "l"(s2), "l"(c2), "l"(nm2));
                         float t0, t1;
                         asm("mov.b64 {%0, %1}, %2;" : "=f"(t0), "=f"(t1) : "l"(t2));
-                        float p0 = ex2(t0), p1 = ex2(t1);
-                        if (tile_masked) {
-                            if (c * 32 + i >= vis) p0 = 0.f;
-                            if (c * 32 + i + 1 >= vis) p1 = 0.f;
-                        }
-                        uint64_t p2;
+                        const float p0 = ex2(t0), p1 = ex2(t1);
                         asm("mov.b64 %0, {%1, %2};" : "=l"(p2) : "f"(p0), "f"(p1));
-                        asm("add.rn.f32x2 %0, %0, %1;" : "+l"(sum2) : "l"(p2));
+                        if (i & 2) asm("add.rn.f32x2 %0, %0, %1;" : "+l"(sum3) : "l"(p2));
+                        else asm("add.rn.f32x2 %0, %0, %1;" : "+l"(sum2) : "l"(p2));
                         __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
                         pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                     }
                     tmem_st16(t_s + c * 16, pk);
                 }
                 {
-                    float s0, s1;
+                    float s0, s1, s2f, s3;
                     asm("mov.b64 {%0, %1}, %2;" : "=f"(s0), "=f"(s1) : "l"(sum2));
-                    l += s0 + s1;
+                    asm("mov.b64 {%0, %1}, %2;" : "=f"(s2f), "=f"(s3) : "l"(sum3));
+                    l += (s0 + s1) + (s2f + s3);
                 }
+                if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 3);
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full(w));
+                if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 4);
             }
             if (ok) {
                 if (!mbar_wait(o_final(w), 0, abort_flag)) {
@@ -667,6 +683,10 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     kp.q_blocks = (p.q_len + 2 * kTileRows - 1) / (2 * kTileRows);
     kp.status = ctx->dev_status;
     kp.rope_q_table = q_table;
+    kp.trace = nullptr;
+#ifdef FLAT_TRACE
+    if (const char *tp = getenv("FLAT_TRACE_PTR")) kp.trace = reinterpret_cast<long long *>(strtoull(tp, nullptr, 0));
+#endif
 
     const long long grid = (long long)kp.q_blocks * p.batch * p.q_heads;
     if (grid > 2147483647LL) return fail(ctx, FLAT_ERR_DISPATCH_LIMIT, "forward grid of %lld blocks is too large", grid);
