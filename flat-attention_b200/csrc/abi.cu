@@ -1289,10 +1289,11 @@ int32_t flat_backward_layout_for(int32_t dtype, const flat_attention_shape *shap
     out->out_offset = off; off = align(off + d.q_elements * es);
     out->lse_offset = off; off += d.lse_elements * 4;
     out->input_bytes = off;
+    // gradients are f32 in both modes (tight packing; every section is a multiple of 4 bytes)
     off = 0;
-    out->dq_offset = off; off = align(off + d.q_elements * es);
-    out->dk_offset = off; off = align(off + d.kv_elements * es);
-    out->dv_offset = off; off += d.kv_elements * es;
+    out->dq_offset = off; off = align(off + d.q_elements * 4);
+    out->dk_offset = off; off = align(off + d.kv_elements * 4);
+    out->dv_offset = off; off += d.kv_elements * 4;
     out->output_bytes = off;
     return FLAT_OK;
 }

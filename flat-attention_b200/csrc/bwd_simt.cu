@@ -1,4 +1,4 @@
-// Generic SIMT backward (LSE recompute): f32 arithmetic, f32 or bf16 storage, any head_dim <= 128.
+// Generic SIMT backward (LSE recompute): f32 arithmetic, f32 or bf16 inputs, f32 gradients, any head_dim <= 128.
 // It is the f32 parity kernel for dQ/dK/dV and the catch-all for shapes the tcgen05 backward does
 // not take.  Math per visible (query, key) pair, as in src/backward_grouped.rs:56-88:
 //   delta = dO.O,  P = exp(S*scale - LSE),  dP = dO.V,  dS = P*(dP - delta),
@@ -144,7 +144,7 @@ __global__ void __launch_bounds__(kThreads) bwd_dq_kernel(const __grid_constant_
             axpy_smem<DPT>(d_dot, &ks[j * DP], sub, dq);
         }
     }
-    if (valid) store_row<T, DPT>((T *)p.dq + (q_base + row) * D, sub, D, dq);
+    if (valid) store_row<float, DPT>((float *)p.dq + (q_base + row) * D, sub, D, dq);
 }
 
 // dK/dV: CTA = 32 key rows of one (batch, kv_head); the group's query heads and their query rows
@@ -200,8 +200,8 @@ __global__ void __launch_bounds__(kThreads) bwd_dkv_kernel(const __grid_constant
         }
     }
     if (valid) {
-        store_row<T, DPT>((T *)p.dk + (kv_base + row) * D, sub, D, dk);
-        store_row<T, DPT>((T *)p.dv + (kv_base + row) * D, sub, D, dv);
+        store_row<float, DPT>((float *)p.dk + (kv_base + row) * D, sub, D, dk);
+        store_row<float, DPT>((float *)p.dv + (kv_base + row) * D, sub, D, dv);
     }
 }
 

@@ -1,6 +1,443 @@
+// tcgen05 backward (LSE recompute) for bf16, head_dim 64 or 128, head-major, equal length,
+// seq_len a multiple of 128.  Math per visible (query q, key k) pair (src/backward_grouped.rs:56-88):
+//   P = exp(S*scale - LSE),  dP = dO.V,  dS = P*(dP - delta),  delta = dO.O
+//   dV[kv_head] += P^T dO,  dK[kv_head] += scale * dS^T Q,  dQ += scale * dS K
+// Two deterministic kernels, no atomics, results bitwise repeatable like the reference:
+//
+//  * KV-stationary (dK, dV): one CTA owns 128 keys of one (batch, kv_head); K and V stay in shared
+//    memory, (Q_i, dO_i) tiles of every query head of the group stream through a TMA ring.  Per
+//    tile: S^T = K Q_i^T and dP^T = V dO_i^T (SS MMAs into TMEM, keys on TMEM lanes), the eight
+//    elementwise warps turn them into bf16 P^T and dS^T in place (a thread owns a key row and half of
+//    the query columns; LSE and delta are per-column values read from shared memory), then
+//    dV += P^T dO_i and dK += dS^T Q_i (A operand from TMEM) accumulate in TMEM over all tiles and
+//    all heads of the group: the GQA reduction never leaves the SM.
+//  * Q-stationary (dQ): one CTA owns 128 queries of one (batch, q_head); (K_j, V_j) stream;
+//    S = Q K_j^T, dP = dO V_j^T, dS in place, dQ += dS K_j in TMEM.
+//
+// The score recompute is done twice (7 GEMM units instead of 5); in exchange nothing is accumulated
+// through global memory.  A prologue kernel writes delta and -LSE*log2(e) to context scratch.
+// Gradients are written in f32: the accumulators are f32, and a bf16 rounding of a gradient above 4
+// (ulp 2^-5) would by itself use up the 2e-2 absolute error bound.
+#include <cuda.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+
 #include "common.h"
+#include "sm100_host.cuh"
+#include "sm100_ptx.cuh"
+
 namespace flat {
-bool backward_sm100_supported(const BwdParams &) { return false; }
-uint64_t backward_sm100_workspace_bytes(const BwdParams &) { return 0; }
-int launch_backward_sm100(flat_ctx *ctx, const BwdParams &) { return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE, "not built"); }
+namespace {
+
+using namespace sm100;
+
+constexpr int kTile = 128;
+constexpr int kThreads = 384;
+constexpr int kProducerWarp = 8;
+constexpr int kMmaWarp = 9;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct BwdKernelParams {
+    CUtensorMap map_q, map_k, map_v, map_do;
+    const float *neg_lse2;  // -LSE * log2(e), [B, Hq, N]
+    const float *delta;     // dO . O, [B, Hq, N]
+    void *out0, *out1;      // f32 outputs.  KV-stationary: dV, dK; Q-stationary: dQ, unused
+    int batch, q_heads, kv_heads, seq_len, group, n_tiles;
+    int causal;
+    float scale, scale_log2;
+    uint32_t idesc_k, idesc_mn;
+    DeviceStatus *status;
+};
+
+template <int D> struct BCfg {
+    static constexpr int kBoxes = D / 64;
+    static constexpr int kBoxBytes = kTile * 128;
+    static constexpr int kTileBytes = kBoxes * kBoxBytes;
+    static constexpr int kStageBytes = 2 * kTileBytes + 1024;  // two tiles + 128 f32 lse + 128 f32 delta
+    static constexpr int kStages = D == 128 ? 2 : 4;
+    static constexpr int kBars = 1 + 2 * kStages + 3;
+    static constexpr int kSmemBytes = 2 * kTileBytes + kStages * kStageBytes + kBars * 8 + 16 + 1024;
+};
+
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+                 "l"(src), "r"(bytes), "r"(bar)
+                 : "memory");
 }
+
+__device__ __forceinline__ void timeout(const BwdKernelParams &p, int where) {
+    if (p.status) {
+        p.status->code = FLAT_ERR_DEVICE_WAIT_TIMEOUT;
+        p.status->where = where;
+    }
+}
+
+// KV == true: stationary (K, V), streamed (Q, dO), outputs dV (out0) and dK (out1).
+// KV == false: stationary (Q, dO), streamed (K, V), output dQ (out0).
+template <int D, bool KV>
+__global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_constant__ BwdKernelParams p) {
+    using C = BCfg<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *st0 = smem;                    // stationary tile 0 (K or Q)
+    uint8_t *st1 = smem + C::kTileBytes;    // stationary tile 1 (V or dO)
+    uint8_t *ring = smem + 2 * C::kTileBytes;
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring + C::kStages * C::kStageBytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + C::kBars);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+    const uint32_t bar0 = smem_u32(bars);
+    const uint32_t st_full = bar0;
+    auto rg_full = [&](int s) { return bar0 + 8u * (1 + s); };
+    auto rg_empty = [&](int s) { return bar0 + 8u * (1 + C::kStages + s); };
+    const uint32_t xy_full = bar0 + 8u * (1 + 2 * C::kStages);   // both score products in TMEM
+    const uint32_t ds_full = bar0 + 8u * (2 + 2 * C::kStages);   // bf16 P / dS written
+    const uint32_t acc_final = bar0 + 8u * (3 + 2 * C::kStages);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // block -> (tile, head, batch); blocks with more work first
+    const int heads = KV ? p.kv_heads : p.q_heads;
+    const int lin = blockIdx.x;
+    const int tile_rank = lin / (heads * p.batch);
+    const int bh = lin % (heads * p.batch);
+    const int b = bh / heads, h = bh % heads;
+    // KV-stationary: early key tiles see the most queries; Q-stationary: late query tiles see the most keys
+    const int t_own = p.causal ? (KV ? tile_rank : p.n_tiles - 1 - tile_rank) : tile_rank;
+    const int first = p.causal ? (KV ? t_own : 0) : 0;
+    const int last = p.causal ? (KV ? p.n_tiles - 1 : t_own) : p.n_tiles - 1;
+    const int per_head = last - first + 1;
+    const int n_iter = KV ? per_head * p.group : per_head;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(st_full, 1);
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(rg_full(s), 1);
+            mbar_init(rg_empty(s), 1);
+        }
+        mbar_init(xy_full, 1);
+        mbar_init(ds_full, 8);
+        mbar_init(acc_final, 1);
+        mbar_fence_init();
+        fence_proxy_async();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    constexpr uint32_t kColX = 0, kColY = 128, kColA0 = 256, kColA1 = 256 + D;
+
+    if (warp >= 8) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        if (warp == kProducerWarp && lane == 0) {
+            // ================= TMA producer =================
+            const CUtensorMap *m_st0 = KV ? &p.map_k : &p.map_q, *m_st1 = KV ? &p.map_v : &p.map_do;
+            const CUtensorMap *m_r0 = KV ? &p.map_q : &p.map_k, *m_r1 = KV ? &p.map_do : &p.map_v;
+            mbar_expect_tx(st_full, 2 * C::kTileBytes);
+            for (int kb = 0; kb < C::kBoxes; ++kb) {
+                tma_load_4d(smem_u32(st0 + kb * C::kBoxBytes), m_st0, kb * 64, t_own * kTile, h, b, st_full);
+                tma_load_4d(smem_u32(st1 + kb * C::kBoxBytes), m_st1, kb * 64, t_own * kTile, h, b, st_full);
+            }
+            for (int it = 0; it < n_iter; ++it) {
+                const int s = it % C::kStages;
+                const uint32_t phase = (it / C::kStages) & 1;
+                if (!mbar_wait(rg_empty(s), phase ^ 1, abort_flag)) {
+                    timeout(p, 100 + s);
+                    break;
+                }
+                const int t = first + it % per_head;
+                const int hs = KV ? h * p.group + it / per_head : h / p.group;  // head of the streamed tensors
+                uint8_t *stage = ring + s * C::kStageBytes;
+                mbar_expect_tx(rg_full(s), KV ? C::kStageBytes : 2 * C::kTileBytes);
+                for (int kb = 0; kb < C::kBoxes; ++kb) {
+                    tma_load_4d(smem_u32(stage + kb * C::kBoxBytes), m_r0, kb * 64, t * kTile, hs, b, rg_full(s));
+                    tma_load_4d(smem_u32(stage + C::kTileBytes + kb * C::kBoxBytes), m_r1, kb * 64, t * kTile, hs, b,
+                                rg_full(s));
+                }
+                if (KV) {  // per-query LSE and delta of the streamed query tile
+                    const long long row0 = ((long long)b * p.q_heads + hs) * p.seq_len + (long long)t * kTile;
+                    bulk_copy_g2s(smem_u32(stage + 2 * C::kTileBytes), p.neg_lse2 + row0, 512, rg_full(s));
+                    bulk_copy_g2s(smem_u32(stage + 2 * C::kTileBytes + 512), p.delta + row0, 512, rg_full(s));
+                }
+            }
+        } else if (warp == kMmaWarp && lane == 0) {
+            // ================= MMA issuer =================
+            bool ok = true;
+            auto wait = [&](uint32_t bar, uint32_t parity, int where) {
+                if (!ok) return;
+                if (!mbar_wait(bar, parity, abort_flag)) {
+                    timeout(p, where);
+                    ok = false;
+                }
+            };
+            // X = st0 * r0^T, Y = st1 * r1^T: both operands K-major tiles in shared memory
+            auto issue_xy = [&](uint32_t col, const uint8_t *a_tile, const uint8_t *b_tile) {
+                const uint32_t a0 = smem_u32(a_tile), b0 = smem_u32(b_tile);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off = (kk / 4) * C::kBoxBytes + (kk % 4) * 32;
+                    mma_ss(tmem_base + col, make_smem_desc(a0 + off, 0, 1024), make_smem_desc(b0 + off, 0, 1024), p.idesc_k,
+                           kk > 0);
+                }
+            };
+            // acc (+)= A[tmem, 128 x 128 bf16 in two 32-column halves] * B[smem tile as MN-major, 128 x D]
+            auto issue_acc = [&](uint32_t col_acc, uint32_t col_a, const uint8_t *b_tile, bool accumulate) {
+                const uint32_t b0 = smem_u32(b_tile);
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk) {
+                    const uint32_t a_col = col_a + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
+                    mma_ts(tmem_base + col_acc, tmem_base + a_col, make_smem_desc(b0 + kk * 16 * 128, C::kBoxBytes, 1024),
+                           p.idesc_mn, (accumulate || kk > 0));
+                }
+            };
+            wait(st_full, 0, 200);
+            for (int it = 0; ok && it < n_iter; ++it) {
+                const int s = it % C::kStages;
+                const uint8_t *stage = ring + s * C::kStageBytes;
+                wait(rg_full(s), (it / C::kStages) & 1, 210);
+                if (!ok) break;
+                tc_fence_after();
+                issue_xy(kColX, st0, stage);
+                issue_xy(kColY, st1, stage + C::kTileBytes);
+                tc_commit(xy_full);
+                wait(ds_full, it & 1, 220);
+                if (!ok) break;
+                tc_fence_after();
+                if (KV) {
+                    issue_acc(kColA0, kColX, stage + C::kTileBytes, it > 0);  // dV += P^T dO
+                    issue_acc(kColA1, kColY, stage, it > 0);                  // dK += dS^T Q
+                } else {
+                    issue_acc(kColA0, kColX, stage, it > 0);                  // dQ += dS K
+                }
+                tc_commit(rg_empty(s));
+            }
+            if (ok) tc_commit(acc_final);
+        }
+    } else {
+        // ================= elementwise warps + epilogue =================
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        const int half = warp >> 2;                  // which 64 columns of the 128
+        const int lane_base = (warp & 3) * 32;
+        const int row_local = lane_base + lane;      // TMEM lane: key (KV) or query (Q-stationary)
+        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16);
+        const uint32_t t_x = t_lane + kColX + half * 64, t_y = t_lane + kColY + half * 64;
+        uint64_t c2;
+        asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(p.scale_log2));
+        float my_neg_lse2 = 0.f, my_delta = 0.f;
+        if (!KV) {
+            const long long row = ((long long)b * p.q_heads + h) * p.seq_len + (long long)t_own * kTile + row_local;
+            my_neg_lse2 = p.neg_lse2[row];
+            my_delta = p.delta[row];
+        }
+        bool ok = true;
+        for (int it = 0; ok && it < n_iter; ++it) {
+            const int s = it % C::kStages;
+            const uint8_t *stage = ring + s * C::kStageBytes;
+            if (KV && !mbar_wait(rg_full(s), (it / C::kStages) & 1, abort_flag)) {  // LSE / delta of this stage
+                timeout(p, 300);
+                ok = false;
+                break;
+            }
+            if (!mbar_wait(xy_full, it & 1, abort_flag)) {
+                timeout(p, 310);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const int t = first + it % per_head;
+            const bool diag = p.causal && t == t_own;
+            uint32_t x[64], y[64];
+            tmem_ld32(t_x, x);
+            tmem_ld32(t_x + 32, x + 32);
+            tmem_ld32(t_y, y);
+            tmem_ld32(t_y + 32, y + 32);
+            tc_wait_ld();
+            const float *lse_s = reinterpret_cast<const float *>(stage + 2 * C::kTileBytes) + half * 64;
+            const float *delta_s = lse_s + 128;
+            uint32_t pp[32], ds[32];
+#pragma unroll
+            for (int i = 0; i < 64; i += 2) {
+                uint64_t s2, nl2, dl2, t2, y2, d2;
+                asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(x[i]), "r"(x[i + 1]));
+                asm("mov.b64 %0, {%1, %2};" : "=l"(y2) : "r"(y[i]), "r"(y[i + 1]));
+                if (KV) {
+                    const float2 nl = *reinterpret_cast<const float2 *>(lse_s + i);
+                    const float2 dl = *reinterpret_cast<const float2 *>(delta_s + i);
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(nl2) : "f"(nl.x), "f"(nl.y));
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(dl2) : "f"(dl.x), "f"(dl.y));
+                } else {
+                    asm("mov.b64 %0, {%1, %1};" : "=l"(nl2) : "f"(my_neg_lse2));
+                    asm("mov.b64 %0, {%1, %1};" : "=l"(dl2) : "f"(my_delta));
+                }
+                asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(t2) : "l"(s2), "l"(c2), "l"(nl2));
+                asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d2) : "l"(y2), "l"(dl2));
+                float t0, t1, e0, e1;
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(t0), "=f"(t1) : "l"(t2));
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(e0), "=f"(e1) : "l"(d2));
+                float p0 = ex2(t0), p1 = ex2(t1);
+                if (diag) {
+                    // visible iff key <= query.  KV: row = key, column = query.  Q-stationary: row = query, column = key.
+                    const int c0 = half * 64 + i;
+                    const bool v0 = KV ? (row_local <= c0) : (c0 <= row_local);
+                    const bool v1 = KV ? (row_local <= c0 + 1) : (c0 + 1 <= row_local);
+                    if (!v0) p0 = 0.f;
+                    if (!v1) p1 = 0.f;
+                }
+                const __nv_bfloat162 dsb = __floats2bfloat162_rn(p0 * e0, p1 * e1);
+                ds[i >> 1] = *reinterpret_cast<const uint32_t *>(&dsb);
+                if (KV) {
+                    const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+                    pp[i >> 1] = *reinterpret_cast<const uint32_t *>(&pb);
+                }
+            }
+            // bf16 results go to the first 32 columns of this warp group's own 64-column range
+            if (KV) {
+                tmem_st32(t_x, pp);   // P^T over S^T
+                tmem_st32(t_y, ds);   // dS^T over dP^T
+            } else {
+                tmem_st32(t_x, ds);   // dS over S
+            }
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ds_full);
+        }
+        if (ok && !mbar_wait(acc_final, 0, abort_flag)) {
+            timeout(p, 320);
+            ok = false;
+        }
+        if (ok) {
+            tc_fence_after();
+            // each warp group writes half of the head dimension of the accumulator rows
+            const long long out_row = ((long long)b * heads + h) * p.seq_len + (long long)t_own * kTile + row_local;
+            constexpr int kColsPerHalf = D / 2;
+#pragma unroll
+            for (int a = 0; a < (KV ? 2 : 1); ++a) {
+                const float mul = (KV && a == 0) ? 1.0f : p.scale;  // dV unscaled; dK and dQ carry the softmax scale
+                float *op = reinterpret_cast<float *>(a == 0 ? p.out0 : p.out1) + out_row * D + half * kColsPerHalf;
+                const uint32_t t_acc = t_lane + (a == 0 ? kColA0 : kColA1) + half * kColsPerHalf;
+#pragma unroll
+                for (int c = 0; c < kColsPerHalf / 32; ++c) {
+                    uint32_t r[32];
+                    tmem_ld32(t_acc + c * 32, r);
+                    tc_wait_ld();
+                    float4 *dst = reinterpret_cast<float4 *>(op + c * 32);
+#pragma unroll
+                    for (int q4 = 0; q4 < 8; ++q4)
+                        dst[q4] = make_float4(__uint_as_float(r[q4 * 4]) * mul, __uint_as_float(r[q4 * 4 + 1]) * mul,
+                                              __uint_as_float(r[q4 * 4 + 2]) * mul, __uint_as_float(r[q4 * 4 + 3]) * mul);
+                }
+            }
+        }
+    }
+
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let copies in flight land before the CTA exits
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+// delta = dO . O and -LSE*log2(e), one warp per row
+__global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16 *__restrict__ d_out,
+                                                       const __nv_bfloat16 *__restrict__ out, const float *__restrict__ lse,
+                                                       float *__restrict__ delta, float *__restrict__ neg_lse2, int64_t rows,
+                                                       int head_dim) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    float acc = 0.f;
+    for (int d = lane * 2; d < head_dim; d += 64) {
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(d_out + row * head_dim + d));
+        const float2 o = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(out + row * head_dim + d));
+        acc = fmaf(a.x, o.x, acc);
+        acc = fmaf(a.y, o.y, acc);
+    }
+#pragma unroll
+    for (int w = 16; w >= 1; w >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
+    if (lane == 0) {
+        delta[row] = acc;
+        neg_lse2[row] = -lse[row] * kLog2e;
+    }
+}
+
+bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+}  // namespace
+
+bool backward_sm100_supported(const BwdParams &p) {
+    if (p.head_dim != 64 && p.head_dim != 128) return false;
+    if (p.seq_len % kTile != 0) return false;
+    const void *ptrs[] = {p.q, p.k, p.v, p.d_out, p.out, p.dq, p.dk, p.dv};
+    for (const void *x : ptrs)
+        if (!aligned16(x)) return false;
+    return true;
+}
+
+uint64_t backward_sm100_workspace_bytes(const BwdParams &p) {
+    return 2 * (uint64_t)p.batch * p.q_heads * p.seq_len * sizeof(float);
+}
+
+int launch_backward_sm100(flat_ctx *ctx, const BwdParams &p) {
+    int st = ensure_workspace(ctx, kWorkspaceMeta + backward_sm100_workspace_bytes(p));
+    if (st) return st;
+    const int D = p.head_dim, N = p.seq_len;
+    const int64_t rows = (int64_t)p.batch * p.q_heads * N;
+    float *delta = reinterpret_cast<float *>(scratch_ptr(ctx));
+    float *neg_lse2 = delta + rows;
+    bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, ctx->stream>>>(
+        static_cast<const __nv_bfloat16 *>(p.d_out), static_cast<const __nv_bfloat16 *>(p.out), p.lse, delta, neg_lse2, rows, D);
+    ctx->launches += 1;
+
+    BwdKernelParams kp{};
+    const int64_t rs = D, hs = (int64_t)N * D;
+    if ((st = make_map(ctx, &kp.map_q, false, p.q, D, N, p.q_heads, p.batch, rs, hs, hs * p.q_heads, kTile))) return st;
+    if ((st = make_map(ctx, &kp.map_do, false, p.d_out, D, N, p.q_heads, p.batch, rs, hs, hs * p.q_heads, kTile))) return st;
+    if ((st = make_map(ctx, &kp.map_k, false, p.k, D, N, p.kv_heads, p.batch, rs, hs, hs * p.kv_heads, kTile))) return st;
+    if ((st = make_map(ctx, &kp.map_v, false, p.v, D, N, p.kv_heads, p.batch, rs, hs, hs * p.kv_heads, kTile))) return st;
+    kp.neg_lse2 = neg_lse2;
+    kp.delta = delta;
+    kp.batch = p.batch; kp.q_heads = p.q_heads; kp.kv_heads = p.kv_heads; kp.seq_len = N; kp.group = p.group;
+    kp.n_tiles = N / kTile;
+    kp.causal = p.causal;
+    kp.scale = p.scale;
+    kp.scale_log2 = p.scale * kLog2e;
+    kp.idesc_k = make_idesc(kFmtBF16, kFmtBF16, 0, 0, 128, 128);
+    kp.idesc_mn = make_idesc(kFmtBF16, kFmtBF16, 0, 1, 128, (uint32_t)D);
+    kp.status = ctx->dev_status;
+
+    auto run = [&](auto kernel, int smem_bytes, long long grid) -> int {
+        FLAT_CUDA_OK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        KernelTimer timer(ctx);
+        kernel<<<(unsigned)grid, kThreads, smem_bytes, ctx->stream>>>(kp);
+        return FLAT_OK;
+    };
+    const long long grid_kv = (long long)kp.n_tiles * p.kv_heads * p.batch;
+    const long long grid_q = (long long)kp.n_tiles * p.q_heads * p.batch;
+    kp.out0 = p.dv;
+    kp.out1 = p.dk;
+    if (D == 128) st = run(bwd_sm100_kernel<128, true>, BCfg<128>::kSmemBytes, grid_kv);
+    else st = run(bwd_sm100_kernel<64, true>, BCfg<64>::kSmemBytes, grid_kv);
+    if (st) return st;
+    kp.out0 = p.dq;
+    kp.out1 = nullptr;
+    if (D == 128) st = run(bwd_sm100_kernel<128, false>, BCfg<128>::kSmemBytes, grid_q);
+    else st = run(bwd_sm100_kernel<64, false>, BCfg<64>::kSmemBytes, grid_q);
+    if (st) return st;
+    ctx->launches += 2;
+    FLAT_CUDA_OK(ctx, cudaGetLastError());
+    return FLAT_OK;
+}
+
+}  // namespace flat

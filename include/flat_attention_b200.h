@@ -438,7 +438,8 @@ int32_t flat_backward_layout_for(int32_t dtype, const flat_attention_shape *shap
 /* WgpuGroupedBackwardRecomputePipeline::encode (src/wgpu_backward_grouped.rs:318-326) and
  * WgpuBackwardRecomputePipeline::encode (src/wgpu_backward.rs:286-308; the q_heads ==
  * kv_heads case): head-major, equal length, inputs Q,K,V,dO,O,LSE packed per the layout,
- * outputs dQ|dK|dV with dK/dV reduced over each KV head's query-head group. */
+ * outputs dQ|dK|dV with dK/dV reduced over each KV head's query-head group.  Gradients are f32
+ * in both dtypes (bf16 mode: bf16 Q,K,V,dO,O in, f32 dQ,dK,dV out). */
 int32_t flat_backward_grouped(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
                               const flat_attention_config *config, flat_buffer packed_inputs,
                               flat_buffer packed_grads);

@@ -232,6 +232,23 @@ def backward_units(q, k, v, d_out, fwd_out, fwd_lse, batch, q_heads, kv_heads, s
     return dq, dk, dv
 
 
+def backward_rows(q, k, v, d_out, fwd_out, fwd_lse, batch, q_heads, kv_heads, seq_len, head_dim, dq_rows, dkv_rows,
+                  causal=False, softmax_scale=None, threads=1):
+    """Oracle backward on sampled rows: dq_rows = (batch, q_head, query), dkv_rows = (batch, kv_head, key)."""
+    q, k, v, d_out, fwd_out, fwd_lse = map(_f32, (q, k, v, d_out, fwd_out, fwd_lse))
+    a = np.ascontiguousarray(np.array(dq_rows, dtype=np.uint64).reshape(-1, 3))
+    b = np.ascontiguousarray(np.array(dkv_rows, dtype=np.uint64).reshape(-1, 3))
+    dq = np.empty((max(a.shape[0], 1), head_dim), np.float32)
+    dk = np.empty((max(b.shape[0], 1), head_dim), np.float32)
+    dv = np.empty((max(b.shape[0], 1), head_dim), np.float32)
+    cfg = make_config(causal, softmax_scale)
+    _check(lib().flat_oracle_backward_rows(_p(q), _p(k), _p(v), _p(d_out), _p(fwd_out), _p(fwd_lse), C.c_uint64(batch),
+                                           C.c_uint64(q_heads), C.c_uint64(kv_heads), C.c_uint64(seq_len),
+                                           C.c_uint64(head_dim), C.byref(cfg), _u64p(a), C.c_uint64(a.shape[0]), _u64p(b),
+                                           C.c_uint64(b.shape[0]), C.c_int32(threads), _p(dq), _p(dk), _p(dv)))
+    return dq[:a.shape[0]], dk[:b.shape[0]], dv[:b.shape[0]]
+
+
 def rotate_rows(src, head_dim, positions, theta):
     """Materialised RoPE of rows [row_count, head_dim] at the given absolute positions."""
     src = _f32(src)

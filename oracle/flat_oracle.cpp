@@ -563,6 +563,78 @@ int32_t flat_oracle_backward_units(const float *q, const float *k, const float *
     return FLAT_OK;
 }
 
+// Backward on sampled output rows for the large configurations.  dq_rows holds (batch, q_head, query)
+// triples, dkv_rows holds (batch, kv_head, key) triples.  Every output element is accumulated in the
+// order the reference visits its contributions (src/backward_grouped.rs:44-88: q_head ascending, then
+// query ascending for dK/dV; key ascending for dQ), so a row equals the same row of
+// flat_oracle_backward_grouped bit for bit.
+int32_t flat_oracle_backward_rows(const float *q, const float *k, const float *v, const float *d_out,
+                                  const float *fwd_out, const float *fwd_lse, uint64_t batch, uint64_t q_heads,
+                                  uint64_t kv_heads, uint64_t seq_len, uint64_t head_dim,
+                                  const flat_attention_config *cfg, const uint64_t *dq_rows, uint64_t n_dq,
+                                  const uint64_t *dkv_rows, uint64_t n_dkv, int32_t threads, float *dq_out,
+                                  float *dk_out, float *dv_out) {
+    Shape s{batch, q_heads, kv_heads, seq_len, seq_len, head_dim, 0};
+    int st = validate_shape(s);
+    if (st) return st;
+    float scale;
+    if ((st = resolved_scale(cfg->has_softmax_scale, cfg->softmax_scale, head_dim, &scale))) return st;
+    const usize group = q_heads / kv_heads, D = head_dim, N = seq_len;
+    auto pair_terms = [&](usize b, usize q_head, usize query_pos, usize key_pos, float delta, float *prob, float *d_dot) {
+        const usize kv_head = q_head / group;
+        const usize q_base = ((b * q_heads + q_head) * N + query_pos) * D;
+        const usize kv_base = ((b * kv_heads + kv_head) * N + key_pos) * D;
+        float dot_qk = 0.0f, d_probability = 0.0f;
+        for (usize d = 0; d < D; ++d) {
+            dot_qk += q[q_base + d] * k[kv_base + d];
+            d_probability += d_out[q_base + d] * v[kv_base + d];
+        }
+        const float score = dot_qk * scale;
+        *prob = expf(score - fwd_lse[(b * q_heads + q_head) * N + query_pos]);
+        const float d_score = *prob * (d_probability - delta);
+        *d_dot = d_score * scale;
+    };
+    auto delta_of = [&](usize b, usize q_head, usize query_pos) {
+        const usize q_base = ((b * q_heads + q_head) * N + query_pos) * D;
+        float delta = 0.0f;
+        for (usize d = 0; d < D; ++d) delta += d_out[q_base + d] * fwd_out[q_base + d];
+        return delta;
+    };
+    run_parallel(n_dq, threads, [&](usize i) {
+        const usize b = dq_rows[3 * i], q_head = dq_rows[3 * i + 1], query_pos = dq_rows[3 * i + 2];
+        const usize kv_head = q_head / group;
+        float *out = dq_out + i * D;
+        for (usize d = 0; d < D; ++d) out[d] = 0.0f;
+        const float delta = delta_of(b, q_head, query_pos);
+        const usize key_limit = cfg->causal ? query_pos + 1 : N;
+        for (usize key_pos = 0; key_pos < key_limit; ++key_pos) {
+            float prob, d_dot;
+            pair_terms(b, q_head, query_pos, key_pos, delta, &prob, &d_dot);
+            const usize kv_base = ((b * kv_heads + kv_head) * N + key_pos) * D;
+            for (usize d = 0; d < D; ++d) out[d] += d_dot * k[kv_base + d];
+        }
+    });
+    run_parallel(n_dkv, threads, [&](usize i) {
+        const usize b = dkv_rows[3 * i], kv_head = dkv_rows[3 * i + 1], key_pos = dkv_rows[3 * i + 2];
+        float *ok = dk_out + i * D, *ov = dv_out + i * D;
+        for (usize d = 0; d < D; ++d) ok[d] = 0.0f, ov[d] = 0.0f;
+        for (usize g = 0; g < group; ++g) {
+            const usize q_head = kv_head * group + g;
+            for (usize query_pos = cfg->causal ? key_pos : 0; query_pos < N; ++query_pos) {
+                const float delta = delta_of(b, q_head, query_pos);
+                float prob, d_dot;
+                pair_terms(b, q_head, query_pos, key_pos, delta, &prob, &d_dot);
+                const usize q_base = ((b * q_heads + q_head) * N + query_pos) * D;
+                for (usize d = 0; d < D; ++d) {
+                    ok[d] += d_dot * q[q_base + d];
+                    ov[d] += prob * d_out[q_base + d];
+                }
+            }
+        }
+    });
+    return FLAT_OK;
+}
+
 // Materialised RoPE, the helper of tests/rotary_grouped.rs:15-47 generalised to a list of rows:
 // row r (head_dim contiguous floats at src + r*head_dim) is rotated at positions[r].
 void flat_oracle_rotate_rows(const float *src, float *dst, uint64_t row_count, uint64_t head_dim,

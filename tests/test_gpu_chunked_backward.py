@@ -100,10 +100,9 @@ def run_backward(dtype, B, Hq, Hkv, N, D, causal, scale, q, k, v, do, fo, fl, mh
     grads.fill_(0x7f)
     (c.backward_mha if mha else c.backward_grouped)(dtype, shp, fa.config(causal, scale), packed.cuda(), grads)
     raw = grads.cpu()
-    es = 2 if dtype == fa.BF16 else 4
-    dq = raw[L.dq_offset:L.dq_offset + L.q_elements * es].view(td).float().numpy()
-    dk = raw[L.dk_offset:L.dk_offset + L.kv_elements * es].view(td).float().numpy()
-    dv = raw[L.dv_offset:L.dv_offset + L.kv_elements * es].view(td).float().numpy()
+    dq = raw[L.dq_offset:L.dq_offset + L.q_elements * 4].view(torch.float32).numpy()   # gradients are f32 in both modes
+    dk = raw[L.dk_offset:L.dk_offset + L.kv_elements * 4].view(torch.float32).numpy()
+    dv = raw[L.dv_offset:L.dv_offset + L.kv_elements * 4].view(torch.float32).numpy()
     return dq, dk, dv
 
 

@@ -76,6 +76,21 @@ def test_backward_cardinality_and_units_equal_full():
         assert np.array_equal(bits(uv.reshape(-1)), bits(dv))
 
 
+def test_backward_rows_equal_full_oracle():
+    B, Hq, Hkv, N, D = 2, 4, 2, 7, 8
+    q, k, v = bfix(B * Hq * N * D, 0.2), bfix(B * Hkv * N * D, 0.8), bfix(B * Hkv * N * D, 1.3)
+    d_out = bfix(B * Hq * N * D, 1.9)
+    for causal in (False, True):
+        fo, fl = ob.forward_reference_grouped(q, k, v, B, Hq, Hkv, N, D, causal)
+        dq, dk, dv = ob.backward_reference_grouped(q, k, v, d_out, fo, fl, B, Hq, Hkv, N, D, causal)
+        qr = [(b, h, r) for b in range(B) for h in range(Hq) for r in range(N)]
+        kr = [(b, h, r) for b in range(B) for h in range(Hkv) for r in range(N)]
+        rq, rk, rv = ob.backward_rows(q, k, v, d_out, fo, fl, B, Hq, Hkv, N, D, qr, kr, causal, threads=3)
+        assert np.array_equal(bits(rq.reshape(-1)), bits(dq))
+        assert np.array_equal(bits(rk.reshape(-1)), bits(dk))
+        assert np.array_equal(bits(rv.reshape(-1)), bits(dv))
+
+
 # ---- src/paged_kv.rs:200-270 ------------------------------------------------------------------
 def test_mapping_is_stable_across_page_boundaries():
     t = ob.PagedKvTable(4, 3)
