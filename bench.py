@@ -246,6 +246,85 @@ def bench_decode(torch, np, fa, ctx, peaks, steps, warmup):
     }
 
 
+def bench_backward(torch, fa, ctx, peaks, steps, warmup):
+    """Config 5: grouped backward recompute, TFLOP/s of the 5 algorithmic GEMMs (10*B*Hq*N^2*D/2 flop)."""
+    c = C5
+    B, Hq, Hkv, N, D = c["B"], c["Hq"], c["Hkv"], c["N"], c["D"]
+    g = torch.Generator(device="cuda").manual_seed(11)
+    q = torch.randn(B, Hq, N, D, generator=g, device="cuda").bfloat16()
+    k = torch.randn(B, Hkv, N, D, generator=g, device="cuda").bfloat16()
+    v = torch.randn(B, Hkv, N, D, generator=g, device="cuda").bfloat16()
+    do = torch.randn(B, Hq, N, D, generator=g, device="cuda").bfloat16()
+    shp = fa.shape(B, Hq, Hkv, N, N, D)
+    FL, L = fa.forward_layout(fa.BF16, shp), fa.backward_layout(fa.BF16, shp)
+    fwd = ctx.create_output_buffer(fa.BF16, shp)
+    ctx.forward_grouped(fa.BF16, shp, fa.config(True), q, k, v, fwd)
+    packed = ctx.empty_bytes(L.input_bytes)
+    for off, t in ((L.q_offset, q), (L.k_offset, k), (L.v_offset, v), (L.d_out_offset, do)):
+        packed[off:off + t.numel() * 2] = t.view(torch.uint8).reshape(-1)
+    packed[L.out_offset:L.out_offset + FL.q_bytes] = fwd[:FL.q_bytes]
+    packed[L.lse_offset:L.lse_offset + 4 * FL.lse_elements] = fwd[FL.lse_byte_offset:FL.lse_byte_offset + 4 * FL.lse_elements]
+    grads = ctx.empty_bytes(L.output_bytes)
+    cfg = fa.config(True)
+    for _ in range(warmup):
+        ctx.backward_grouped(fa.BF16, shp, cfg, packed, grads)
+    ctx.set_kernel_timing(True)
+    ctx.take_kernel_time()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        ctx.backward_grouped(fa.BF16, shp, cfg, packed, grads)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    kms, kn = ctx.take_kernel_time()
+    ctx.set_kernel_timing(False)
+    flops = 10 * B * Hq * N * N * D // 2
+    kernel_ms = kms / steps  # the two tensor-core kernels of one call
+    return {"metric": "grouped_backward_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
+            "flop_per_step": flops, "workload": "C5 B=2 Hq=32 Hkv=8 N=8192 D=128 causal bf16, f32 gradients",
+            "roofline": {"bound": "tensor", "achieved": flops / (kernel_ms * 1e-3) / 1e12, "peak": peaks["bf16_sustained"] or peaks["bf16_tflops"],
+                         "unit": "TFLOP/s", "frac": flops / (kernel_ms * 1e-3) / 1e12 / (peaks["bf16_sustained"] or peaks["bf16_tflops"]),
+                         "traffic": None, "kernel": "bwd_sm100_kernel<128,true> + bwd_sm100_kernel<128,false>",
+                         "kernel_ms": kernel_ms, "peak_source": peaks["source"] + " (sustained cuBLAS bf16: the step runs for milliseconds)",
+                         "note": "7 GEMM units are executed for 5 algorithmic ones (scores recomputed in both kernels)"}}
+
+
+def bench_chunked_prefill(torch, fa, ctx, peaks, warmup):
+    """Config 4 (prefill part): one 32768-token sequence fed in 2048-token chunks into a growing paged cache."""
+    Hq, Hkv, D, N, chunk, ps, theta = 64, 8, 128, 32768, 2048, 16, 500000.0
+    g = torch.Generator(device="cuda").manual_seed(13)
+    q = torch.randn(N, Hq * D, generator=g, device="cuda").bfloat16()
+    k = torch.randn(N, Hkv * D, generator=g, device="cuda").bfloat16()
+    v = torch.randn(N, Hkv * D, generator=g, device="cuda").bfloat16()
+    cache = fa.CudaPagedKvCache(ctx, fa.BF16, ps, N // ps + 8, Hkv, D)
+    out = ctx.empty_bytes(chunk * Hq * D * 2 + Hq * chunk * 4)
+    cfg = fa.config(True)
+
+    def run():
+        cache.reset()
+        for start in range(0, N, chunk):
+            ctx.chunked_prefill_paged(cache, Hq, chunk, cfg, theta, 0, q[start:start + chunk], k[start:start + chunk],
+                                      v[start:start + chunk], out)
+    for _ in range(max(1, warmup - 2)):
+        run()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 3
+    e0.record()
+    for _ in range(reps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    flops = 4 * Hq * D * N * N // 2
+    return {"metric": "chunked_prefill_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_sequence": ms,
+            "flop_per_sequence": flops, "frac_of_peak": flops / (ms * 1e-3) / 1e12 / (peaks["bf16_sustained"] or peaks["bf16_tflops"]),
+            "workload": "C4 1 x 32768 tokens in 2048-token chunks, Hq=64 Hkv=8 D=128 causal bf16, page 16, RoPE fused "
+                        "into the cache append (K) and into the attention kernel (Q)"}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -336,8 +415,10 @@ def main():
     ms_per_step = ms / args.steps
     value = world * flops / (ms_per_step * 1e-3) / 1e12
     kms = kernel_ms / max(kernel_n, 1)
-    # the step is short and the GPU is idle between bench phases: the burst peak is the denominator
-    peak = peaks["bf16_tflops"]
+    # denominator: the sustained cuBLAS figure when the timed loop ran into the power cap (back-to-back
+    # steps for a good fraction of a second), the burst figure when it did not
+    capped = bool(clocks and "sw_power_cap" in (clocks.get("reasons") or []))
+    peak = (peaks["bf16_sustained"] or peaks["bf16_tflops"]) if capped else peaks["bf16_tflops"]
     line = {
         "metric": "prefill_attention_tflops", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
@@ -352,7 +433,9 @@ def main():
         "gpu_launches": int(launches),
         "roofline": {"bound": "tensor", "achieved": flops / (kms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
                      "frac": flops / (kms * 1e-3) / 1e12 / peak, "traffic": None, "kernel": "fwd_sm100_kernel<128,false>",
-                     "kernel_ms": kms, "peak_source": peaks["source"] + " (burst cuBLAS bf16)"},
+                     "kernel_ms": kms,
+                     "peak_source": peaks["source"] + (" (sustained cuBLAS bf16: sw_power_cap was active during the timed loop)"
+                                                       if capped else " (burst cuBLAS bf16)")},
         "clocks": clocks,
         "parity": parity,
         "device_status": status,
@@ -367,6 +450,8 @@ def main():
     if rank == 0 and world == 1:
         if not args.skip_extras:
             line["decode"] = bench_decode(torch, np, fa, ctx, peaks, max(5, min(args.steps, 20)), args.warmup)
+            line["backward"] = bench_backward(torch, fa, ctx, peaks, max(3, min(args.steps, 10)), args.warmup)
+            line["chunked_prefill"] = bench_chunked_prefill(torch, fa, ctx, peaks, args.warmup)
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -338,6 +338,23 @@ class Context:
             C.c_void_p(q_rope_positions_dev.data_ptr()), ip(host_context_lens), ip(host_q_rope_positions),
             C.byref(cfg), C.c_float(theta), C.c_uint32(kv_splits), buf(q), _b(k), _b(v), buf(out)))
 
+    def decode_paged_batched_partial(self, dtype, num_seqs, q_heads, kv_heads, head_dim, page_size, physical_pages,
+                                     max_pages_per_seq, page_tables_dev, context_lens_dev, q_rope_positions_dev,
+                                     host_page_tables, host_context_lens, cfg, theta, q, k, v, out):
+        """Per-GPU leg of KV-split decode: f32 [O | LSE] of this cache slice."""
+        def ip(a):
+            return None if a is None else a.ctypes.data_as(C.POINTER(C.c_int32))
+        self.check(lib().flat_decode_paged_batched_partial(
+            self.h, C.c_int32(dtype), C.c_uint64(num_seqs), C.c_uint64(q_heads), C.c_uint64(kv_heads),
+            C.c_uint64(head_dim), C.c_uint64(page_size), C.c_uint64(physical_pages), C.c_uint64(max_pages_per_seq),
+            C.c_void_p(page_tables_dev.data_ptr()), C.c_void_p(context_lens_dev.data_ptr()),
+            C.c_void_p(q_rope_positions_dev.data_ptr()), ip(host_page_tables), ip(host_context_lens), C.byref(cfg),
+            C.c_float(theta), buf(q), _b(k), _b(v), buf(out)))
+
+    def splitkv_merge_packed(self, dtype, parts, rows, head_dim, gathered, out):
+        self.check(lib().flat_splitkv_merge_packed(self.h, C.c_int32(dtype), C.c_uint64(parts), C.c_uint64(rows),
+                                                   C.c_uint64(head_dim), buf(gathered), buf(out)))
+
     def splitkv_merge(self, dtype, parts, rows, head_dim, partial_o, partial_lse, out):
         self.check(lib().flat_splitkv_merge(self.h, C.c_int32(dtype), C.c_uint64(parts), C.c_uint64(rows),
                                             C.c_uint64(head_dim), buf(partial_o), buf(partial_lse), buf(out)))

@@ -1053,14 +1053,14 @@ int32_t flat_decode_paged(flat_ctx *ctx, int32_t dtype, const flat_paged_kv_tabl
     return run_decode(ctx, dtype, p);
 }
 
-int32_t flat_decode_paged_batched(flat_ctx *ctx, int32_t dtype, uint64_t num_seqs, uint64_t q_heads,
-                                  uint64_t kv_heads, uint64_t head_dim, uint64_t page_size, uint64_t physical_pages,
-                                  uint64_t max_pages_per_seq, const int32_t *page_tables_dev,
-                                  const int32_t *context_lens_dev, const int32_t *q_rope_positions_dev,
-                                  const int32_t *host_page_tables, const int32_t *host_context_lens,
-                                  const int32_t *host_q_rope_positions, const flat_attention_config *config,
-                                  float theta, uint32_t kv_splits, flat_buffer q, flat_buffer k, flat_buffer v,
-                                  flat_buffer out_and_lse) {
+static int32_t decode_paged_batched_impl(flat_ctx *ctx, int32_t dtype, uint64_t num_seqs, uint64_t q_heads,
+                                         uint64_t kv_heads, uint64_t head_dim, uint64_t page_size, uint64_t physical_pages,
+                                         uint64_t max_pages_per_seq, const int32_t *page_tables_dev,
+                                         const int32_t *context_lens_dev, const int32_t *q_rope_positions_dev,
+                                         const int32_t *host_page_tables, const int32_t *host_context_lens,
+                                         const int32_t *host_q_rope_positions, const flat_attention_config *config,
+                                         float theta, uint32_t kv_splits, flat_buffer q, flat_buffer k, flat_buffer v,
+                                         flat_buffer out_and_lse, bool out_f32) {
     if (!ctx) return FLAT_ERR_NULL_POINTER;
     int st;
     if ((st = check_dtype(ctx, dtype))) return st;
@@ -1114,7 +1114,7 @@ int32_t flat_decode_paged_batched(flat_ctx *ctx, int32_t dtype, uint64_t num_seq
     const uint64_t es = dtype_size(dtype);
     const uint64_t q_elems = num_seqs * q_heads * head_dim;
     const uint64_t kv_bytes = pool_rows * kv_heads * head_dim * es;
-    const uint64_t lse_off = lse_offset_bytes(dtype, q_elems);
+    const uint64_t lse_off = out_f32 ? q_elems * 4 : lse_offset_bytes(dtype, q_elems);
     if ((st = check_buffer(ctx, "Q", q, q_elems * es))) return st;
     if ((st = check_buffer(ctx, "K", k, kv_bytes))) return st;
     if ((st = check_buffer(ctx, "V", v, kv_bytes))) return st;
@@ -1132,12 +1132,63 @@ int32_t flat_decode_paged_batched(flat_ctx *ctx, int32_t dtype, uint64_t num_seq
     p.q_rope_positions = q_rope_positions_dev;
     p.scale = scale;
     p.rope_q = 1;
+    p.out_f32 = out_f32 ? 1 : 0;
     fill_inv_freq(theta, p.head_dim, p.inv_freq);
     std::vector<int32_t> offsets;
     const uint64_t scratch = plan_decode(ctx, dtype, p, host_context_lens, total, max_len, kv_splits, &offsets);
     if ((st = ensure_workspace(ctx, kWorkspaceMeta + scratch))) return st;
     if ((st = upload_decode_plan(ctx, p, offsets))) return st;
     return run_decode(ctx, dtype, p);
+}
+
+int32_t flat_decode_paged_batched(flat_ctx *ctx, int32_t dtype, uint64_t num_seqs, uint64_t q_heads,
+                                  uint64_t kv_heads, uint64_t head_dim, uint64_t page_size, uint64_t physical_pages,
+                                  uint64_t max_pages_per_seq, const int32_t *page_tables_dev,
+                                  const int32_t *context_lens_dev, const int32_t *q_rope_positions_dev,
+                                  const int32_t *host_page_tables, const int32_t *host_context_lens,
+                                  const int32_t *host_q_rope_positions, const flat_attention_config *config,
+                                  float theta, uint32_t kv_splits, flat_buffer q, flat_buffer k, flat_buffer v,
+                                  flat_buffer out_and_lse) {
+    return decode_paged_batched_impl(ctx, dtype, num_seqs, q_heads, kv_heads, head_dim, page_size, physical_pages,
+                                     max_pages_per_seq, page_tables_dev, context_lens_dev, q_rope_positions_dev,
+                                     host_page_tables, host_context_lens, host_q_rope_positions, config, theta, kv_splits, q,
+                                     k, v, out_and_lse, false);
+}
+
+int32_t flat_decode_paged_batched_partial(flat_ctx *ctx, int32_t dtype, uint64_t num_seqs, uint64_t q_heads,
+                                          uint64_t kv_heads, uint64_t head_dim, uint64_t page_size,
+                                          uint64_t physical_pages, uint64_t max_pages_per_seq,
+                                          const int32_t *page_tables_dev, const int32_t *context_lens_dev,
+                                          const int32_t *q_rope_positions_dev, const int32_t *host_page_tables,
+                                          const int32_t *host_context_lens, const flat_attention_config *config,
+                                          float theta, flat_buffer q, flat_buffer k, flat_buffer v,
+                                          flat_buffer partial_out_and_lse) {
+    // the query position is global while this cache holds a slice of the sequence: the visibility
+    // precondition is the caller's (host_q_rope_positions = null skips the per-slice check)
+    return decode_paged_batched_impl(ctx, dtype, num_seqs, q_heads, kv_heads, head_dim, page_size, physical_pages,
+                                     max_pages_per_seq, page_tables_dev, context_lens_dev, q_rope_positions_dev,
+                                     host_page_tables, host_context_lens, nullptr, config, theta, 0, q, k, v,
+                                     partial_out_and_lse, true);
+}
+
+int32_t flat_splitkv_merge_packed(flat_ctx *ctx, int32_t dtype, uint64_t parts, uint64_t rows, uint64_t head_dim,
+                                  flat_buffer gathered, flat_buffer out_and_lse) {
+    if (!ctx) return FLAT_ERR_NULL_POINTER;
+    int st;
+    if ((st = check_dtype(ctx, dtype))) return st;
+    if (parts == 0 || rows == 0 || head_dim == 0) return fail(ctx, FLAT_ERR_ZERO_DIMENSION, "merge dimensions must be non-zero");
+    if (head_dim > (uint64_t)kMaxHeadDim)
+        return fail(ctx, FLAT_ERR_UNSUPPORTED_HEAD_DIM, "head_dim %llu exceeds maximum %d", (unsigned long long)head_dim, kMaxHeadDim);
+    if (parts > 65536 || rows > ((uint64_t)1 << 31))
+        return fail(ctx, FLAT_ERR_INDEX_SPACE_EXCEEDED, "merge geometry exceeds the index space");
+    const uint64_t part_floats = rows * (head_dim + 1);
+    const uint64_t lse_off = lse_offset_bytes(dtype, rows * head_dim);
+    if ((st = check_buffer(ctx, "gathered partials", gathered, parts * part_floats * 4))) return st;
+    if ((st = check_buffer(ctx, "O|LSE", out_and_lse, lse_off + rows * 4))) return st;
+    const float *base = static_cast<const float *>(gathered.ptr);
+    return launch_splitkv_merge(ctx, dtype, (int)parts, (int64_t)rows, (int)head_dim, base, base + rows * head_dim,
+                                (int64_t)part_floats, (int64_t)part_floats, out_and_lse.ptr,
+                                reinterpret_cast<float *>(static_cast<char *>(out_and_lse.ptr) + lse_off));
 }
 
 int32_t flat_splitkv_merge(flat_ctx *ctx, int32_t dtype, uint64_t parts, uint64_t rows, uint64_t head_dim,
@@ -1156,7 +1207,7 @@ int32_t flat_splitkv_merge(flat_ctx *ctx, int32_t dtype, uint64_t parts, uint64_
     if ((st = check_buffer(ctx, "O|LSE", out_and_lse, lse_off + rows * 4))) return st;
     return launch_splitkv_merge(ctx, dtype, (int)parts, (int64_t)rows, (int)head_dim,
                                 static_cast<const float *>(partial_o.ptr), static_cast<const float *>(partial_lse.ptr),
-                                out_and_lse.ptr,
+                                (int64_t)(rows * head_dim), (int64_t)rows, out_and_lse.ptr,
                                 reinterpret_cast<float *>(static_cast<char *>(out_and_lse.ptr) + lse_off));
 }
 

@@ -146,6 +146,7 @@ struct DecodeParams {
     // sequences they belong to.  seq_offsets[s] is where sequence s starts (device, num_seqs+1
     // entries).  Partial slot of (sequence, CTA) = CTA index - first CTA touching the sequence;
     // kv_splits then holds the maximum number of slots per sequence.
+    int out_f32;                         // write the final O as f32 whatever the storage type (cross-GPU partials)
     int balanced;
     int span_tokens;
     int num_ctas;
@@ -157,8 +158,10 @@ int launch_decode(flat_ctx *ctx, int dtype, const DecodeParams &p);
 // bf16 tensor-core decode (mma.sync), head_dim 64/128, group <= 8, pages of a multiple of 16 tokens
 bool decode_mma_supported(int dtype, const DecodeParams &p);
 int launch_decode_mma(flat_ctx *ctx, const DecodeParams &p);
+// part i of the partial O / LSE starts part_stride_o / part_stride_lse floats after part i-1
 int launch_splitkv_merge(flat_ctx *ctx, int dtype, int parts, int64_t rows, int head_dim,
-                         const float *partial_o, const float *partial_lse, void *o, float *lse);
+                         const float *partial_o, const float *partial_lse, int64_t part_stride_o,
+                         int64_t part_stride_lse, void *o, float *lse);
 
 // ---- KV cache --------------------------------------------------------------------------------
 // Copies `rows` source rows of `row_elems` elements to destination rows dst_rows[i] (device

@@ -244,7 +244,8 @@ __global__ void __launch_bounds__(128) merge_kernel(int parts, int64_t rows, int
                                                     const float *__restrict__ partial_lse, T *__restrict__ o,
                                                     float *__restrict__ lse, const int32_t *context_lens,
                                                     int uniform_len, int chunk_tokens, int rows_per_seq,
-                                                    const int32_t *seq_offsets, int span_tokens) {
+                                                    const int32_t *seq_offsets, int span_tokens, int64_t stride_o,
+                                                    int64_t stride_lse) {
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (row >= rows) return;
@@ -259,19 +260,19 @@ __global__ void __launch_bounds__(128) merge_kernel(int parts, int64_t rows, int
         live = min(parts, (len + chunk_tokens - 1) / chunk_tokens);
     }
     float mx = -INFINITY;
-    for (int i = lane; i < live; i += 32) mx = fmaxf(mx, partial_lse[(int64_t)i * rows + row]);
+    for (int i = lane; i < live; i += 32) mx = fmaxf(mx, partial_lse[(int64_t)i * stride_lse + row]);
 #pragma unroll
     for (int w = 16; w >= 1; w >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, w));
     float sum = 0.f;
-    for (int i = lane; i < live; i += 32) sum += expf(partial_lse[(int64_t)i * rows + row] - mx);
+    for (int i = lane; i < live; i += 32) sum += expf(partial_lse[(int64_t)i * stride_lse + row] - mx);
 #pragma unroll
     for (int w = 16; w >= 1; w >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
     const float total = mx + logf(sum);
     for (int d = lane; d < head_dim; d += 32) {
         float acc = 0.f;
         for (int i = 0; i < live; ++i) {
-            float w = expf(partial_lse[(int64_t)i * rows + row] - total);
-            acc = fmaf(w, partial_o[((int64_t)i * rows + row) * head_dim + d], acc);
+            float w = expf(partial_lse[(int64_t)i * stride_lse + row] - total);
+            acc = fmaf(w, partial_o[(int64_t)i * stride_o + row * head_dim + d], acc);
         }
         if constexpr (sizeof(T) == 4) o[row * head_dim + d] = acc;
         else o[row * head_dim + d] = __float2bfloat16_rn(acc);
@@ -286,7 +287,8 @@ int merge_chunks(flat_ctx *ctx, const DecodeParams &p) {
     int blocks = (int)((rows + 3) / 4);
     merge_kernel<T><<<blocks, 128, 0, ctx->stream>>>(p.kv_splits, rows, p.head_dim, p.partial_o, p.partial_lse, (T *)p.o,
                                                       p.lse, p.context_lens, p.uniform_len, p.chunk_tokens, p.q_heads,
-                                                      p.balanced ? p.seq_offsets : nullptr, p.span_tokens);
+                                                      p.balanced ? p.seq_offsets : nullptr, p.span_tokens,
+                                                      rows * p.head_dim, rows);
     ctx->launches += 1;
     FLAT_CUDA_OK(ctx, cudaGetLastError());
     return FLAT_OK;
@@ -348,21 +350,24 @@ int launch_decode(flat_ctx *ctx, int dtype, const DecodeParams &p) {
         launch_decode_mma(ctx, p);
         ctx->launches += 1;
         FLAT_CUDA_OK(ctx, cudaGetLastError());
-        return merge_chunks<__nv_bfloat16>(ctx, p);
+        return p.out_f32 ? merge_chunks<float>(ctx, p) : merge_chunks<__nv_bfloat16>(ctx, p);
     }
+    if (p.out_f32 && dtype != FLAT_F32)
+        return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE, "f32 partial output needs the tensor-core decode shape (head_dim 64/128, group <= 8, pages of 16)");
     int st = dtype == FLAT_BF16 ? launch_t<__nv_bfloat16>(ctx, p) : launch_t<float>(ctx, p);
     return st;
 }
 
 int launch_splitkv_merge(flat_ctx *ctx, int dtype, int parts, int64_t rows, int head_dim, const float *partial_o,
-                         const float *partial_lse, void *o, float *lse) {
+                         const float *partial_lse, int64_t part_stride_o, int64_t part_stride_lse, void *o, float *lse) {
     int blocks = (int)((rows + 3) / 4);
     if (dtype == FLAT_BF16)
         merge_kernel<__nv_bfloat16><<<blocks, 128, 0, ctx->stream>>>(parts, rows, head_dim, partial_o, partial_lse,
-                                                                      (__nv_bfloat16 *)o, lse, nullptr, 0, 0, 1, nullptr, 0);
+                                                                      (__nv_bfloat16 *)o, lse, nullptr, 0, 0, 1, nullptr, 0, part_stride_o,
+                                                                      part_stride_lse);
     else
         merge_kernel<float><<<blocks, 128, 0, ctx->stream>>>(parts, rows, head_dim, partial_o, partial_lse, (float *)o,
-                                                             lse, nullptr, 0, 0, 1, nullptr, 0);
+                                                             lse, nullptr, 0, 0, 1, nullptr, 0, part_stride_o, part_stride_lse);
     ctx->launches += 1;
     FLAT_CUDA_OK(ctx, cudaGetLastError());
     return FLAT_OK;

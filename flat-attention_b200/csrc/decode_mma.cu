@@ -227,6 +227,12 @@ __device__ __forceinline__ void decode_range(const DecodeParams &p, int seq, int
             for (int e = 0; e < kDims; e += 4)
                 *reinterpret_cast<float4 *>(po + e) = make_float4(vals[e], vals[e + 1], vals[e + 2], vals[e + 3]);
             if (g == 0) p.partial_lse[(int64_t)split * p.num_seqs * p.q_heads + out_row] = lse;
+        } else if (p.out_f32) {
+            float *po = (float *)p.o + out_row * D + kDims * g;
+#pragma unroll
+            for (int e = 0; e < kDims; e += 4)
+                *reinterpret_cast<float4 *>(po + e) = make_float4(vals[e], vals[e + 1], vals[e + 2], vals[e + 3]);
+            if (g == 0) p.lse[out_row] = lse;
         } else {
             __nv_bfloat16 *op = (__nv_bfloat16 *)p.o + out_row * D + kDims * g;
 #pragma unroll

@@ -372,6 +372,28 @@ int32_t flat_decode_paged_batched(flat_ctx *ctx, int32_t dtype, uint64_t num_seq
                                   uint32_t kv_splits, flat_buffer q, flat_buffer k,
                                   flat_buffer v, flat_buffer out_and_lse);
 
+/* Per-GPU leg of single-sequence (or few-sequence) long-context decode split along KV across
+ * GPUs: this cache holds a slice of each sequence; the result is the slice's normalised O and
+ * LSE, both f32, packed [O(num_seqs*q_heads*head_dim) | LSE(num_seqs*q_heads)] - exactly the
+ * block a rank contributes to the all-gather.  q_rope_positions are global positions.  The
+ * reference never splits KV; there is no counterpart. */
+int32_t flat_decode_paged_batched_partial(flat_ctx *ctx, int32_t dtype, uint64_t num_seqs,
+                                          uint64_t q_heads, uint64_t kv_heads, uint64_t head_dim,
+                                          uint64_t page_size, uint64_t physical_pages,
+                                          uint64_t max_pages_per_seq, const int32_t *page_tables_dev,
+                                          const int32_t *context_lens_dev,
+                                          const int32_t *q_rope_positions_dev,
+                                          const int32_t *host_page_tables,
+                                          const int32_t *host_context_lens,
+                                          const flat_attention_config *config, float theta,
+                                          flat_buffer q, flat_buffer k, flat_buffer v,
+                                          flat_buffer partial_out_and_lse);
+
+/* Merge of `parts` such blocks laid end to end (the all-gather output): part i starts
+ * rows*(head_dim+1) floats after part i-1.  Output packed [O | LSE] in `dtype`. */
+int32_t flat_splitkv_merge_packed(flat_ctx *ctx, int32_t dtype, uint64_t parts, uint64_t rows,
+                                  uint64_t head_dim, flat_buffer gathered, flat_buffer out_and_lse);
+
 /* The same batched split-KV decode for callers that cannot allocate device memory when the
  * call is made (a latency-critical serving loop where an allocation would stall the device, a
  * plug-in under a framework allocator that forbids side allocations, or a process whose memory

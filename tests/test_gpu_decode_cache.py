@@ -336,3 +336,52 @@ def test_splitkv_merge_matches_unsplit():
     eo = (w[:, :, None] * po.double()).sum(0)
     assert_close("O", o, eo.float().numpy(), 1e-5, 1e-5)
     assert_close("LSE", l, tot.float().numpy(), 1e-5, 1e-5)
+
+
+@pytest.mark.parametrize("parts", [2, 8])
+def test_kv_split_across_ranks_emulated_on_one_gpu(parts):
+    """Single-sequence long-context decode split along KV: every 'rank' holds a contiguous page range
+    in its own cache slice, computes the f32 partial (O_i, LSE_i); the packed partials (the all-gather
+    output) are merged.  Result = unsplit decode = oracle."""
+    import importlib.util, os
+    spec = importlib.util.spec_from_file_location("fd", os.path.join(os.path.dirname(fa.__file__), "distributed.py"))
+    fd = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(fd)
+    c = ctx()
+    Hq, Hkv, D, ps, theta, n = 32, 8, 128, 16, 5e5, 16 * 515 + 7
+    g = torch.Generator().manual_seed(9)
+    K = torch.randn(n, Hkv * D, generator=g).bfloat16()
+    V = torch.randn(n, Hkv * D, generator=g).bfloat16()
+    Q = torch.randn(1, Hq * D, generator=g).bfloat16()
+    qpos = np.array([n - 1], np.int32)
+    blocks = []
+    for r in range(parts):
+        first, count = fd.shard_pages(n, ps, parts, r)
+        pages = (count + ps - 1) // ps
+        pool = pages + 3
+        perm = np.random.default_rng(r).permutation(pool).astype(np.int32)[:pages]
+        Kc, Vc = torch.zeros(pool * ps, Hkv * D, dtype=torch.bfloat16), torch.zeros(pool * ps, Hkv * D, dtype=torch.bfloat16)
+        for i in range(pages):
+            lo, hi = first + i * ps, min(first + count, first + (i + 1) * ps)
+            Kc[perm[i] * ps:perm[i] * ps + hi - lo] = K[lo:hi]
+            Vc[perm[i] * ps:perm[i] * ps + hi - lo] = V[lo:hi]
+        lens = np.array([count], np.int32)
+        tab = perm.reshape(1, pages)
+        out = torch.empty(Hq * (D + 1), dtype=torch.float32, device="cuda")
+        c.decode_paged_batched_partial(fa.BF16, 1, Hq, Hkv, D, ps, pool, pages, torch.from_numpy(tab).cuda(),
+                                       torch.from_numpy(lens).cuda(), torch.from_numpy(qpos).cuda(), tab, lens,
+                                       fa.config(True), theta, Q.cuda(), Kc.cuda(), Vc.cuda(), out)
+        blocks.append(out)
+    gathered = torch.stack(blocks)
+    final = c.empty_bytes(Hq * D * 2 + Hq * 4)
+    c.splitkv_merge_packed(fa.BF16, parts, Hq, D, gathered, final)
+    o, l = unpack(final, fa.BF16, Hq, D)
+    eo, el = oracle_decode(Q[0].float().numpy(), K.float().numpy(), V.float().numpy(), Hq, Hkv, D, theta, n - 1, 0, True)
+    assert_close("O", o, eo, 2e-2, 0.0)
+    assert_close("LSE", l, el, 2e-3, 0.0)
+    # the reference merge formula on the same partials
+    po = gathered[:, :Hq * D].reshape(parts, Hq, D).cpu()
+    pl = gathered[:, Hq * D:].cpu()
+    mo, ml = fd.merge_partials_reference(po, pl)
+    assert_close("merge O", o, mo.numpy(), 8e-3, 0.0)
+    assert_close("merge LSE", l, ml.numpy(), 1e-5, 0.0)
