@@ -325,6 +325,59 @@ def bench_chunked_prefill(torch, fa, ctx, peaks, warmup):
                         "into the cache append (K) and into the attention kernel (Q)"}
 
 
+def bench_splitkv_128k(torch, np, dist, fa, ctx, rank, world, steps, warmup):
+    """Config 4 (decode part): one 131072-token sequence, KV axis split across the ranks; every rank
+    decodes its slice, the (O, LSE) partials are all-gathered over NCCL and merged on every rank."""
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("flat_distributed", os.path.join(ROOT, "flat-attention_b200", "distributed.py"))
+    fd = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(fd)
+    Hq, Hkv, D, ps, theta, n = 64, 8, 128, 16, 500000.0, 131072
+    first, count = fd.shard_pages(n, ps, world, rank)
+    pages = count // ps
+    g = torch.Generator(device="cuda").manual_seed(100 + rank)
+    K = torch.randn(pages * ps, Hkv * D, generator=g, device="cuda").bfloat16()
+    V = torch.randn(pages * ps, Hkv * D, generator=g, device="cuda").bfloat16()
+    Q = torch.randn(1, Hq * D, generator=torch.Generator(device="cuda").manual_seed(99), device="cuda").bfloat16()
+    tab = np.random.default_rng(rank).permutation(pages).astype(np.int32).reshape(1, pages)
+    lens, qpos = np.array([count], np.int32), np.array([n - 1], np.int32)
+    args = dict(num_seqs=1, q_heads=Hq, kv_heads=Hkv, head_dim=D, page_size=ps, physical_pages=pages, max_pages_per_seq=pages,
+                page_tables_dev=torch.from_numpy(tab).cuda(), context_lens_dev=torch.from_numpy(lens).cuda(),
+                q_rope_positions_dev=torch.from_numpy(qpos).cuda(), host_page_tables=None, host_context_lens=lens,
+                cfg=fa.config(True), theta=theta, q=Q, k=K, v=V)
+    out = ctx.empty_bytes(Hq * D * 2 + Hq * 4)
+    partial = torch.empty(Hq * (D + 1), dtype=torch.float32, device="cuda")
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def step():
+        return fd.splitkv_decode(ctx, fa, fa.BF16, args, Hq, D, out)
+    for _ in range(warmup):
+        step()
+    tot, tot_merge = 0.0, 0.0
+    for _ in range(steps):
+        flush.zero_()
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record()
+        ctx.decode_paged_batched_partial(fa.BF16, out=partial, **args)
+        e1.record()
+        gathered = fd.all_gather_partials(partial)
+        ctx.splitkv_merge_packed(fa.BF16, world, Hq, D, gathered, out)
+        e2.record()
+        torch.cuda.synchronize()
+        tot += e0.elapsed_time(e2)
+        tot_merge += e1.elapsed_time(e2)
+    t = torch.tensor([tot / steps, tot_merge / steps], device="cuda", dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, ms_merge = float(t[0]), float(t[1])
+    kv_bytes = n * Hkv * D * 2 * 2
+    return {"metric": "splitkv_decode_128k", "ms_per_step": ms, "gather_merge_ms": ms_merge,
+            "aggregate_kv_gbs": kv_bytes / (ms * 1e-3) / 1e9, "per_gpu_kv_gbs": kv_bytes / world / ((ms - ms_merge) * 1e-3) / 1e9,
+            "kv_bytes_total": kv_bytes, "gathered_bytes": world * Hq * (D + 1) * 4,
+            "workload": "1 sequence x 131072 tokens, Hq=64 Hkv=8 D=128 bf16, page 16, KV split over %d GPUs, NCCL all-gather" % world}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -452,6 +505,9 @@ def main():
             line["decode"] = bench_decode(torch, np, fa, ctx, peaks, max(5, min(args.steps, 20)), args.warmup)
             line["backward"] = bench_backward(torch, fa, ctx, peaks, max(3, min(args.steps, 10)), args.warmup)
             line["chunked_prefill"] = bench_chunked_prefill(torch, fa, ctx, peaks, args.warmup)
+    if world > 1 and not args.skip_extras:
+        extra = bench_splitkv_128k(torch, np, dist, fa, ctx, rank, world, max(5, min(args.steps, 20)), args.warmup)
+        line["splitkv_decode_128k"] = extra
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

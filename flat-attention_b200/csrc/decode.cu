@@ -235,23 +235,29 @@ __global__ void __launch_bounds__(256) decode_kernel(const __grid_constant__ Dec
     }
 }
 
-// Merge of split-KV partials: one warp per (sequence, q_head) row.
+// Merge of split-KV partials: one CTA of 128 threads per (sequence, q_head) row.
 //   LSE = log(sum_i exp(LSE_i)),  O = sum_i exp(LSE_i - LSE) O_i
-// parts_for_row: when context_lens is given, only ceil(ctx/chunk) parts of a row are live.
+// Phase 1: the threads reduce max and sum of the parts' LSE; phase 2: thread d accumulates column d
+// over the parts with the weights staged in shared memory (coalesced rows, several loads in flight).
+// Fixed-chunk mode: only ceil(ctx/chunk) parts of a row are live.  Balanced mode: one slot per CTA that
+// touched the sequence; a single slot was already written as the final result.
+constexpr int kMergeThreads = 128;
+constexpr int kMergeBatch = 512;  // weights staged per pass
+
 template <typename T>
-__global__ void __launch_bounds__(128) merge_kernel(int parts, int64_t rows, int head_dim,
-                                                    const float *__restrict__ partial_o,
-                                                    const float *__restrict__ partial_lse, T *__restrict__ o,
-                                                    float *__restrict__ lse, const int32_t *context_lens,
-                                                    int uniform_len, int chunk_tokens, int rows_per_seq,
-                                                    const int32_t *seq_offsets, int span_tokens, int64_t stride_o,
-                                                    int64_t stride_lse) {
-    const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-    if (row >= rows) return;
+__global__ void __launch_bounds__(kMergeThreads) merge_kernel(int parts, int64_t rows, int head_dim,
+                                                              const float *__restrict__ partial_o,
+                                                              const float *__restrict__ partial_lse, T *__restrict__ o,
+                                                              float *__restrict__ lse, const int32_t *context_lens,
+                                                              int uniform_len, int chunk_tokens, int rows_per_seq,
+                                                              const int32_t *seq_offsets, int span_tokens, int64_t stride_o,
+                                                              int64_t stride_lse) {
+    __shared__ float w_s[kMergeBatch];
+    __shared__ float red[kMergeThreads / 32];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int64_t row = blockIdx.x;
     int live = parts;
     if (seq_offsets) {
-        // balanced mode: one slot per CTA that touched the sequence; a single slot was written as the final result
         const int seq = (int)(row / rows_per_seq);
         live = (seq_offsets[seq + 1] - 1) / span_tokens - seq_offsets[seq] / span_tokens + 1;
         if (live <= 1) return;
@@ -259,33 +265,59 @@ __global__ void __launch_bounds__(128) merge_kernel(int parts, int64_t rows, int
         int len = context_lens ? context_lens[row / rows_per_seq] : uniform_len;
         live = min(parts, (len + chunk_tokens - 1) / chunk_tokens);
     }
-    float mx = -INFINITY;
-    for (int i = lane; i < live; i += 32) mx = fmaxf(mx, partial_lse[(int64_t)i * stride_lse + row]);
+    auto block_reduce = [&](float x, bool is_max) {
 #pragma unroll
-    for (int w = 16; w >= 1; w >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, w));
-    float sum = 0.f;
-    for (int i = lane; i < live; i += 32) sum += expf(partial_lse[(int64_t)i * stride_lse + row] - mx);
-#pragma unroll
-    for (int w = 16; w >= 1; w >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, w);
-    const float total = mx + logf(sum);
-    for (int d = lane; d < head_dim; d += 32) {
-        float acc = 0.f;
-        for (int i = 0; i < live; ++i) {
-            float w = expf(partial_lse[(int64_t)i * stride_lse + row] - total);
-            acc = fmaf(w, partial_o[(int64_t)i * stride_o + row * head_dim + d], acc);
+        for (int s = 16; s >= 1; s >>= 1) {
+            const float y = __shfl_xor_sync(0xffffffffu, x, s);
+            x = is_max ? fmaxf(x, y) : x + y;
         }
-        if constexpr (sizeof(T) == 4) o[row * head_dim + d] = acc;
-        else o[row * head_dim + d] = __float2bfloat16_rn(acc);
+        __syncthreads();
+        if (lane == 0) red[warp] = x;
+        __syncthreads();
+        float r = red[0];
+        for (int i = 1; i < kMergeThreads / 32; ++i) r = is_max ? fmaxf(r, red[i]) : r + red[i];
+        return r;
+    };
+    float mx = -INFINITY;
+    for (int i = tid; i < live; i += kMergeThreads) mx = fmaxf(mx, partial_lse[(int64_t)i * stride_lse + row]);
+    mx = block_reduce(mx, true);
+    float sum = 0.f;
+    for (int i = tid; i < live; i += kMergeThreads) sum += expf(partial_lse[(int64_t)i * stride_lse + row] - mx);
+    sum = block_reduce(sum, false);
+    const float total = mx + logf(sum);
+    float acc = 0.f;
+    for (int base = 0; base < live; base += kMergeBatch) {
+        const int n = min(kMergeBatch, live - base);
+        __syncthreads();
+        for (int i = tid; i < n; i += kMergeThreads) w_s[i] = expf(partial_lse[(int64_t)(base + i) * stride_lse + row] - total);
+        __syncthreads();
+        if (tid < head_dim) {
+            const float *src = partial_o + (int64_t)base * stride_o + row * head_dim + tid;
+            int i = 0;
+            for (; i + 4 <= n; i += 4) {
+                const float a0 = src[(int64_t)(i + 0) * stride_o], a1 = src[(int64_t)(i + 1) * stride_o];
+                const float a2 = src[(int64_t)(i + 2) * stride_o], a3 = src[(int64_t)(i + 3) * stride_o];
+                acc = fmaf(w_s[i], a0, acc);
+                acc = fmaf(w_s[i + 1], a1, acc);
+                acc = fmaf(w_s[i + 2], a2, acc);
+                acc = fmaf(w_s[i + 3], a3, acc);
+            }
+            for (; i < n; ++i) acc = fmaf(w_s[i], src[(int64_t)i * stride_o], acc);
+        }
     }
-    if (lane == 0) lse[row] = total;
+    if (tid < head_dim) {
+        if constexpr (sizeof(T) == 4) o[row * head_dim + tid] = acc;
+        else o[row * head_dim + tid] = __float2bfloat16_rn(acc);
+    }
+    if (tid == 0) lse[row] = total;
 }
 
 template <typename T>
 int merge_chunks(flat_ctx *ctx, const DecodeParams &p) {
     if (p.kv_splits <= 1) return FLAT_OK;
     int64_t rows = (int64_t)p.num_seqs * p.q_heads;
-    int blocks = (int)((rows + 3) / 4);
-    merge_kernel<T><<<blocks, 128, 0, ctx->stream>>>(p.kv_splits, rows, p.head_dim, p.partial_o, p.partial_lse, (T *)p.o,
+    int blocks = (int)rows;
+    merge_kernel<T><<<blocks, kMergeThreads, 0, ctx->stream>>>(p.kv_splits, rows, p.head_dim, p.partial_o, p.partial_lse, (T *)p.o,
                                                       p.lse, p.context_lens, p.uniform_len, p.chunk_tokens, p.q_heads,
                                                       p.balanced ? p.seq_offsets : nullptr, p.span_tokens,
                                                       rows * p.head_dim, rows);
@@ -360,13 +392,13 @@ int launch_decode(flat_ctx *ctx, int dtype, const DecodeParams &p) {
 
 int launch_splitkv_merge(flat_ctx *ctx, int dtype, int parts, int64_t rows, int head_dim, const float *partial_o,
                          const float *partial_lse, int64_t part_stride_o, int64_t part_stride_lse, void *o, float *lse) {
-    int blocks = (int)((rows + 3) / 4);
+    int blocks = (int)rows;
     if (dtype == FLAT_BF16)
-        merge_kernel<__nv_bfloat16><<<blocks, 128, 0, ctx->stream>>>(parts, rows, head_dim, partial_o, partial_lse,
+        merge_kernel<__nv_bfloat16><<<blocks, kMergeThreads, 0, ctx->stream>>>(parts, rows, head_dim, partial_o, partial_lse,
                                                                       (__nv_bfloat16 *)o, lse, nullptr, 0, 0, 1, nullptr, 0, part_stride_o,
                                                                       part_stride_lse);
     else
-        merge_kernel<float><<<blocks, 128, 0, ctx->stream>>>(parts, rows, head_dim, partial_o, partial_lse, (float *)o,
+        merge_kernel<float><<<blocks, kMergeThreads, 0, ctx->stream>>>(parts, rows, head_dim, partial_o, partial_lse, (float *)o,
                                                              lse, nullptr, 0, 0, 1, nullptr, 0, part_stride_o, part_stride_lse);
     ctx->launches += 1;
     FLAT_CUDA_OK(ctx, cudaGetLastError());
