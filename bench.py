@@ -426,10 +426,8 @@ def main():
         ctx.forward_grouped_rope(fa.BF16, shp, cfg, rot, dq, dk, dv, out)
 
     def step_e2e():
-        a, b_, c_ = hq.cuda(non_blocking=True), hk.cuda(non_blocking=True), hv.cuda(non_blocking=True)
-        ctx.forward_grouped_rope(fa.BF16, shp, cfg, rot, a, b_, c_, out)
-        host_out.copy_(out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()  # the caller reads the result
+        # the public host-slice call: pinned host Q/K/V in, pinned host [O | LSE] out, blocks until the result is readable
+        ctx.forward_host(fa.BF16, fa.HEAD_MAJOR, shp, cfg, rot, hq, hk, hv, host_out)
 
     for _ in range(args.warmup):
         step()

@@ -296,6 +296,14 @@ class Context:
                                                              C.byref(rot), arr, C.c_uint64(len(sequences)), buf(q),
                                                              buf(k), buf(v), buf(out)))
 
+    def forward_host(self, dtype, layout, shp, cfg, rot, q, k, v, out, check_finite=False):
+        """Host tensors in (torch CPU, ideally pinned), host packed [O | LSE] out; blocks."""
+        self.check(lib().flat_forward_host(self.h, C.c_int32(dtype), C.c_int32(layout), C.byref(shp), C.byref(cfg),
+                                           C.byref(rot) if rot is not None else None, C.c_void_p(q.data_ptr()),
+                                           C.c_uint64(q.numel()), C.c_void_p(k.data_ptr()), C.c_uint64(k.numel()),
+                                           C.c_void_p(v.data_ptr()), C.c_uint64(v.numel()), C.c_int32(int(check_finite)),
+                                           C.c_void_p(out.data_ptr()), C.c_uint64(out.numel() * out.element_size())))
+
     def decode_resident(self, dtype, batch, q_heads, kv_heads, head_dim, kv_len, kv_capacity, cfg, theta,
                         q_rope_position, q, k, v, out):
         self.check(lib().flat_decode_resident(self.h, C.c_int32(dtype), C.c_uint64(batch), C.c_uint64(q_heads),
@@ -594,9 +602,18 @@ class CudaFlatAttention:
 
     def forward(self, q, k, v, shp: Shape, cfg: Config, rot: Optional[Rotary] = None,
                 layout: int = HEAD_MAJOR) -> FlatAttentionOutput:
-        dq, dk, dv = self.upload(q), self.upload(k), self.upload(v)
-        out = self.forward_resident(dq, dk, dv, shp, cfg, rot, layout)
-        return self.download_attention(out, shp, layout)
+        """Host slices in, host result out, inputs validated like the reference's validate_input."""
+        torch = _torch()
+        td = torch_dtype(self.dtype)
+        hq, hk, hv = (torch.as_tensor(x).to(td).contiguous().reshape(-1) for x in (q, k, v))
+        L = forward_layout(self.dtype, shp)
+        out = torch.empty(L.combined_bytes, dtype=torch.uint8)
+        self.ctx.forward_host(self.dtype, layout, shp, cfg, rot, hq, hk, hv, out, check_finite=True)
+        o = out[:L.q_bytes].view(td)
+        lse = out[L.lse_byte_offset:L.lse_byte_offset + 4 * L.lse_elements].view(torch.float32)
+        B, Hq, Nq, D = shp.batch, shp.q_heads, shp.query_len, shp.head_dim
+        o = o.view(B, Hq, Nq, D) if layout == HEAD_MAJOR else o.view(B * Nq, Hq * D)
+        return FlatAttentionOutput(o, lse.view(B, Hq, Nq))
 
 
 def exported_symbols_in_header() -> list[str]:

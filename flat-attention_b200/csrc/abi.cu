@@ -267,6 +267,9 @@ int table_init(flat_paged_kv_table *t, uint64_t page_size, uint64_t physical_pag
     if (page_size == 0 || physical_pages == 0) return FLAT_ERR_ZERO_DIMENSION;
     uint64_t cap;
     if (!mul_ok(page_size, physical_pages, &cap)) return FLAT_ERR_CAPACITY_OVERFLOW;
+    // the free list is materialised and device page tables hold int32 entries: pools beyond 2^28 pages
+    // (far more than 180 GB of HBM can back) are refused instead of being allocated
+    if (physical_pages > (uint64_t(1) << 28)) return FLAT_ERR_CAPACITY_OVERFLOW;
     t->page_size = page_size;
     t->physical_pages = physical_pages;
     t->free_pages.clear();
@@ -488,6 +491,7 @@ void flat_ctx_destroy(flat_ctx *ctx) {
         cudaEventDestroy(pr.second);
     }
     if (ctx->workspace) cudaFree(ctx->workspace);
+    if (ctx->host_stage) cudaFree(ctx->host_stage);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     delete ctx;
 }
@@ -678,6 +682,79 @@ int32_t flat_forward_projection_rope_varlen(flat_ctx *ctx, int32_t dtype, const 
                                             flat_buffer q, flat_buffer k, flat_buffer v, flat_buffer out_and_lse) {
     ForwardCall c{dtype, FLAT_LAYOUT_PROJECTION, true, rotary, sequences, sequence_count, true};
     return forward_common(ctx, c, shape, config, q, k, v, out_and_lse);
+}
+
+// validate_input (src/lib.rs:428-447): exact length, then the first non-finite element
+static int validate_host_tensor(flat_ctx *ctx, const char *name, int dtype, const void *data, uint64_t actual,
+                                uint64_t expected, int check_finite) {
+    if (!data) return fail(ctx, FLAT_ERR_NULL_POINTER, "%s is null", name);
+    if (actual != expected)
+        return fail(ctx, FLAT_ERR_LENGTH_MISMATCH, "tensor %s contains %llu elements, expected %llu", name,
+                    (unsigned long long)actual, (unsigned long long)expected);
+    if (!check_finite) return FLAT_OK;
+    if (dtype == FLAT_F32) {
+        const uint32_t *p = static_cast<const uint32_t *>(data);
+        for (uint64_t i = 0; i < actual; ++i)
+            if ((p[i] & 0x7f800000u) == 0x7f800000u)
+                return fail(ctx, FLAT_ERR_NON_FINITE_INPUT, "tensor %s contains a non-finite value at index %llu", name,
+                            (unsigned long long)i);
+    } else {
+        const uint16_t *p = static_cast<const uint16_t *>(data);
+        for (uint64_t i = 0; i < actual; ++i)
+            if ((p[i] & 0x7f80u) == 0x7f80u)
+                return fail(ctx, FLAT_ERR_NON_FINITE_INPUT, "tensor %s contains a non-finite value at index %llu", name,
+                            (unsigned long long)i);
+    }
+    return FLAT_OK;
+}
+
+int32_t flat_forward_host(flat_ctx *ctx, int32_t dtype, int32_t layout, const flat_attention_shape *shape,
+                          const flat_attention_config *config, const flat_rotary_config *rotary, const void *q,
+                          uint64_t q_elements, const void *k, uint64_t k_elements, const void *v, uint64_t v_elements,
+                          int32_t check_finite, void *out_and_lse, uint64_t out_bytes) {
+    if (!ctx) return FLAT_ERR_NULL_POINTER;
+    int st;
+    if ((st = check_dtype(ctx, dtype))) return st;
+    if (layout != FLAT_LAYOUT_HEAD_MAJOR && layout != FLAT_LAYOUT_PROJECTION)
+        return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE, "unknown layout %d", layout);
+    Dims d;
+    if ((st = validate_shape(ctx, shape, &d))) return st;
+    if (rotary) {
+        if ((st = validate_rotary(ctx, rotary->theta, rotary->query_position_offset, shape->head_dim, shape->query_len))) return st;
+        if ((st = validate_rotary(ctx, rotary->theta, rotary->kv_position_offset, shape->head_dim, shape->kv_len))) return st;
+    }
+    if ((st = validate_host_tensor(ctx, "Q", dtype, q, q_elements, d.q_elements, check_finite))) return st;
+    if ((st = validate_host_tensor(ctx, "K", dtype, k, k_elements, d.kv_elements, check_finite))) return st;
+    if ((st = validate_host_tensor(ctx, "V", dtype, v, v_elements, d.kv_elements, check_finite))) return st;
+    float scale;
+    if ((st = resolve_scale(ctx, config, shape->head_dim, &scale))) return st;
+    const uint64_t es = dtype_size(dtype);
+    const uint64_t combined = lse_offset_bytes(dtype, d.q_elements) + d.lse_elements * 4;
+    if (!out_and_lse) return fail(ctx, FLAT_ERR_NULL_POINTER, "output is null");
+    if (out_bytes < combined)
+        return fail(ctx, FLAT_ERR_BUFFER_TOO_SMALL, "O|LSE buffer has %llu bytes, requires %llu", (unsigned long long)out_bytes,
+                    (unsigned long long)combined);
+    auto up = [](uint64_t x) { return (x + 255) & ~uint64_t(255); };
+    const uint64_t qb = up(d.q_elements * es), kb = up(d.kv_elements * es), ob = up(combined);
+    const uint64_t need = qb + 2 * kb + ob;
+    if (need > ctx->host_stage_bytes) {
+        FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+        if (ctx->host_stage) FLAT_CUDA_OK(ctx, cudaFree(ctx->host_stage));
+        ctx->host_stage = nullptr;
+        ctx->host_stage_bytes = 0;
+        FLAT_CUDA_OK(ctx, cudaMalloc(&ctx->host_stage, need));
+        ctx->host_stage_bytes = need;
+    }
+    char *base = static_cast<char *>(ctx->host_stage);
+    flat_buffer dq{base, qb}, dk{base + qb, kb}, dv{base + qb + kb, kb}, dout{base + qb + 2 * kb, ob};
+    FLAT_CUDA_OK(ctx, cudaMemcpyAsync(dq.ptr, q, d.q_elements * es, cudaMemcpyHostToDevice, ctx->stream));
+    FLAT_CUDA_OK(ctx, cudaMemcpyAsync(dk.ptr, k, d.kv_elements * es, cudaMemcpyHostToDevice, ctx->stream));
+    FLAT_CUDA_OK(ctx, cudaMemcpyAsync(dv.ptr, v, d.kv_elements * es, cudaMemcpyHostToDevice, ctx->stream));
+    ForwardCall c{dtype, layout, rotary != nullptr, rotary, nullptr, 0, false};
+    if ((st = forward_common(ctx, c, shape, config, dq, dk, dv, dout))) return st;
+    FLAT_CUDA_OK(ctx, cudaMemcpyAsync(out_and_lse, dout.ptr, combined, cudaMemcpyDeviceToHost, ctx->stream));
+    FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    return FLAT_OK;
 }
 
 // ---- paged-KV metadata -----------------------------------------------------------------------

@@ -36,6 +36,8 @@ struct flat_ctx {
     flat::DeviceStatus *dev_status = nullptr;  // device memory
     uint64_t launches = 0;
     std::string detail;
+    void *host_stage = nullptr;       // device staging of the host-slice entry points (Q | K | V | O|LSE)
+    uint64_t host_stage_bytes = 0;
     // optional timing of the dominant kernel of each call (CUDA events on the launch stream)
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;

@@ -269,6 +269,19 @@ int32_t flat_forward_projection_rope_varlen(flat_ctx *ctx, int32_t dtype,
                                             flat_buffer k, flat_buffer v,
                                             flat_buffer out_and_lse);
 
+/* WgpuFlatAttention::forward / WgpuGroupedAttention::forward / WgpuRotaryGroupedAttention::forward
+ * (src/wgpu_backend.rs:445-463, src/wgpu_grouped_backend.rs:126-146,
+ * src/wgpu_rotary_grouped_backend.rs:117-139): host slices in, host [O | LSE] out.  Validates
+ * like validate_input (src/lib.rs:428-447: exact element counts, and with check_finite != 0 the
+ * first non-finite element by tensor name and index), uploads into staging owned by the context,
+ * launches the forward of `layout` (with RoPE when rotary != NULL, rectangular shapes allowed),
+ * downloads and blocks.  Pinned host memory makes the copies asynchronous to the host. */
+int32_t flat_forward_host(flat_ctx *ctx, int32_t dtype, int32_t layout, const flat_attention_shape *shape,
+                          const flat_attention_config *config, const flat_rotary_config *rotary,
+                          const void *q, uint64_t q_elements, const void *k, uint64_t k_elements,
+                          const void *v, uint64_t v_elements, int32_t check_finite,
+                          void *out_and_lse, uint64_t out_bytes);
+
 /* ---- paged-KV metadata (host only) --------------------------------------------------- */
 
 /* PagedKvTable::new / append / address / telemetry / reset (src/paged_kv.rs:84-188). */

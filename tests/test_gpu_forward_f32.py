@@ -240,3 +240,32 @@ def test_owning_executor_forward_host_to_host():
     eo, el = ob.forward_reference(q, k, v, B, H, N, D, True)
     assert_close("O", r.output.numpy(), eo, *O_TOL)
     assert_close("LSE", r.lse.numpy(), el, *LSE_TOL)
+
+
+def test_host_slice_forward_validates_like_validate_input():
+    # src/lib.rs:428-447 through the host-slice entry point: exact lengths, first non-finite index by tensor name
+    c = ctx()
+    B, H, N, D = 1, 2, 9, 8
+    shp = fa.shape(B, H, H, N, N, D)
+    q, k, v = (torch.as_tensor(ramp(B * H * N * D, ph)) for ph in (0.1, 0.7, 1.3))
+    out = torch.empty(fa.forward_layout(fa.F32, shp).combined_bytes, dtype=torch.uint8)
+    c.forward_host(fa.F32, fa.HEAD_MAJOR, shp, fa.config(True), None, q, k, v, out, check_finite=True)
+    eo, el = ob.forward_reference(q.numpy(), k.numpy(), v.numpy(), B, H, N, D, True)
+    assert_close("O", out[:4 * q.numel()].view(torch.float32).numpy(), eo, *O_TOL)
+    assert_close("LSE", out[4 * q.numel():].view(torch.float32).numpy(), el, *LSE_TOL)
+    with pytest.raises(fa.FlatAttentionError) as e:
+        c.forward_host(fa.F32, fa.HEAD_MAJOR, shp, fa.config(True), None, q, k[:-1], v, out, check_finite=True)
+    assert e.value.kind == "LengthMismatch" and "K" in e.value.detail and str(k.numel() - 1) in e.value.detail
+    bad = v.clone()
+    bad[5] = float("inf")
+    with pytest.raises(fa.FlatAttentionError) as e:
+        c.forward_host(fa.F32, fa.HEAD_MAJOR, shp, fa.config(True), None, q, k, bad, out, check_finite=True)
+    assert e.value.kind == "NonFiniteInput" and "V" in e.value.detail and "index 5" in e.value.detail
+    badb = q.bfloat16()
+    badb[3] = float("nan")
+    with pytest.raises(fa.FlatAttentionError) as e:
+        c.forward_host(fa.BF16, fa.HEAD_MAJOR, shp, fa.config(True), None, badb, k.bfloat16(), v.bfloat16(), out, check_finite=True)
+    assert e.value.kind == "NonFiniteInput" and "Q" in e.value.detail and "index 3" in e.value.detail
+    with pytest.raises(fa.FlatAttentionError) as e:
+        c.forward_host(fa.F32, fa.HEAD_MAJOR, shp, fa.config(True), None, q, k, v, out[:-1], check_finite=True)
+    assert e.value.kind == "BufferTooSmall"

@@ -1,0 +1,121 @@
+"""Host-API fuzz in the spirit of tests/m39_host_api_fuzz.rs:54-188: 4096 xorshift cases of hostile
+shapes through the pure C-ABI functions; nothing may crash, every outcome is a typed status, and the
+status agrees with an independent big-integer model of the validation rules (src/api.rs:36-59)."""
+import ctypes as C
+
+from __graft_entry__ import load_package
+
+fa = load_package()
+U64 = (1 << 64) - 1
+
+
+class XorShift:
+    def __init__(self, seed):
+        self.s = seed
+
+    def next(self):
+        x = self.s
+        x ^= (x << 13) & U64
+        x ^= x >> 7
+        x ^= (x << 17) & U64
+        self.s = x
+        return x
+
+
+def hostile(rng):
+    r = rng.next() % 10
+    if r == 0:
+        return 0
+    if r == 1:
+        return U64
+    if r == 2:
+        return (1 << 32) + rng.next() % 5
+    if r == 3:
+        return (1 << 63) + rng.next() % 3
+    if r == 4:
+        return (1 << 31) - 1 + rng.next() % 3
+    if r == 5:
+        return 1 + rng.next() % 5000
+    return 1 + rng.next() % 130
+
+
+def model(b, hq, hkv, nq, nkv, d, off):
+    """Expected status of flat_forward_layout_for."""
+    if 0 in (b, hq, hkv, nq, nkv, d):
+        return "ZeroDimension"
+    if hq % hkv:
+        return "InvalidHeadGrouping"
+    lse = b * hq * nq
+    if lse > U64 or lse * d > U64 or b * hkv * nkv * d > U64:
+        return "ShapeOverflow"
+    if off + nq - 1 > U64:
+        return "PositionOverflow"
+    if d > 128:
+        return "UnsupportedHeadDim"
+    lim = (1 << 31) - 1
+    if b > lim or hq > lim or nq > lim or nkv > lim or off + nq - 1 > lim or lse * d > 1 << 46 or b * hkv * nkv * d > 1 << 46:
+        return "IndexSpaceExceeded"
+    return "OK"
+
+
+def test_layout_functions_never_crash_and_match_the_model():
+    rng = XorShift(0x39F0_5EED_1234_ABCD)
+    lib = fa.lib()
+    seen = set()
+    for _ in range(4096):
+        dims = [hostile(rng) for _ in range(6)]
+        off = hostile(rng) if rng.next() % 4 == 0 else rng.next() % 1000
+        shp = fa.Shape(*dims, off)
+        out = fa.ForwardLayout()
+        st = lib.flat_forward_layout_for(C.c_int32(rng.next() % 2), C.byref(shp), C.byref(out))
+        kind = fa.STATUS.get(st)
+        assert kind is not None, st
+        assert kind == model(*dims, off), (dims, off, kind)
+        seen.add(kind)
+        bl = fa.BackwardLayout()
+        st2 = lib.flat_backward_layout_for(C.c_int32(rng.next() % 2), C.byref(shp), C.byref(bl))
+        assert st2 in fa.STATUS
+        if st == 0:
+            es = 4
+            assert out.q_elements == dims[0] * dims[1] * dims[3] * dims[5]
+            assert out.kv_elements == dims[0] * dims[2] * dims[4] * dims[5]
+            assert out.combined_bytes >= out.lse_byte_offset + 4 * out.lse_elements
+    assert {"OK", "ZeroDimension", "InvalidHeadGrouping", "ShapeOverflow"} <= seen
+    assert lib.flat_forward_layout_for(C.c_int32(0), C.byref(fa.shape(1, 2, 1, 3, 3, 130)), C.byref(fa.ForwardLayout())) == 20
+    assert lib.flat_forward_layout_for(C.c_int32(7), C.byref(fa.shape(1, 1, 1, 1, 1, 2)), C.byref(fa.ForwardLayout())) == 26
+    assert lib.flat_forward_layout_for(C.c_int32(0), None, C.byref(fa.ForwardLayout())) == 27
+
+
+def test_paged_table_fuzz_never_crashes():
+    rng = XorShift(0x1357_9BDF_2468_ACE0)
+    lib = fa.lib()
+    for _ in range(512):
+        ps, pages = hostile(rng), hostile(rng)
+        h = C.c_void_p()
+        st = lib.flat_paged_kv_table_create(C.c_uint64(ps), C.c_uint64(pages), C.byref(h))
+        assert st in fa.STATUS
+        if pages > 1 << 28:
+            assert st in (1, 40)   # ZeroDimension (page_size 0) or CapacityOverflow: refused, never allocated
+        if st:
+            continue
+        for _ in range(8):
+            st = lib.flat_paged_kv_table_append(h, C.c_uint64(hostile(rng)))
+            assert st in fa.STATUS
+            addr = fa.PagedKvAddress()
+            st = lib.flat_paged_kv_table_address(h, C.c_uint64(hostile(rng)), C.byref(addr))
+            assert st in (0, 34)
+            tel = fa.PagedKvTelemetry()
+            assert lib.flat_paged_kv_table_telemetry(h, C.byref(tel)) == 0
+            assert tel.live_tokens <= tel.capacity_tokens and tel.mapped_pages + tel.free_pages == pages
+        lib.flat_paged_kv_table_destroy(h)
+
+
+def test_null_context_is_an_error_not_a_crash():
+    lib = fa.lib()
+    z = fa.Buffer(None, 0)
+    shp, cfg = fa.shape(1, 1, 1, 1, 1, 2), fa.config()
+    assert lib.flat_forward_grouped(None, C.c_int32(0), C.byref(shp), C.byref(cfg), z, z, z, z) == 27
+    assert lib.flat_backward_grouped(None, C.c_int32(0), C.byref(shp), C.byref(cfg), z, z) == 27
+    assert lib.flat_synchronize(None) == 27
+    assert lib.flat_forward_host(None, C.c_int32(0), C.c_int32(0), C.byref(shp), C.byref(cfg), None, None, C.c_uint64(0), None,
+                                 C.c_uint64(0), None, C.c_uint64(0), C.c_int32(1), None, C.c_uint64(0)) == 27
