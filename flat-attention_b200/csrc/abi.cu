@@ -130,9 +130,15 @@ struct ForwardCall {
     bool varlen;
 };
 
+int launch_forward(flat_ctx *ctx, int dtype, const FwdParams &p) {
+    if (dtype == FLAT_BF16 && forward_sm100_supported(p)) return launch_forward_sm100(ctx, p);
+    return launch_forward_simt(ctx, dtype, p);
+}
+
+// Validates the call and builds the kernel parameters; launches unless `params_out` is given.
 int forward_common(flat_ctx *ctx, const ForwardCall &call, const flat_attention_shape *shape,
                    const flat_attention_config *config, flat_buffer q, flat_buffer k, flat_buffer v,
-                   flat_buffer out_and_lse) {
+                   flat_buffer out_and_lse, FwdParams *params_out = nullptr) {
     if (!ctx) return FLAT_ERR_NULL_POINTER;
     int st;
     if ((st = check_dtype(ctx, call.dtype))) return st;
@@ -224,8 +230,11 @@ int forward_common(flat_ctx *ctx, const ForwardCall &call, const flat_attention_
         p.varlen = static_cast<const flat_varlen_sequence *>(ctx->workspace);
         return launch_forward_simt(ctx, call.dtype, p);
     }
-    if (call.dtype == FLAT_BF16 && forward_sm100_supported(p)) return launch_forward_sm100(ctx, p);
-    return launch_forward_simt(ctx, call.dtype, p);
+    if (params_out) {
+        *params_out = p;
+        return FLAT_OK;
+    }
+    return launch_forward(ctx, call.dtype, p);
 }
 
 }  // namespace
@@ -492,6 +501,9 @@ void flat_ctx_destroy(flat_ctx *ctx) {
     }
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->host_stage) cudaFree(ctx->host_stage);
+    for (cudaEvent_t e : ctx->pipe_events) cudaEventDestroy(e);
+    if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
+    if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
     delete ctx;
 }
@@ -747,12 +759,51 @@ int32_t flat_forward_host(flat_ctx *ctx, int32_t dtype, int32_t layout, const fl
     }
     char *base = static_cast<char *>(ctx->host_stage);
     flat_buffer dq{base, qb}, dk{base + qb, kb}, dv{base + qb + kb, kb}, dout{base + qb + 2 * kb, ob};
-    FLAT_CUDA_OK(ctx, cudaMemcpyAsync(dq.ptr, q, d.q_elements * es, cudaMemcpyHostToDevice, ctx->stream));
-    FLAT_CUDA_OK(ctx, cudaMemcpyAsync(dk.ptr, k, d.kv_elements * es, cudaMemcpyHostToDevice, ctx->stream));
-    FLAT_CUDA_OK(ctx, cudaMemcpyAsync(dv.ptr, v, d.kv_elements * es, cudaMemcpyHostToDevice, ctx->stream));
     ForwardCall c{dtype, layout, rotary != nullptr, rotary, nullptr, 0, false};
-    if ((st = forward_common(ctx, c, shape, config, dq, dk, dv, dout))) return st;
-    FLAT_CUDA_OK(ctx, cudaMemcpyAsync(out_and_lse, dout.ptr, combined, cudaMemcpyDeviceToHost, ctx->stream));
+    FwdParams p;
+    if ((st = forward_common(ctx, c, shape, config, dq, dk, dv, dout, &p))) return st;
+
+    // Batch elements are independent: upload, attention and download of consecutive elements overlap
+    // on three streams (PCIe is full duplex), which is where the host-to-host time goes.
+    if (!ctx->copy_in) {
+        FLAT_CUDA_OK(ctx, cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
+        FLAT_CUDA_OK(ctx, cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
+    }
+    const int B = p.batch;
+    while ((int)ctx->pipe_events.size() < 2 * B + 1) {
+        cudaEvent_t e;
+        FLAT_CUDA_OK(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+        ctx->pipe_events.push_back(e);
+    }
+    // the staging buffers may still be read by earlier work on the context stream
+    FLAT_CUDA_OK(ctx, cudaEventRecord(ctx->pipe_events[2 * B], ctx->stream));
+    FLAT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->pipe_events[2 * B], 0));
+    const uint64_t q_b = (uint64_t)p.q_bs * es, kv_b = (uint64_t)p.kv_bs * es;
+    const uint64_t lse_b = (uint64_t)p.q_heads * p.lse_hs * sizeof(float);
+    const uint64_t lse_off = lse_offset_bytes(dtype, d.q_elements);
+    const char *hq = static_cast<const char *>(q), *hk = static_cast<const char *>(k), *hv = static_cast<const char *>(v);
+    char *ho = static_cast<char *>(out_and_lse);
+    for (int b = 0; b < B; ++b) {
+        FLAT_CUDA_OK(ctx, cudaMemcpyAsync((char *)dq.ptr + b * q_b, hq + b * q_b, q_b, cudaMemcpyHostToDevice, ctx->copy_in));
+        FLAT_CUDA_OK(ctx, cudaMemcpyAsync((char *)dk.ptr + b * kv_b, hk + b * kv_b, kv_b, cudaMemcpyHostToDevice, ctx->copy_in));
+        FLAT_CUDA_OK(ctx, cudaMemcpyAsync((char *)dv.ptr + b * kv_b, hv + b * kv_b, kv_b, cudaMemcpyHostToDevice, ctx->copy_in));
+        FLAT_CUDA_OK(ctx, cudaEventRecord(ctx->pipe_events[b], ctx->copy_in));
+        FLAT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->stream, ctx->pipe_events[b], 0));
+        FwdParams pb = p;
+        pb.batch = 1;
+        pb.q = (const char *)p.q + b * q_b;
+        pb.k = (const char *)p.k + b * kv_b;
+        pb.v = (const char *)p.v + b * kv_b;
+        pb.o = (char *)p.o + b * q_b;
+        pb.lse = p.lse + (uint64_t)b * p.q_heads * p.lse_hs;
+        if ((st = launch_forward(ctx, dtype, pb))) return st;
+        FLAT_CUDA_OK(ctx, cudaEventRecord(ctx->pipe_events[B + b], ctx->stream));
+        FLAT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->pipe_events[B + b], 0));
+        FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ho + b * q_b, (char *)p.o + b * q_b, q_b, cudaMemcpyDeviceToHost, ctx->copy_out));
+        FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ho + lse_off + b * lse_b, (char *)p.lse + b * lse_b, lse_b, cudaMemcpyDeviceToHost,
+                                          ctx->copy_out));
+    }
+    FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->copy_out));
     FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
     return FLAT_OK;
 }

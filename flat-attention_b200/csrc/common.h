@@ -38,6 +38,8 @@ struct flat_ctx {
     std::string detail;
     void *host_stage = nullptr;       // device staging of the host-slice entry points (Q | K | V | O|LSE)
     uint64_t host_stage_bytes = 0;
+    cudaStream_t copy_in = nullptr, copy_out = nullptr;  // upload / download streams of the host-slice entry points
+    std::vector<cudaEvent_t> pipe_events;
     // optional timing of the dominant kernel of each call (CUDA events on the launch stream)
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;
