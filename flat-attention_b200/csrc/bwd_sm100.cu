@@ -22,6 +22,7 @@
 
 #include <algorithm>
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 
 #include "common.h"
@@ -39,6 +40,16 @@ constexpr int kProducerWarp = 8;
 constexpr int kMmaWarp = 9;
 constexpr float kLog2e = 1.4426950408889634f;
 
+// Debug timeline (compiled in with -DFLAT_TRACE), same layout as in the forward kernel.
+#ifdef FLAT_TRACE
+#define TRACE(role, it, slot)                                                                          \
+    do {                                                                                               \
+        if (p.trace && blockIdx.x == 0 && (it) < 64) p.trace[((role) * 64 + (it)) * 8 + (slot)] = clock64(); \
+    } while (0)
+#else
+#define TRACE(role, it, slot) do { } while (0)
+#endif
+
 struct BwdKernelParams {
     CUtensorMap map_q, map_k, map_v, map_do;
     const float *neg_lse2;  // -LSE * log2(e), [B, Hq, N]
@@ -49,6 +60,7 @@ struct BwdKernelParams {
     float scale, scale_log2;
     uint32_t idesc_k, idesc_mn;
     DeviceStatus *status;
+    long long *trace;
 };
 
 template <int D> struct BCfg {
@@ -203,12 +215,15 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                 const uint8_t *stage = ring + s * C::kStageBytes;
                 wait(rg_full(s), (it / C::kStages) & 1, 210);
                 if (!ok) break;
+                TRACE(2, it, 0);
                 tc_fence_after();
                 issue_xy(kColX, st0, stage);
                 issue_xy(kColY, st1, stage + C::kTileBytes);
                 tc_commit(xy_full);
+                TRACE(2, it, 1);
                 wait(ds_full, it & 1, 220);
                 if (!ok) break;
+                TRACE(2, it, 2);
                 tc_fence_after();
                 if (KV) {
                     issue_acc(kColA0, kColX, stage + C::kTileBytes, it > 0);  // dV += P^T dO
@@ -217,6 +232,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                     issue_acc(kColA0, kColX, stage, it > 0);                  // dQ += dS K
                 }
                 tc_commit(rg_empty(s));
+                TRACE(2, it, 3);
             }
             if (ok) tc_commit(acc_final);
         }
@@ -251,6 +267,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                 break;
             }
             tc_fence_after();
+            if (warp == 0 && lane == 0) TRACE(0, it, 0);
             const int t = first + it % per_head;
             const bool diag = p.causal && t == t_own;
             uint32_t x[64], y[64];
@@ -259,6 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
             tmem_ld32(t_y, y);
             tmem_ld32(t_y + 32, y + 32);
             tc_wait_ld();
+            if (warp == 0 && lane == 0) TRACE(0, it, 1);
             const float *lse_s = reinterpret_cast<const float *>(stage + 2 * C::kTileBytes) + half * 64;
             const float *delta_s = lse_s + 128;
             uint32_t pp[32], ds[32];
@@ -297,6 +315,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                     pp[i >> 1] = *reinterpret_cast<const uint32_t *>(&pb);
                 }
             }
+            if (warp == 0 && lane == 0) TRACE(0, it, 2);
             // bf16 results go to the first 32 columns of this warp group's own 64-column range
             if (KV) {
                 tmem_st32(t_x, pp);   // P^T over S^T
@@ -308,6 +327,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(ds_full);
+            if (warp == 0 && lane == 0) TRACE(0, it, 3);
         }
         if (ok && !mbar_wait(acc_final, 0, abort_flag)) {
             timeout(p, 320);
@@ -416,6 +436,10 @@ int launch_backward_sm100(flat_ctx *ctx, const BwdParams &p) {
     kp.idesc_k = make_idesc(kFmtBF16, kFmtBF16, 0, 0, 128, 128);
     kp.idesc_mn = make_idesc(kFmtBF16, kFmtBF16, 0, 1, 128, (uint32_t)D);
     kp.status = ctx->dev_status;
+    kp.trace = nullptr;
+#ifdef FLAT_TRACE
+    if (const char *tp = getenv("FLAT_TRACE_PTR")) kp.trace = reinterpret_cast<long long *>(strtoull(tp, nullptr, 0));
+#endif
 
     auto run = [&](auto kernel, int smem_bytes, long long grid) -> int {
         FLAT_CUDA_OK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
