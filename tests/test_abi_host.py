@@ -135,3 +135,21 @@ def test_backward_layout_matches_reference_packing():
         0, 4 * q, 4 * (q + kv), 4 * (q + 2 * kv), 4 * (2 * q + 2 * kv), 4 * (3 * q + 2 * kv))
     assert L.input_bytes == 4 * (3 * q + 2 * kv + lse)
     assert (L.dq_offset, L.dk_offset, L.dv_offset, L.output_bytes) == (0, 4 * q, 4 * (q + kv), 4 * (q + 2 * kv))
+
+
+def test_cpp_host_mirror_compiles_and_runs(tmp_path):
+    """The header-only C++ mirror (flat-attention_b200/host/flat_attention.hpp) builds against the C ABI
+    with plain g++ and its host-only logic gives the reference's known answers."""
+    import os
+    import subprocess
+    import torch
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    exe = str(tmp_path / "host_mirror_check")
+    libdir = os.path.join(root, "flat-attention_b200")
+    subprocess.run(["g++", "-std=c++17", "-O1", "-Wall", os.path.join(root, "tests", "host_mirror_check.cpp"), "-o", exe,
+                    "-L" + libdir, "-lflat_attention_b200", "-Wl,-rpath," + libdir], check=True, capture_output=True, timeout=300)
+    env = dict(os.environ)
+    if not torch.cuda.is_available():
+        env["FLAT_EXPECT_NO_DEVICE"] = "1"
+    r = subprocess.run([exe], capture_output=True, text=True, timeout=120, env=env)
+    assert r.returncode == 0 and "host mirror ok" in r.stdout, r.stdout + r.stderr
