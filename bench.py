@@ -26,6 +26,15 @@ import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
+
+# DRAM bytes (read + written) per launch of each leg's dominant kernel(s) on exactly the workloads timed below, taken from
+# one `ncu --set full` capture each; the summaries and their commands are under profiles/.  The profiler cannot run inside
+# this script, so the figures are carried as constants and change only when a kernel changes.
+NCU_TRAFFIC = {
+    "forward": 341_415_680 + 106_866_944,  # fwd_sm100_kernel<128,false>, C2
+    "decode": 1_110_867_000 + 4_535_296,  # decode_mma_kernel<128>, C3
+    "backward": 1_188_420_000 + 114_253_568 + 740_095_000 + 237_467_904,  # dK/dV kernel + dQ kernel, C5
+}
 sys.path.insert(0, ROOT)
 
 C2 = dict(B=4, Hq=32, Hkv=8, N=4096, D=128, theta=500000.0)
@@ -240,7 +249,8 @@ def bench_decode(torch, np, fa, ctx, peaks, steps, warmup):
         "metric": "paged_decode_hbm_gbs", "value": alg / (ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": ms,
         "algorithmic_bytes": alg, "sequences": S, "context_tokens": int(lens.sum()),
         "roofline": {"bound": "hbm", "achieved": alg / (kernel_ms * 1e-3) / 1e9, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": alg / (kernel_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": None,
+                     "frac": alg / (kernel_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], "traffic": NCU_TRAFFIC["decode"],
+                     "traffic_source": "dram bytes read+written per launch, one ncu capture of this workload (profiles/)",
                      "kernel": "decode_mma_kernel<128>", "kernel_ms": kernel_ms, "peak_source": peaks["source"]},
         "l2": "flushed between steps (256 MiB write)",
     }
@@ -286,7 +296,8 @@ def bench_backward(torch, fa, ctx, peaks, steps, warmup):
             "flop_per_step": flops, "workload": "C5 B=2 Hq=32 Hkv=8 N=8192 D=128 causal bf16, f32 gradients",
             "roofline": {"bound": "tensor", "achieved": flops / (kernel_ms * 1e-3) / 1e12, "peak": peaks["bf16_sustained"] or peaks["bf16_tflops"],
                          "unit": "TFLOP/s", "frac": flops / (kernel_ms * 1e-3) / 1e12 / (peaks["bf16_sustained"] or peaks["bf16_tflops"]),
-                         "traffic": None, "kernel": "bwd_sm100_kernel<128,true> + bwd_sm100_kernel<128,false>",
+                         "traffic": NCU_TRAFFIC["backward"], "traffic_source": "dram bytes read+written, both kernels, one ncu capture of this workload (profiles/)",
+                         "kernel": "bwd_sm100_kernel<128,true> + bwd_sm100_kernel<128,false>",
                          "kernel_ms": kernel_ms, "peak_source": peaks["source"] + " (sustained cuBLAS bf16: the step runs for milliseconds)",
                          "note": "7 GEMM units are executed for 5 algorithmic ones (scores recomputed in both kernels)"}}
 
@@ -483,7 +494,9 @@ def main():
                 "ms_per_step": ms_e2e / e2e_steps},
         "gpu_launches": int(launches),
         "roofline": {"bound": "tensor", "achieved": flops / (kms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
-                     "frac": flops / (kms * 1e-3) / 1e12 / peak, "traffic": None, "kernel": "fwd_sm100_kernel<128,false>",
+                     "frac": flops / (kms * 1e-3) / 1e12 / peak, "traffic": NCU_TRAFFIC["forward"],
+                     "traffic_source": "dram bytes read+written per launch, one ncu capture of this workload (profiles/)",
+                     "kernel": "fwd_sm100_kernel<128,false>",
                      "kernel_ms": kms,
                      "peak_source": peaks["source"] + (" (sustained cuBLAS bf16: sw_power_cap was active during the timed loop)"
                                                        if capped else " (burst cuBLAS bf16)")},
