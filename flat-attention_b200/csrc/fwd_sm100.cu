@@ -48,12 +48,15 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 
-// Debug timeline (compiled in with -DFLAT_TRACE): clock64 stamps of CTA 0, written to the buffer whose
+// Debug timeline (compiled in with -DFLAT_TRACE): clock64 stamps of CTA FLAT_TRACE_BLOCK (default 0), written to the buffer whose
 // address is given in the environment variable FLAT_TRACE_PTR.  Layout [role 0..2][iteration 0..63][slot 0..7].
 #ifdef FLAT_TRACE
+#ifndef FLAT_TRACE_BLOCK
+#define FLAT_TRACE_BLOCK 0
+#endif
 #define TRACE(role, it, slot)                                                                          \
     do {                                                                                               \
-        if (p.trace && blockIdx.x == 0 && (it) < 64) p.trace[((role) * 64 + (it)) * 8 + (slot)] = clock64(); \
+        if (p.trace && blockIdx.x == FLAT_TRACE_BLOCK && (it) < 64) p.trace[((role) * 64 + (it)) * 8 + (slot)] = clock64(); \
     } while (0)
 #else
 #define TRACE(role, it, slot) do { } while (0)
@@ -74,6 +77,7 @@ struct KernelParams {
     int q_blocks;
     DeviceStatus *status;
     const float2 *rope_q_table;  // (cos, sin) of row r, pair j at [r * D/2 + j]; null = Q is used as loaded
+    float2 rope_step[kMaxHeadDim / 2];  // (cos, sin)(rows_per_step * inv_freq[j]): advances a row's rotation
     long long *trace;
 };
 
@@ -143,7 +147,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     }
     const int n_max = max(n_tiles[0], n_tiles[1]);
 
-    if (threadIdx.x == 0) {
+    if (threadIdx.x == 0) TRACE(0, 63, 0);
+    if (warp == kProducerWarp && lane == 0) {
         *abort_flag = 0;
         for (int w = 0; w < 2; ++w) {
             mbar_init(q_full(w), 1);
@@ -158,6 +163,17 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
         }
         mbar_fence_init();
         fence_proxy_async();
+        // the Q tiles are requested at once: their latency overlaps the TMEM allocation and the setup barrier
+        tma_prefetch_desc(&p.map_q);
+        for (int w = 0; w < 2; ++w) {
+            if (!active[w]) continue;
+            mbar_expect_tx(q_full(w), C::kTileBytes);
+            for (int kb = 0; kb < C::kBoxes; ++kb)
+                tma_load_4d(smem_u32(q_s + w * C::kQParts * C::kTileBytes + kb * C::kBoxBytes), &p.map_q, kb * 64,
+                            r0 + w * kTileRows, h, b, q_full(w));
+        }
+        tma_prefetch_desc(&p.map_k);
+        tma_prefetch_desc(&p.map_v);
     }
     if (warp == kMmaWarp) {
         tmem_alloc(smem_u32(tmem_slot), 512);
@@ -176,16 +192,6 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     if (warp == kProducerWarp) {
         // ================= TMA producer =================
         if (lane == 0) {
-            tma_prefetch_desc(&p.map_q);
-            tma_prefetch_desc(&p.map_k);
-            tma_prefetch_desc(&p.map_v);
-            for (int w = 0; w < 2; ++w) {
-                if (!active[w]) continue;
-                mbar_expect_tx(q_full(w), C::kTileBytes);
-                for (int kb = 0; kb < C::kBoxes; ++kb)
-                    tma_load_4d(smem_u32(q_s + w * C::kQParts * C::kTileBytes + kb * C::kBoxBytes), &p.map_q, kb * 64,
-                                r0 + w * kTileRows, h, b, q_full(w));
-            }
             bool ok = true;
             for (int i = 0; ok && i < 2 * n_max; ++i) {
                 const int s = i % C::kStages;
@@ -306,23 +312,60 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             const uint32_t t_s = t_lane + col_s[w];
             const uint32_t t_o = t_lane + col_o[w];
             bool ok = true;
+            if (threadIdx.x == 0) TRACE(0, 63, 1);
 
             if (p.rope_q_table) {
-                // rotate this thread's Q row in place (fp16), or into bf16 hi / lo tiles
+                // Rotate the Q tile in place (fp16), or into bf16 hi / lo tiles.  A warp rotates its 32 rows; lane l
+                // takes the 16-byte chunk (l mod CH) of row (step * RPS + l / CH), so that the (cos, sin) table is
+                // read in contiguous row segments.  The table goes to registers before the wait on the Q tile:
+                // its latency overlaps the TMA.
+                constexpr int CH = D / 8;     // 16-byte chunks (8 elements, 4 pairs) per row
+                constexpr int RPS = 32 / CH;  // rows per step of one warp
+                const int ch = lane % CH;
+                // (cos, sin) of the lane's first row come from the table; each further step advances the angle by
+                // RPS positions with the rotation (cos, sin)(RPS * inv_freq), which keeps the table traffic at two
+                // 16-byte loads per thread.  The recurrence error (a few 1e-7 over CH steps) is far below the
+                // rounding of the fp16 / bf16 result.
+                float cc[4], ss[4], cstep[4], sstep[4];
+                {
+                    const int rr = min(r0 + w * kTileRows + lane_base + lane / CH, p.q_len - 1);
+                    const float4 *tp = reinterpret_cast<const float4 *>(p.rope_q_table + (long long)rr * (D / 2)) + 2 * ch;
+                    const float4 cs0 = __ldg(tp), cs1 = __ldg(tp + 1);  // (c, s, c, s) x 2
+                    cc[0] = cs0.x; ss[0] = cs0.y; cc[1] = cs0.z; ss[1] = cs0.w;
+                    cc[2] = cs1.x; ss[2] = cs1.y; cc[3] = cs1.z; ss[3] = cs1.w;
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float2 stp = p.rope_step[ch * 4 + e];
+                        cstep[e] = stp.x;
+                        sstep[e] = stp.y;
+                    }
+                }
                 if (!mbar_wait(q_full(w), 0, abort_flag)) {
                     record_timeout(p, 290 + w);
                     ok = false;
                 }
-                if (ok && row < p.q_len) {
+                if (threadIdx.x == 0) TRACE(0, 63, 2);
+                if (ok) {
                     uint8_t *tile = q_s + w * C::kQParts * C::kTileBytes;
-                    const float4 *tab = reinterpret_cast<const float4 *>(p.rope_q_table + (long long)row * (D / 2));
-#pragma unroll 4
-                    for (int ch = 0; ch < D / 8; ++ch) {  // 16-byte chunks of the row: 8 elements, 4 pairs
-                        const int off = (ch >> 3) * C::kBoxBytes + row_in_tile * 128 + (((ch & 7) ^ (row_in_tile & 7)) << 4);
+#pragma unroll
+                    for (int st = 0; st < CH; ++st) {
+                        const int rt = lane_base + st * RPS + lane / CH;  // row in tile
+                        const int off = (ch >> 3) * C::kBoxBytes + rt * 128 + (((ch & 7) ^ (rt & 7)) << 4);
+                        if (st > 0) {
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float c1 = cc[e] * cstep[e] - ss[e] * sstep[e];
+                                ss[e] = ss[e] * cstep[e] + cc[e] * sstep[e];
+                                cc[e] = c1;
+                            }
+                        }
+                        if (r0 + w * kTileRows + rt >= p.q_len) {
+                            // rows past q_len were zero-filled by TMA in the hi tile; the lo tile has to be zero too
+                            if (SPLIT) *reinterpret_cast<uint4 *>(tile + C::kTileBytes + off) = make_uint4(0, 0, 0, 0);
+                            continue;
+                        }
                         const uint4 raw = *reinterpret_cast<const uint4 *>(tile + off);
-                        const float4 cs0 = __ldg(tab + 2 * ch), cs1 = __ldg(tab + 2 * ch + 1);  // (c, s, c, s) x 2
                         const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
-                        const float cc[4] = {cs0.x, cs0.z, cs1.x, cs1.z}, ss[4] = {cs0.y, cs0.w, cs1.y, cs1.w};
                         uint32_t hi[4], lo[4];
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
@@ -342,16 +385,11 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                         *reinterpret_cast<uint4 *>(tile + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                         if (SPLIT) *reinterpret_cast<uint4 *>(tile + C::kTileBytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                     }
-                } else if (ok && SPLIT) {
-                    // rows past q_len were zero-filled by TMA in the hi tile; the lo tile has to be zero too
-                    uint8_t *tile = q_s + (w * C::kQParts + 1) * C::kTileBytes;
-                    for (int ch = 0; ch < D / 8; ++ch)
-                        *reinterpret_cast<uint4 *>(tile + (ch >> 3) * C::kBoxBytes + row_in_tile * 128 + ((ch & 7) << 4)) =
-                            make_uint4(0, 0, 0, 0);
                 }
                 fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
                 __syncwarp();
                 if (lane == 0) mbar_arrive(q_ready(w));
+                if (threadIdx.x == 0) TRACE(0, 63, 3);
             }
 
             long long lim = (long long)p.kv_len - 1;  // last visible key of this row
@@ -460,6 +498,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             }
             if (ok) {
                 tc_fence_after();
+                if (threadIdx.x == 0) TRACE(0, 63, 5);
                 const float inv = 1.0f / l;
                 const bool store = row < p.q_len;
                 __nv_bfloat16 *op = reinterpret_cast<__nv_bfloat16 *>(p.o) + (long long)b * p.o_bs + (long long)h * p.o_hs +
@@ -484,6 +523,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     }
                 }
                 if (store) p.lse[((long long)b * p.q_heads + h) * p.lse_hs + row] = (m + log2f(l)) * kLn2;
+                if (threadIdx.x == 0) TRACE(0, 63, 6);
             }
         }
     }
@@ -650,6 +690,13 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     kp.q_blocks = (p.q_len + 2 * kTileRows - 1) / (2 * kTileRows);
     kp.status = ctx->dev_status;
     kp.rope_q_table = q_table;
+    if (q_table) {
+        const double rows_per_step = 32.0 / (D / 8);
+        for (int j = 0; j < D / 2; ++j) {
+            const double a = rows_per_step * (double)p.inv_freq[j];
+            kp.rope_step[j] = make_float2((float)std::cos(a), (float)std::sin(a));
+        }
+    }
     kp.trace = nullptr;
 #ifdef FLAT_TRACE
     if (const char *tp = getenv("FLAT_TRACE_PTR")) kp.trace = reinterpret_cast<long long *>(strtoull(tp, nullptr, 0));
