@@ -763,45 +763,63 @@ int32_t flat_forward_host(flat_ctx *ctx, int32_t dtype, int32_t layout, const fl
     FwdParams p;
     if ((st = forward_common(ctx, c, shape, config, dq, dk, dv, dout, &p))) return st;
 
-    // Batch elements are independent: upload, attention and download of consecutive elements overlap
-    // on three streams (PCIe is full duplex), which is where the host-to-host time goes.
+    // Batch elements, and in the head-major layout groups of KV heads, are independent: upload, attention and
+    // download of consecutive chunks overlap on three streams (PCIe is full duplex), which is where the
+    // host-to-host time goes.  Eight chunks measured best on the Llama-3-8B prefill shape (4: 4.87 ms, 8: 4.78 ms,
+    // 16: 5.35 ms, 32: 5.87 ms): more chunks shorten fill and drain, but mixed-direction PCIe traffic and the
+    // per-chunk enqueue cost grow.
     if (!ctx->copy_in) {
         FLAT_CUDA_OK(ctx, cudaStreamCreateWithFlags(&ctx->copy_in, cudaStreamNonBlocking));
         FLAT_CUDA_OK(ctx, cudaStreamCreateWithFlags(&ctx->copy_out, cudaStreamNonBlocking));
     }
     const int B = p.batch;
-    while ((int)ctx->pipe_events.size() < 2 * B + 1) {
+    int heads_per_chunk = p.kv_heads;
+    if (layout == FLAT_LAYOUT_HEAD_MAJOR) {
+        while (heads_per_chunk % 2 == 0 && (int64_t)B * (p.kv_heads / heads_per_chunk) < 8) heads_per_chunk /= 2;
+    }
+    const int chunks_per_b = p.kv_heads / heads_per_chunk;
+    const int n_chunks = B * chunks_per_b;
+    while ((int)ctx->pipe_events.size() < 2 * n_chunks + 1) {
         cudaEvent_t e;
         FLAT_CUDA_OK(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         ctx->pipe_events.push_back(e);
     }
     // the staging buffers may still be read by earlier work on the context stream
-    FLAT_CUDA_OK(ctx, cudaEventRecord(ctx->pipe_events[2 * B], ctx->stream));
-    FLAT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->pipe_events[2 * B], 0));
-    const uint64_t q_b = (uint64_t)p.q_bs * es, kv_b = (uint64_t)p.kv_bs * es;
-    const uint64_t lse_b = (uint64_t)p.q_heads * p.lse_hs * sizeof(float);
+    FLAT_CUDA_OK(ctx, cudaEventRecord(ctx->pipe_events[2 * n_chunks], ctx->stream));
+    FLAT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->pipe_events[2 * n_chunks], 0));
     const uint64_t lse_off = lse_offset_bytes(dtype, d.q_elements);
     const char *hq = static_cast<const char *>(q), *hk = static_cast<const char *>(k), *hv = static_cast<const char *>(v);
     char *ho = static_cast<char *>(out_and_lse);
-    for (int b = 0; b < B; ++b) {
-        FLAT_CUDA_OK(ctx, cudaMemcpyAsync((char *)dq.ptr + b * q_b, hq + b * q_b, q_b, cudaMemcpyHostToDevice, ctx->copy_in));
-        FLAT_CUDA_OK(ctx, cudaMemcpyAsync((char *)dk.ptr + b * kv_b, hk + b * kv_b, kv_b, cudaMemcpyHostToDevice, ctx->copy_in));
-        FLAT_CUDA_OK(ctx, cudaMemcpyAsync((char *)dv.ptr + b * kv_b, hv + b * kv_b, kv_b, cudaMemcpyHostToDevice, ctx->copy_in));
-        FLAT_CUDA_OK(ctx, cudaEventRecord(ctx->pipe_events[b], ctx->copy_in));
-        FLAT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->stream, ctx->pipe_events[b], 0));
+    for (int c = 0; c < n_chunks; ++c) {
+        const int b = c / chunks_per_b, kvh0 = (c % chunks_per_b) * heads_per_chunk;
+        // byte offsets and sizes of this chunk; with one chunk per batch element the whole element is contiguous
+        // in both layouts, a group of heads is contiguous only in the head-major one
+        const uint64_t q_off = ((uint64_t)b * p.q_bs + (uint64_t)kvh0 * p.group * p.q_hs) * es;
+        const uint64_t kv_off = ((uint64_t)b * p.kv_bs + (uint64_t)kvh0 * p.kv_hs) * es;
+        const uint64_t q_sz = chunks_per_b == 1 ? (uint64_t)p.q_bs * es : (uint64_t)heads_per_chunk * p.group * p.q_hs * es;
+        const uint64_t kv_sz = chunks_per_b == 1 ? (uint64_t)p.kv_bs * es : (uint64_t)heads_per_chunk * p.kv_hs * es;
+        const uint64_t lse_row0 = ((uint64_t)b * p.q_heads + (uint64_t)kvh0 * p.group) * p.lse_hs;
+        const uint64_t lse_sz = (uint64_t)heads_per_chunk * p.group * p.lse_hs * sizeof(float);
+        FLAT_CUDA_OK(ctx, cudaMemcpyAsync((char *)dq.ptr + q_off, hq + q_off, q_sz, cudaMemcpyHostToDevice, ctx->copy_in));
+        FLAT_CUDA_OK(ctx, cudaMemcpyAsync((char *)dk.ptr + kv_off, hk + kv_off, kv_sz, cudaMemcpyHostToDevice, ctx->copy_in));
+        FLAT_CUDA_OK(ctx, cudaMemcpyAsync((char *)dv.ptr + kv_off, hv + kv_off, kv_sz, cudaMemcpyHostToDevice, ctx->copy_in));
+        FLAT_CUDA_OK(ctx, cudaEventRecord(ctx->pipe_events[c], ctx->copy_in));
+        FLAT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->stream, ctx->pipe_events[c], 0));
         FwdParams pb = p;
         pb.batch = 1;
-        pb.q = (const char *)p.q + b * q_b;
-        pb.k = (const char *)p.k + b * kv_b;
-        pb.v = (const char *)p.v + b * kv_b;
-        pb.o = (char *)p.o + b * q_b;
-        pb.lse = p.lse + (uint64_t)b * p.q_heads * p.lse_hs;
+        pb.q_heads = heads_per_chunk * p.group;
+        pb.kv_heads = heads_per_chunk;
+        pb.q = (const char *)p.q + q_off;
+        pb.k = (const char *)p.k + kv_off;
+        pb.v = (const char *)p.v + kv_off;
+        pb.o = (char *)p.o + q_off;
+        pb.lse = p.lse + lse_row0;
         if ((st = launch_forward(ctx, dtype, pb))) return st;
-        FLAT_CUDA_OK(ctx, cudaEventRecord(ctx->pipe_events[B + b], ctx->stream));
-        FLAT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->pipe_events[B + b], 0));
-        FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ho + b * q_b, (char *)p.o + b * q_b, q_b, cudaMemcpyDeviceToHost, ctx->copy_out));
-        FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ho + lse_off + b * lse_b, (char *)p.lse + b * lse_b, lse_b, cudaMemcpyDeviceToHost,
-                                          ctx->copy_out));
+        FLAT_CUDA_OK(ctx, cudaEventRecord(ctx->pipe_events[n_chunks + c], ctx->stream));
+        FLAT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->copy_out, ctx->pipe_events[n_chunks + c], 0));
+        FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ho + q_off, (char *)p.o + q_off, q_sz, cudaMemcpyDeviceToHost, ctx->copy_out));
+        FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ho + lse_off + lse_row0 * sizeof(float), (char *)(p.lse + lse_row0), lse_sz,
+                                          cudaMemcpyDeviceToHost, ctx->copy_out));
     }
     FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->copy_out));
     FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));

@@ -58,8 +58,20 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 domain
     do {                                                                                               \
         if (p.trace && blockIdx.x == FLAT_TRACE_BLOCK && (it) < 64) p.trace[((role) * 64 + (it)) * 8 + (slot)] = clock64(); \
     } while (0)
+// Stamps of the softmax loop are kept in registers and written one iteration later, so that no global store is
+// outstanding when the thread signals the MMA warp.
+#define TRACE_LOCAL long long tr_[5] = {0, 0, 0, 0, 0}
+#define TRACE_STAMP(slot) tr_[slot] = clock64()
+#define TRACE_FLUSH(role, it)                                                                                  \
+    do {                                                                                                       \
+        if (p.trace && blockIdx.x == FLAT_TRACE_BLOCK && (it) >= 0 && (it) < 64)                               \
+            for (int s_ = 0; s_ < 5; ++s_) p.trace[((role) * 64 + (it)) * 8 + s_] = tr_[s_];                   \
+    } while (0)
 #else
 #define TRACE(role, it, slot) do { } while (0)
+#define TRACE_LOCAL do { } while (0)
+#define TRACE_STAMP(slot) do { } while (0)
+#define TRACE_FLUSH(role, it) do { } while (0)
 #endif
 
 struct KernelParams {
@@ -405,6 +417,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
 
             // Online softmax, log2 domain, one thread per row; the whole 128-column score row sits in
             // registers.  O in TMEM is rescaled only when the running max grew by more than 2^8.
+            TRACE_LOCAL;
             for (int j = 0; ok && j < n; ++j) {
                 if (!mbar_wait(s_full(w), j & 1, abort_flag)) {
                     record_timeout(p, 300 + w);
@@ -412,7 +425,10 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     break;
                 }
                 tc_fence_after();
-                if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 0);
+                if ((warp & 3) == 0 && lane == 0) {
+                    TRACE_FLUSH(w, j - 1);
+                    TRACE_STAMP(0);
+                }
                 const int key0 = j * kTileRows;
                 const bool tile_masked = (long long)key0 + kTileRows - 1 > lim_first;  // uniform over the Q tile
                 const int vis = (int)min((long long)kTileRows, lim - key0 + 1);        // visible columns of this row
@@ -420,7 +436,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, r + c * 32);
                 tc_wait_ld();
-                if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 1);
+                if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(1);
                 if (tile_masked) {
 #pragma unroll
                     for (int i = 0; i < 128; ++i)
@@ -451,7 +467,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     }
                 }
                 l *= alpha;
-                if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 2);
+                if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(2);
                 // P = exp2(S*c - m) as bf16, written over S; two scores per packed f32x2 FMA
                 uint64_t nm2, sum2 = 0, sum3 = 0;
                 {
@@ -483,13 +499,14 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     asm("mov.b64 {%0, %1}, %2;" : "=f"(s2f), "=f"(s3) : "l"(sum3));
                     l += (s0 + s1) + (s2f + s3);
                 }
-                if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 3);
+                if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(3);
                 tc_wait_st();
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) mbar_arrive(p_full(w));
-                if ((warp & 3) == 0 && lane == 0) TRACE(w, j, 4);
+                if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(4);
             }
+            if ((warp & 3) == 0 && lane == 0) TRACE_FLUSH(w, n - 1);
             if (ok) {
                 if (!mbar_wait(o_final(w), 0, abort_flag)) {
                     record_timeout(p, 310 + w);

@@ -41,16 +41,32 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same test, but the thread may stay suspended in hardware for up to `hint_ns` nanoseconds while the phase
+// is incomplete: a waiting warp then leaves the issue slots to the warps that compute.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 
 // Bounded wait: gives up after `kWaitCycles` clock cycles, or as soon as another thread of the CTA
 // has given up (`*abort_flag != 0`).  Returns false on give-up; the caller records where and
 // leaves its loop, so the kernel always terminates and the context stays usable.
 constexpr long long kWaitCycles = 4000000000LL;  // about two seconds
+constexpr uint32_t kSuspendNs = 20000;           // one suspended poll lasts at most 20 us
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     for (;;) {
-        if (mbar_try_wait(bar, parity)) return true;
+        if (mbar_try_wait_suspend(bar, parity, kSuspendNs)) return true;
         if (*abort_flag != 0) return false;
         if (clock64() - start > kWaitCycles) {
             *abort_flag = 1;

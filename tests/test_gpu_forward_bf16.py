@@ -120,7 +120,7 @@ def test_config2_llama8b_prefill_sampled_rows():
 
 
 def test_host_slice_forward_pipelined_over_batch_matches_resident_call():
-    """flat_forward_host overlaps upload / attention / download per batch element; the packed host
+    """flat_forward_host overlaps upload / attention / download per batch element and KV-head group; the packed host
     result must equal the resident-buffer call bit for bit (bf16 tensor-core path and f32 path)."""
     c = ctx()
     for dtype, B, Hq, Hkv, N, D in ((fa.BF16, 3, 4, 2, 256, 128), (fa.F32, 3, 4, 2, 40, 32)):
@@ -137,3 +137,10 @@ def test_host_slice_forward_pipelined_over_batch_matches_resident_call():
         dev_out = c.create_output_buffer(dtype, shp)
         c.forward_grouped_rope(dtype, shp, fa.config(True), rot, q.cuda(), k.cuda(), v.cuda(), dev_out)
         assert torch.equal(host_out, dev_out.cpu())
+        # projection layout [B, N, H*D]: one chunk per batch element
+        qp, kp, vp = (t.transpose(1, 2).contiguous() for t in (q, k, v))
+        host_out2 = torch.empty(L.combined_bytes, dtype=torch.uint8).pin_memory()
+        c.forward_host(dtype, fa.PROJECTION, shp, fa.config(True), rot, qp.pin_memory(), kp.pin_memory(), vp.pin_memory(), host_out2)
+        dev_out2 = c.create_output_buffer(dtype, shp)
+        c.forward_projection_rope(dtype, shp, fa.config(True), rot, qp.cuda(), kp.cuda(), vp.cuda(), dev_out2)
+        assert torch.equal(host_out2, dev_out2.cpu())
