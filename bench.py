@@ -440,8 +440,13 @@ def main():
         # the public host-slice call: pinned host Q/K/V in, pinned host [O | LSE] out, blocks until the result is readable
         ctx.forward_host(fa.BF16, fa.HEAD_MAJOR, shp, cfg, rot, hq, hk, hv, host_out)
 
-    for _ in range(args.warmup):
+    for i in range(args.warmup):
         step()
+        if i == 0:
+            # a kernel whose bounded waits gave up reports it here: stop at once instead of timing a broken path
+            st = ctx.device_status()
+            if st != 0:
+                raise SystemExit(f"bench: the forward kernel reported device status {st} on its first launch")
     torch.cuda.synchronize()
 
     # parity gate before timing (reference bench protocol): a few sampled rows against the oracle

@@ -56,7 +56,12 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 #endif
 #define TRACE(role, it, slot)                                                                          \
     do {                                                                                               \
-        if (p.trace && blockIdx.x == FLAT_TRACE_BLOCK && (it) < 64) p.trace[((role) * 64 + (it)) * 8 + (slot)] = clock64(); \
+        if (p.trace && trace_item && blockIdx.x == FLAT_TRACE_BLOCK && (it) < 64) p.trace[((role) * 64 + (it)) * 8 + (slot)] = clock64(); \
+    } while (0)
+#define TRACEB(k, role, slot)                                                                                \
+    do {                                                                                                     \
+        if (p.trace && blockIdx.x == FLAT_TRACE_BLOCK && (k) >= 0 && (k) < 4)                                 \
+            p.trace[((role) * 64 + 56 + (k)) * 8 + (slot)] = clock64();                                      \
     } while (0)
 // Stamps of the softmax loop are kept in registers and written one iteration later, so that no global store is
 // outstanding when the thread signals the MMA warp.
@@ -64,7 +69,7 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 #define TRACE_STAMP(slot) tr_[slot] = clock64()
 #define TRACE_FLUSH(role, it)                                                                                  \
     do {                                                                                                       \
-        if (p.trace && blockIdx.x == FLAT_TRACE_BLOCK && (it) >= 0 && (it) < 64)                               \
+        if (p.trace && trace_item && blockIdx.x == FLAT_TRACE_BLOCK && (it) >= 0 && (it) < 64)                               \
             for (int s_ = 0; s_ < 5; ++s_) p.trace[((role) * 64 + (it)) * 8 + s_] = tr_[s_];                   \
     } while (0)
 #else
@@ -72,6 +77,7 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 #define TRACE_LOCAL do { } while (0)
 #define TRACE_STAMP(slot) do { } while (0)
 #define TRACE_FLUSH(role, it) do { } while (0)
+#define TRACEB(k, role, slot) do { } while (0)
 #endif
 
 struct KernelParams {
@@ -87,6 +93,7 @@ struct KernelParams {
     const int32_t *page_table;
     int page_size, max_pages, physical_pages;
     int q_blocks;
+    long long total_items;  // q_blocks * batch * q_heads
     DeviceStatus *status;
     const float2 *rope_q_table;  // (cos, sin) of row r, pair j at [r * D/2 + j]; null = Q is used as loaded
     float2 rope_step[kMaxHeadDim / 2];  // (cos, sin)(rows_per_step * inv_freq[j]): advances a row's rotation
@@ -100,7 +107,7 @@ template <int D, bool SPLIT> struct Cfg {
     static constexpr int kTileBytes = kBoxes * kBoxBytes;  // one Q / K / V tile
     static constexpr int kQParts = SPLIT ? 2 : 1;
     static constexpr int kStages = D == 128 ? (SPLIT ? 3 : 4) : 8;  // K/V ring entries
-    static constexpr int kBars = 2 + 2 * kStages + 8;
+    static constexpr int kBars = 2 + 2 * kStages + 10;
     static constexpr int kSmemBytes = (2 * kQParts + kStages) * kTileBytes + kBars * 8 + 16 + 1024;
 };
 
@@ -109,6 +116,43 @@ __device__ __forceinline__ void record_timeout(const KernelParams &p, int where)
         p.status->code = FLAT_ERR_DEVICE_WAIT_TIMEOUT;
         p.status->where = where;
     }
+}
+
+// One unit of work: 256 consecutive query rows of one (batch, q_head).
+struct WorkItem {
+    int b, h, kvh, r0;
+    int n_tiles[2];  // KV tiles each of the two Q tiles visits (0 = the tile starts past q_len)
+};
+
+__device__ __forceinline__ WorkItem make_item(const KernelParams &p, int lin) {
+    // item index -> (query block, batch, head); late (long) query blocks first
+    WorkItem it;
+    const int total_bh = p.batch * p.q_heads;
+    const int qb = p.q_blocks - 1 - lin / total_bh;
+    const int bh = lin % total_bh;
+    it.b = bh / p.q_heads;
+    it.h = bh % p.q_heads;
+    it.kvh = it.h / p.group;
+    it.r0 = qb * 2 * kTileRows;
+#pragma unroll
+    for (int w = 0; w < 2; ++w) {
+        const int first = it.r0 + w * kTileRows;
+        long long visible = p.kv_len;
+        if (p.causal) {
+            const long long last_row = min(first + kTileRows - 1, p.q_len - 1);
+            visible = min((long long)p.kv_len, p.causal_off + last_row + 1);
+        }
+        it.n_tiles[w] = first < p.q_len ? (int)((visible + kTileRows - 1) / kTileRows) : 0;
+    }
+    return it;
+}
+
+// The k-th item of this CTA, or -1.  Items are sorted longest first; CTAs take them in rounds of gridDim.x,
+// odd rounds in reverse CTA order, so that every CTA gets nearly the same number of KV tiles.
+__device__ __forceinline__ int item_index(const KernelParams &p, int k) {
+    const int g = (int)gridDim.x;
+    const long long idx = (long long)k * g + ((k & 1) ? g - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    return idx < p.total_items ? (int)idx : -1;
 }
 
 template <int D, bool SPLIT>
@@ -130,36 +174,11 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     auto p_full = [&](int w) { return bar0 + 8u * (4 + 2 * C::kStages + w); };
     auto o_final = [&](int w) { return bar0 + 8u * (6 + 2 * C::kStages + w); };
     auto q_ready = [&](int w) { return bar0 + 8u * (8 + 2 * C::kStages + w); };
+    auto q_empty = [&](int w) { return bar0 + 8u * (10 + 2 * C::kStages + w); };
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    // block -> (query block, batch, head); late (long) query blocks first
-    const int total_bh = p.batch * p.q_heads;
-    const int lin = blockIdx.x;
-    const int qb = p.q_blocks - 1 - lin / total_bh;
-    const int bh = lin % total_bh;
-    const int b = bh / p.q_heads;
-    const int h = bh % p.q_heads;
-    const int kvh = h / p.group;
-    const int r0 = qb * 2 * kTileRows;
-
-    int n_tiles[2];
-    bool active[2];
-#pragma unroll
-    for (int w = 0; w < 2; ++w) {
-        const int first = r0 + w * kTileRows;
-        active[w] = first < p.q_len;
-        long long visible = p.kv_len;
-        if (p.causal) {
-            const long long last_row = min(first + kTileRows - 1, p.q_len - 1);
-            visible = min((long long)p.kv_len, p.causal_off + last_row + 1);
-        }
-        n_tiles[w] = active[w] ? (int)((visible + kTileRows - 1) / kTileRows) : 0;
-    }
-    const int n_max = max(n_tiles[0], n_tiles[1]);
-
-    if (threadIdx.x == 0) TRACE(0, 63, 0);
     if (warp == kProducerWarp && lane == 0) {
         *abort_flag = 0;
         for (int w = 0; w < 2; ++w) {
@@ -168,6 +187,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             mbar_init(p_full(w), 4);
             mbar_init(o_final(w), 1);
             mbar_init(q_ready(w), 4);
+            mbar_init(q_empty(w), 1);
         }
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(kv_full(s), 1);
@@ -175,15 +195,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
         }
         mbar_fence_init();
         fence_proxy_async();
-        // the Q tiles are requested at once: their latency overlaps the TMEM allocation and the setup barrier
         tma_prefetch_desc(&p.map_q);
-        for (int w = 0; w < 2; ++w) {
-            if (!active[w]) continue;
-            mbar_expect_tx(q_full(w), C::kTileBytes);
-            for (int kb = 0; kb < C::kBoxes; ++kb)
-                tma_load_4d(smem_u32(q_s + w * C::kQParts * C::kTileBytes + kb * C::kBoxBytes), &p.map_q, kb * 64,
-                            r0 + w * kTileRows, h, b, q_full(w));
-        }
         tma_prefetch_desc(&p.map_k);
         tma_prefetch_desc(&p.map_v);
     }
@@ -198,38 +210,65 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     const uint32_t col_s[2] = {0u, 128u};
     const uint32_t col_o[2] = {256u, 256u + D};
 
-    // Register rebalancing: a softmax thread holds a whole 128-column score row in registers.
+    // Register rebalancing: a softmax thread holds a whole 128-column score row in registers.  The pool that
+    // setmaxnreg.inc draws from is what the CTA was launched with (168 registers x 384 threads), not the whole
+    // register file: 56 x 128 + 224 x 256 uses exactly that, and a larger request would block for ever.
+    static_assert(56 * 128 + 224 * 256 <= 168 * kThreads && 72 * 128 + 216 * 256 <= 168 * kThreads,
+                  "setmaxnreg split exceeds the CTA's register allocation");
     if (warp >= 8) {
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if constexpr (SPLIT) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");  // two Q parts: a longer issue sequence
+    else asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == kProducerWarp) {
         // ================= TMA producer =================
         if (lane == 0) {
             bool ok = true;
-            for (int i = 0; ok && i < 2 * n_max; ++i) {
-                const int s = i % C::kStages;
-                const uint32_t phase = (i / C::kStages) & 1;
-                if (!mbar_wait(kv_empty(s), phase ^ 1, abort_flag)) {
-                    record_timeout(p, 100 + s);
-                    ok = false;
-                    break;
-                }
-                const int j = i >> 1;
-                const CUtensorMap *map = (i & 1) ? &p.map_v : &p.map_k;
-                const uint32_t dst = smem_u32(kv_s + s * C::kTileBytes);
-                mbar_expect_tx(kv_full(s), C::kTileBytes);
-                if (p.page_table) {
-                    const int pages_per_tile = kTileRows / p.page_size;
-                    for (int pg = 0; pg < pages_per_tile; ++pg) {
-                        const int tok = j * kTileRows + pg * p.page_size;
-                        const int page = tok < p.kv_len ? p.page_table[(long long)b * p.max_pages + tok / p.page_size]
-                                                        : p.physical_pages;  // out of range: zero fill
-                        for (int kb = 0; kb < C::kBoxes; ++kb)
-                            tma_load_4d(dst + kb * C::kBoxBytes + pg * p.page_size * 128, map, kb * 64, 0, kvh, page,
-                                        kv_full(s));
+            uint32_t ring = 0;         // K/V ring entries requested so far
+            uint32_t q_loads[2] = {0, 0};  // Q tiles requested so far, per slot
+            for (int k = 0; ok; ++k) {
+                const int lin = item_index(p, k);
+                if (lin < 0) break;
+                const WorkItem it = make_item(p, lin);
+                const int n_max = max(it.n_tiles[0], it.n_tiles[1]);
+                for (int w = 0; w < 2 && ok; ++w) {
+                    if (it.n_tiles[w] == 0) continue;
+                    // the slot is free once every S MMA of its previous tile has completed
+                    if (q_loads[w] > 0 && !mbar_wait(q_empty(w), (q_loads[w] - 1) & 1, abort_flag)) {
+                        record_timeout(p, 110 + w);
+                        ok = false;
+                        break;
                     }
-                } else {
+                    ++q_loads[w];
+                    mbar_expect_tx(q_full(w), C::kTileBytes);
                     for (int kb = 0; kb < C::kBoxes; ++kb)
-                        tma_load_4d(dst + kb * C::kBoxBytes, map, kb * 64, j * kTileRows, kvh, b, kv_full(s));
+                        tma_load_4d(smem_u32(q_s + w * C::kQParts * C::kTileBytes + kb * C::kBoxBytes), &p.map_q, kb * 64,
+                                    it.r0 + w * kTileRows, it.h, it.b, q_full(w));
+                }
+                for (int i = 0; ok && i < 2 * n_max; ++i, ++ring) {
+                    const int s = ring % C::kStages;
+                    const uint32_t phase = (ring / C::kStages) & 1;
+                    if (!mbar_wait(kv_empty(s), phase ^ 1, abort_flag)) {
+                        record_timeout(p, 100 + s);
+                        ok = false;
+                        break;
+                    }
+                    const int j = i >> 1;
+                    const CUtensorMap *map = (i & 1) ? &p.map_v : &p.map_k;
+                    const uint32_t dst = smem_u32(kv_s + s * C::kTileBytes);
+                    mbar_expect_tx(kv_full(s), C::kTileBytes);
+                    if (p.page_table) {
+                        const int pages_per_tile = kTileRows / p.page_size;
+                        for (int pg = 0; pg < pages_per_tile; ++pg) {
+                            const int tok = j * kTileRows + pg * p.page_size;
+                            const int page = tok < p.kv_len ? p.page_table[(long long)it.b * p.max_pages + tok / p.page_size]
+                                                            : p.physical_pages;  // out of range: zero fill
+                            for (int kb = 0; kb < C::kBoxes; ++kb)
+                                tma_load_4d(dst + kb * C::kBoxBytes + pg * p.page_size * 128, map, kb * 64, 0, it.kvh, page,
+                                            kv_full(s));
+                        }
+                    } else {
+                        for (int kb = 0; kb < C::kBoxes; ++kb)
+                            tma_load_4d(dst + kb * C::kBoxBytes, map, kb * 64, j * kTileRows, it.kvh, it.b, kv_full(s));
+                    }
                 }
             }
         }
@@ -244,278 +283,328 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     ok = false;
                 }
             };
+            // The issue loops are unrolled (a rolled loop's dependent instructions cost 100+ cycles per MMA on this
+            // single thread, more than the tensor pipe needs), and each descriptor is the tile's base descriptor plus
+            // a compile-time constant, which keeps the thread inside its small register budget.
             auto issue_s = [&](int w, int stage) {
-                const uint32_t b0 = smem_u32(kv_s + stage * C::kTileBytes);
+                const uint64_t b_desc = make_smem_desc(smem_u32(kv_s + stage * C::kTileBytes), 0, 1024);
 #pragma unroll
                 for (int part = 0; part < C::kQParts; ++part) {
-                    const uint32_t a0 = smem_u32(q_s + (w * C::kQParts + part) * C::kTileBytes);
+                    const uint64_t a_desc = make_smem_desc(smem_u32(q_s + (w * C::kQParts + part) * C::kTileBytes), 0, 1024);
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
-                        const uint32_t off = (kk / 4) * C::kBoxBytes + (kk % 4) * 32;
-                        mma_ss(tmem_base + col_s[w], make_smem_desc(a0 + off, 0, 1024),
-                               make_smem_desc(b0 + off, 0, 1024), p.idesc_qk, (part > 0 || kk > 0));
+                        const uint32_t off16 = (kk >> 2) * (C::kBoxBytes >> 4) + (kk & 3) * 2;  // byte offset / 16
+                        mma_ss_off(tmem_base + col_s[w], a_desc, b_desc, off16, p.idesc_qk, (part > 0 || kk > 0));
                     }
                 }
             };
             auto issue_pv = [&](int w, int stage, int j) {
-                const uint32_t b0 = smem_u32(kv_s + stage * C::kTileBytes);
+                const uint64_t b_desc = make_smem_desc(smem_u32(kv_s + stage * C::kTileBytes), C::kBoxBytes, 1024);
 #pragma unroll
                 for (int kk = 0; kk < kTileRows / 16; ++kk)
-                    mma_ts(tmem_base + col_o[w], tmem_base + col_s[w] + kk * 8,
-                           make_smem_desc(b0 + kk * 16 * 128, C::kBoxBytes, 1024), p.idesc_pv, (j > 0 || kk > 0));
+                    mma_ts_off(tmem_base + col_o[w], tmem_base + col_s[w] + kk * 8, b_desc, kk * (16 * 128 >> 4), p.idesc_pv,
+                               (j > 0 || kk > 0));
             };
-            auto stage_of = [&](int i) { return i % C::kStages; };
-            auto phase_of = [&](int i) { return (uint32_t)((i / C::kStages) & 1); };
+            uint32_t ring0 = 0;           // ring entry of K_0 of the current item
+            uint32_t q_uses[2] = {0, 0};  // Q tiles consumed so far, per slot
+            uint32_t p_waits[2] = {0, 0}; // P hand-overs consumed so far, per slot
+            auto stage_of = [&](uint32_t i) { return (int)((ring0 + i) % C::kStages); };
+            auto phase_of = [&](uint32_t i) { return (uint32_t)(((ring0 + i) / C::kStages) & 1); };
 
-            for (int w = 0; w < 2; ++w)
-                if (active[w]) wait(p.rope_q_table ? q_ready(w) : q_full(w), 0, 200 + w);
-            // prologue: S_w(0)
-            wait(kv_full(stage_of(0)), phase_of(0), 210);
-            if (ok) {
-                tc_fence_after();
-                for (int w = 0; w < 2; ++w) {
-                    if (n_tiles[w] > 0) {
-                        issue_s(w, stage_of(0));
-                        tc_commit(s_full(w));
-                    }
-                }
-                tc_commit(kv_empty(stage_of(0)));
-            }
-            for (int j = 0; ok && j < n_max; ++j) {
-                const int iv = 2 * j + 1, ik = 2 * j + 2;
-                wait(kv_full(stage_of(iv)), phase_of(iv), 220);
-                bool k_ready = false;
+            for (int k = 0; ok; ++k) {
+                const int lin = item_index(p, k);
+                if (lin < 0) break;
+                const WorkItem it = make_item(p, lin);
+                const int n_max = max(it.n_tiles[0], it.n_tiles[1]);
+                const bool trace_item = k == 0;
+                (void)trace_item;
+                TRACEB(k, 2, 0);
+                // prologue: S_w(0) as soon as the slot's Q tile is ready (the other slot may still be finishing the
+                // previous item)
+                bool k0_ready = false;
                 for (int w = 0; w < 2 && ok; ++w) {
-                    if (j >= n_tiles[w]) continue;
-                    wait(p_full(w), j & 1, 230 + w);
+                    if (it.n_tiles[w] == 0) continue;
+                    wait(p.rope_q_table ? q_ready(w) : q_full(w), q_uses[w] & 1, 200 + w);
+                    ++q_uses[w];
+                    TRACEB(k, 2, 1 + w);
+                    if (!k0_ready) {
+                        wait(kv_full(stage_of(0)), phase_of(0), 210);
+                        k0_ready = true;
+                    }
                     if (!ok) break;
-                    TRACE(2, j, w * 4 + 0);
                     tc_fence_after();
-                    issue_pv(w, stage_of(iv), j);
-                    TRACE(2, j, w * 4 + 1);
-                    if (w == 1 || j >= n_tiles[1]) tc_commit(kv_empty(stage_of(iv)));  // last reader of V_j
-                    if (j + 1 < n_tiles[w]) {
-                        if (!k_ready) {
-                            wait(kv_full(stage_of(ik)), phase_of(ik), 240);
-                            if (!ok) break;
-                            tc_fence_after();
-                            k_ready = true;
+                    issue_s(w, stage_of(0));
+                    tc_commit(s_full(w));
+                    if (it.n_tiles[w] == 1) tc_commit(q_empty(w));  // the slot's last S of this item
+                }
+                if (ok) {
+                    tc_commit(kv_empty(stage_of(0)));
+                    TRACEB(k, 2, 3);
+                }
+                for (int j = 0; ok && j < n_max; ++j) {
+                    const uint32_t iv = 2 * j + 1, ik = 2 * j + 2;
+                    wait(kv_full(stage_of(iv)), phase_of(iv), 220);
+                    bool k_ready = false;
+                    for (int w = 0; w < 2 && ok; ++w) {
+                        if (j >= it.n_tiles[w]) continue;
+                        wait(p_full(w), p_waits[w] & 1, 230 + w);
+                        if (!ok) break;
+                        ++p_waits[w];
+                        TRACE(2, j, w * 4 + 0);
+                        tc_fence_after();
+                        issue_pv(w, stage_of(iv), j);
+                        TRACE(2, j, w * 4 + 1);
+                        if (w == 1 || j >= it.n_tiles[1]) tc_commit(kv_empty(stage_of(iv)));  // last reader of V_j
+                        if (j + 1 < it.n_tiles[w]) {
+                            if (!k_ready) {
+                                wait(kv_full(stage_of(ik)), phase_of(ik), 240);
+                                if (!ok) break;
+                                tc_fence_after();
+                                k_ready = true;
+                            }
+                            issue_s(w, stage_of(ik));
+                            tc_commit(s_full(w));
+                            if (j + 2 == it.n_tiles[w]) tc_commit(q_empty(w));  // the slot's last S of this item
+                            TRACE(2, j, w * 4 + 2);
+                            if (w == 1 || j + 1 >= it.n_tiles[1]) tc_commit(kv_empty(stage_of(ik)));  // last reader of K_{j+1}
+                        } else {
+                            tc_commit(o_final(w));
                         }
-                        issue_s(w, stage_of(ik));
-                        tc_commit(s_full(w));
-                        TRACE(2, j, w * 4 + 2);
-                        if (w == 1 || j + 1 >= n_tiles[1]) tc_commit(kv_empty(stage_of(ik)));  // last reader of K_{j+1}
-                    } else {
-                        tc_commit(o_final(w));
                     }
                 }
+                ring0 += 2 * n_max;
             }
         }
     }
     } else {
         // ================= softmax + epilogue =================
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        if constexpr (SPLIT) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        else asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int w = warp >> 2;
-        if (active[w]) {
-            const int lane_base = (warp & 3) * 32;
-            const int row_in_tile = lane_base + lane;
-            const int row = r0 + w * kTileRows + row_in_tile;
-            const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16);
-            const uint32_t t_s = t_lane + col_s[w];
-            const uint32_t t_o = t_lane + col_o[w];
-            bool ok = true;
-            if (threadIdx.x == 0) TRACE(0, 63, 1);
+        const int lane_base = (warp & 3) * 32;
+        const int row_in_tile = lane_base + lane;
+        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16);
+        const uint32_t t_s = t_lane + col_s[w];
+        const uint32_t t_o = t_lane + col_o[w];
+        bool ok = true;
+        uint32_t done = 0;     // finished items of this slot (its tile was inside q_len)
+        uint32_t s_waits = 0;  // score tiles of this slot consumed so far
 
-            if (p.rope_q_table) {
-                // Rotate the Q tile in place (fp16), or into bf16 hi / lo tiles.  A warp rotates its 32 rows; lane l
-                // takes the 16-byte chunk (l mod CH) of row (step * RPS + l / CH), so that the (cos, sin) table is
-                // read in contiguous row segments.  The table goes to registers before the wait on the Q tile:
-                // its latency overlaps the TMA.
-                constexpr int CH = D / 8;     // 16-byte chunks (8 elements, 4 pairs) per row
-                constexpr int RPS = 32 / CH;  // rows per step of one warp
-                const int ch = lane % CH;
-                // (cos, sin) of the lane's first row come from the table; each further step advances the angle by
-                // RPS positions with the rotation (cos, sin)(RPS * inv_freq), which keeps the table traffic at two
-                // 16-byte loads per thread.  The recurrence error (a few 1e-7 over CH steps) is far below the
-                // rounding of the fp16 / bf16 result.
-                float cc[4], ss[4], cstep[4], sstep[4];
-                {
-                    const int rr = min(r0 + w * kTileRows + lane_base + lane / CH, p.q_len - 1);
-                    const float4 *tp = reinterpret_cast<const float4 *>(p.rope_q_table + (long long)rr * (D / 2)) + 2 * ch;
-                    const float4 cs0 = __ldg(tp), cs1 = __ldg(tp + 1);  // (c, s, c, s) x 2
-                    cc[0] = cs0.x; ss[0] = cs0.y; cc[1] = cs0.z; ss[1] = cs0.w;
-                    cc[2] = cs1.x; ss[2] = cs1.y; cc[3] = cs1.z; ss[3] = cs1.w;
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float2 stp = p.rope_step[ch * 4 + e];
-                        cstep[e] = stp.x;
-                        sstep[e] = stp.y;
+        // Iteration k runs the KV loop of item k, then rotates the Q tile of item k + 1 (its TMA was issued as soon as
+        // the slot's last S MMA had completed), then stores item k: the next item's first S MMA runs during the
+        // epilogue.  k = -1 only rotates the first tile.
+        for (int k = -1; ok; ++k) {
+            // (item indices are recomputed where they are needed rather than kept in registers across the KV loop)
+            const bool trace_item = k == 0;
+            (void)trace_item;
+            float m = -INFINITY, l = 0.f;
+            bool run = false;
+            if (k >= 0) {
+                const WorkItem it = make_item(p, item_index(p, k));
+                run = it.n_tiles[w] > 0;
+                const int n = it.n_tiles[w];
+                int lim = p.kv_len - 1;  // last visible key of this row
+                int lim_first = lim;     // ... and of the tile's first row: tiles below it need no mask at all
+                if (p.causal) {
+                    const int first = it.r0 + w * kTileRows;
+                    lim = (int)min((long long)lim, p.causal_off + first + row_in_tile);
+                    lim_first = (int)min((long long)lim_first, p.causal_off + first);
+                }
+
+                // Online softmax, log2 domain, one thread per row; the whole 128-column score row sits in
+                // registers.  O in TMEM is rescaled only when the running max grew by more than 2^8.
+                TRACE_LOCAL;
+                for (int j = 0; ok && j < n; ++j) {
+                    if (!mbar_wait(s_full(w), s_waits & 1, abort_flag)) {
+                        record_timeout(p, 300 + w);
+                        ok = false;
+                        break;
                     }
-                }
-                if (!mbar_wait(q_full(w), 0, abort_flag)) {
-                    record_timeout(p, 290 + w);
-                    ok = false;
-                }
-                if (threadIdx.x == 0) TRACE(0, 63, 2);
-                if (ok) {
-                    uint8_t *tile = q_s + w * C::kQParts * C::kTileBytes;
+                    ++s_waits;
+                    tc_fence_after();
+                    if ((warp & 3) == 0 && lane == 0) {
+                        TRACE_FLUSH(w, j - 1);
+                        TRACE_STAMP(0);
+                    }
+                    const int key0 = j * kTileRows;
+                    const bool tile_masked = key0 + kTileRows - 1 > lim_first;  // uniform over the Q tile
+                    const int vis = min(kTileRows, lim - key0 + 1);             // visible columns of this row
+                    const float c_log2 = p.scale_log2;
+                    uint32_t r[128];  // four loads in flight, one wait
 #pragma unroll
-                    for (int st = 0; st < CH; ++st) {
-                        const int rt = lane_base + st * RPS + lane / CH;  // row in tile
-                        const int off = (ch >> 3) * C::kBoxBytes + rt * 128 + (((ch & 7) ^ (rt & 7)) << 4);
-                        if (st > 0) {
+                    for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, r + c * 32);
+                    tc_wait_ld();
+                    if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(1);
+                    if (tile_masked) {
 #pragma unroll
-                            for (int e = 0; e < 4; ++e) {
-                                const float c1 = cc[e] * cstep[e] - ss[e] * sstep[e];
-                                ss[e] = ss[e] * cstep[e] + cc[e] * sstep[e];
-                                cc[e] = c1;
-                            }
+                        for (int i = 0; i < 128; ++i)
+                            if (i >= vis) r[i] = 0xff800000u;  // -inf: exp2 gives exactly 0
+                    }
+                    float mx = -INFINITY, mx1 = -INFINITY;  // two chains for instruction-level parallelism
+#pragma unroll
+                    for (int i = 0; i < 128; i += 4) {
+                        asm("max.f32 %0, %0, %1, %2;" : "+f"(mx) : "f"(__uint_as_float(r[i])), "f"(__uint_as_float(r[i + 1])));
+                        asm("max.f32 %0, %0, %1, %2;" : "+f"(mx1) : "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3])));
+                    }
+                    const float m_cand = fmaxf(m, fmaxf(mx, mx1) * c_log2);
+                    const bool grow = (m_cand - m) > kRescaleThreshold;
+                    float alpha = 1.0f;
+                    if (grow) {
+                        alpha = ex2(m - m_cand);
+                        m = m_cand;
+                    }
+                    if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                        uint32_t o[32];
+#pragma unroll
+                        for (int c = 0; c < D / 32; ++c) {
+                            tmem_ld32(t_o + c * 32, o);
+                            tc_wait_ld();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st32(t_o + c * 32, o);
                         }
-                        if (r0 + w * kTileRows + rt >= p.q_len) {
-                            // rows past q_len were zero-filled by TMA in the hi tile; the lo tile has to be zero too
-                            if (SPLIT) *reinterpret_cast<uint4 *>(tile + C::kTileBytes + off) = make_uint4(0, 0, 0, 0);
-                            continue;
+                    }
+                    l *= alpha;
+                    if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(2);
+                    // P = exp2(S*c - m) as bf16, written over S; two scores per packed f32x2 FMA
+                    uint64_t c2, nm2, sum2 = 0, sum3 = 0;
+                    {
+                        const float neg_m = -m;
+                        asm("mov.b64 %0, {%1, %1};" : "=l"(nm2) : "f"(neg_m));
+                        asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(c_log2));
+                    }
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t pk[16];
+#pragma unroll
+                        for (int i = 0; i < 32; i += 2) {
+                            uint64_t s2, t2, p2;
+                            asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(r[c * 32 + i]), "r"(r[c * 32 + i + 1]));
+                            asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(t2) : "l"(s2), "l"(c2), "l"(nm2));
+                            float t0, t1;
+                            asm("mov.b64 {%0, %1}, %2;" : "=f"(t0), "=f"(t1) : "l"(t2));
+                            const float p0 = ex2(t0), p1 = ex2(t1);
+                            asm("mov.b64 %0, {%1, %2};" : "=l"(p2) : "f"(p0), "f"(p1));
+                            if (i & 2) asm("add.rn.f32x2 %0, %0, %1;" : "+l"(sum3) : "l"(p2));
+                            else asm("add.rn.f32x2 %0, %0, %1;" : "+l"(sum2) : "l"(p2));
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                            pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                         }
-                        const uint4 raw = *reinterpret_cast<const uint4 *>(tile + off);
-                        const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
-                        uint32_t hi[4], lo[4];
+                        tmem_st16(t_s + c * 16, pk);
+                    }
+                    {
+                        float s0, s1, s2f, s3;
+                        asm("mov.b64 {%0, %1}, %2;" : "=f"(s0), "=f"(s1) : "l"(sum2));
+                        asm("mov.b64 {%0, %1}, %2;" : "=f"(s2f), "=f"(s3) : "l"(sum3));
+                        l += (s0 + s1) + (s2f + s3);
+                    }
+                    if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(3);
+                    tc_wait_st();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(p_full(w));
+                    if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(4);
+                }
+                if ((warp & 3) == 0 && lane == 0) TRACE_FLUSH(w, n - 1);
+            }
+
+            if ((warp & 3) == 0 && lane == 0) TRACEB(k, w, 0);
+            const int next_lin = item_index(p, k + 1);
+            if (p.rope_q_table && next_lin >= 0 && ok) {
+                const WorkItem nx = make_item(p, next_lin);
+                if (nx.n_tiles[w] > 0) {
+                    // Rotate the Q tile in place (fp16), or into bf16 hi / lo tiles.  A warp rotates its 32 rows; lane l
+                    // takes the 16-byte chunk (l mod CH) of row (step * RPS + l / CH), so that the (cos, sin) table is
+                    // read in contiguous row segments.
+                    constexpr int CH = D / 8;     // 16-byte chunks (8 elements, 4 pairs) per row
+                    constexpr int RPS = 32 / CH;  // rows per step of one warp
+                    const int ch = lane % CH;
+                    const int first_row = nx.r0 + w * kTileRows;
+                    // (cos, sin) of the lane's first row come from the table; each further step advances the angle by
+                    // RPS positions with the rotation (cos, sin)(RPS * inv_freq), which keeps the table traffic at two
+                    // 16-byte loads per thread.  The recurrence error (a few 1e-7 over CH steps) is far below the
+                    // rounding of the fp16 / bf16 result.
+                    float cc[4], ss[4], cstep[4], sstep[4];
+                    {
+                        const int rr = min(first_row + lane_base + lane / CH, p.q_len - 1);
+                        const float4 *tp = reinterpret_cast<const float4 *>(p.rope_q_table + (long long)rr * (D / 2)) + 2 * ch;
+                        const float4 cs0 = __ldg(tp), cs1 = __ldg(tp + 1);  // (c, s, c, s) x 2
+                        cc[0] = cs0.x; ss[0] = cs0.y; cc[1] = cs0.z; ss[1] = cs0.w;
+                        cc[2] = cs1.x; ss[2] = cs1.y; cc[3] = cs1.z; ss[3] = cs1.w;
 #pragma unroll
                         for (int e = 0; e < 4; ++e) {
-                            const float x = __uint_as_float(in[e] << 16), y = __uint_as_float(in[e] & 0xffff0000u);
-                            const float rx = x * cc[e] - y * ss[e], ry = x * ss[e] + y * cc[e];
-                            if (SPLIT) {
-                                const __nv_bfloat162 h2 = __floats2bfloat162_rn(rx, ry);
-                                const float2 hf = __bfloat1622float2(h2);
-                                const __nv_bfloat162 l2 = __floats2bfloat162_rn(rx - hf.x, ry - hf.y);
-                                hi[e] = *reinterpret_cast<const uint32_t *>(&h2);
-                                lo[e] = *reinterpret_cast<const uint32_t *>(&l2);
-                            } else {
-                                const __half2 h2 = __floats2half2_rn(rx, ry);
-                                hi[e] = *reinterpret_cast<const uint32_t *>(&h2);
-                            }
+                            const float2 stp = p.rope_step[ch * 4 + e];
+                            cstep[e] = stp.x;
+                            sstep[e] = stp.y;
                         }
-                        *reinterpret_cast<uint4 *>(tile + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                        if (SPLIT) *reinterpret_cast<uint4 *>(tile + C::kTileBytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                     }
+                    // rotations before this one: the finished items plus the current one
+                    if (!mbar_wait(q_full(w), (done + (run ? 1u : 0u)) & 1, abort_flag)) {
+                        record_timeout(p, 290 + w);
+                        ok = false;
+                    }
+                    if ((warp & 3) == 0 && lane == 0) TRACEB(k, w, 1);
+                    if (ok) {
+                        uint8_t *tile = q_s + w * C::kQParts * C::kTileBytes;
+#pragma unroll
+                        for (int st = 0; st < CH; ++st) {
+                            const int rt = lane_base + st * RPS + lane / CH;  // row in tile
+                            const int off = (ch >> 3) * C::kBoxBytes + rt * 128 + (((ch & 7) ^ (rt & 7)) << 4);
+                            if (st > 0) {
+#pragma unroll
+                                for (int e = 0; e < 4; ++e) {
+                                    const float c1 = cc[e] * cstep[e] - ss[e] * sstep[e];
+                                    ss[e] = ss[e] * cstep[e] + cc[e] * sstep[e];
+                                    cc[e] = c1;
+                                }
+                            }
+                            if (first_row + rt >= p.q_len) {
+                                // rows past q_len were zero-filled by TMA in the hi tile; the lo tile has to be zero too
+                                if (SPLIT) *reinterpret_cast<uint4 *>(tile + C::kTileBytes + off) = make_uint4(0, 0, 0, 0);
+                                continue;
+                            }
+                            const uint4 raw = *reinterpret_cast<const uint4 *>(tile + off);
+                            const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+                            uint32_t hi[4], lo[4];
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float x = __uint_as_float(in[e] << 16), y = __uint_as_float(in[e] & 0xffff0000u);
+                                const float rx = x * cc[e] - y * ss[e], ry = x * ss[e] + y * cc[e];
+                                if (SPLIT) {
+                                    const __nv_bfloat162 h2 = __floats2bfloat162_rn(rx, ry);
+                                    const float2 hf = __bfloat1622float2(h2);
+                                    const __nv_bfloat162 l2 = __floats2bfloat162_rn(rx - hf.x, ry - hf.y);
+                                    hi[e] = *reinterpret_cast<const uint32_t *>(&h2);
+                                    lo[e] = *reinterpret_cast<const uint32_t *>(&l2);
+                                } else {
+                                    const __half2 h2 = __floats2half2_rn(rx, ry);
+                                    hi[e] = *reinterpret_cast<const uint32_t *>(&h2);
+                                }
+                            }
+                            *reinterpret_cast<uint4 *>(tile + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                            if (SPLIT)
+                                *reinterpret_cast<uint4 *>(tile + C::kTileBytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                        }
+                    }
+                    fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(q_ready(w));
+                    if ((warp & 3) == 0 && lane == 0) TRACEB(k, w, 2);
                 }
-                fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
-                __syncwarp();
-                if (lane == 0) mbar_arrive(q_ready(w));
-                if (threadIdx.x == 0) TRACE(0, 63, 3);
             }
 
-            long long lim = (long long)p.kv_len - 1;  // last visible key of this row
-            if (p.causal) lim = min(lim, p.causal_off + row);
-            // first row of this Q tile: tiles whose last key is visible to it need no mask for any row
-            long long lim_first = (long long)p.kv_len - 1;
-            if (p.causal) lim_first = min(lim_first, p.causal_off + (long long)(r0 + w * kTileRows));
-            float m = -INFINITY, l = 0.f;
-            const int n = n_tiles[w];
-            const float c_log2 = p.scale_log2;
-            uint64_t c2;
-            asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(c_log2));
-
-            // Online softmax, log2 domain, one thread per row; the whole 128-column score row sits in
-            // registers.  O in TMEM is rescaled only when the running max grew by more than 2^8.
-            TRACE_LOCAL;
-            for (int j = 0; ok && j < n; ++j) {
-                if (!mbar_wait(s_full(w), j & 1, abort_flag)) {
-                    record_timeout(p, 300 + w);
-                    ok = false;
-                    break;
-                }
-                tc_fence_after();
-                if ((warp & 3) == 0 && lane == 0) {
-                    TRACE_FLUSH(w, j - 1);
-                    TRACE_STAMP(0);
-                }
-                const int key0 = j * kTileRows;
-                const bool tile_masked = (long long)key0 + kTileRows - 1 > lim_first;  // uniform over the Q tile
-                const int vis = (int)min((long long)kTileRows, lim - key0 + 1);        // visible columns of this row
-                uint32_t r[128];  // four loads in flight, one wait
-#pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, r + c * 32);
-                tc_wait_ld();
-                if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(1);
-                if (tile_masked) {
-#pragma unroll
-                    for (int i = 0; i < 128; ++i)
-                        if (i >= vis) r[i] = 0xff800000u;  // -inf: exp2 gives exactly 0
-                }
-                float mx = -INFINITY, mx1 = -INFINITY;  // two chains for instruction-level parallelism
-#pragma unroll
-                for (int i = 0; i < 128; i += 4) {
-                    asm("max.f32 %0, %0, %1, %2;" : "+f"(mx) : "f"(__uint_as_float(r[i])), "f"(__uint_as_float(r[i + 1])));
-                    asm("max.f32 %0, %0, %1, %2;" : "+f"(mx1) : "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3])));
-                }
-                const float m_cand = fmaxf(m, fmaxf(mx, mx1) * c_log2);
-                const bool grow = (m_cand - m) > kRescaleThreshold;
-                float alpha = 1.0f;
-                if (grow) {
-                    alpha = ex2(m - m_cand);
-                    m = m_cand;
-                }
-                if (j > 0 && __any_sync(0xffffffffu, grow)) {
-                    uint32_t o[32];
-#pragma unroll
-                    for (int c = 0; c < D / 32; ++c) {
-                        tmem_ld32(t_o + c * 32, o);
-                        tc_wait_ld();
-#pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                        tmem_st32(t_o + c * 32, o);
-                    }
-                }
-                l *= alpha;
-                if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(2);
-                // P = exp2(S*c - m) as bf16, written over S; two scores per packed f32x2 FMA
-                uint64_t nm2, sum2 = 0, sum3 = 0;
-                {
-                    const float neg_m = -m;
-                    asm("mov.b64 %0, {%1, %1};" : "=l"(nm2) : "f"(neg_m));
-                }
-#pragma unroll
-                for (int c = 0; c < 4; ++c) {
-                    uint32_t pk[16];
-#pragma unroll
-                    for (int i = 0; i < 32; i += 2) {
-                        uint64_t s2, t2, p2;
-                        asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(r[c * 32 + i]), "r"(r[c * 32 + i + 1]));
-                        asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(t2) : "l"(s2), "l"(c2), "l"(nm2));
-                        float t0, t1;
-                        asm("mov.b64 {%0, %1}, %2;" : "=f"(t0), "=f"(t1) : "l"(t2));
-                        const float p0 = ex2(t0), p1 = ex2(t1);
-                        asm("mov.b64 %0, {%1, %2};" : "=l"(p2) : "f"(p0), "f"(p1));
-                        if (i & 2) asm("add.rn.f32x2 %0, %0, %1;" : "+l"(sum3) : "l"(p2));
-                        else asm("add.rn.f32x2 %0, %0, %1;" : "+l"(sum2) : "l"(p2));
-                        __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-                        pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
-                    }
-                    tmem_st16(t_s + c * 16, pk);
-                }
-                {
-                    float s0, s1, s2f, s3;
-                    asm("mov.b64 {%0, %1}, %2;" : "=f"(s0), "=f"(s1) : "l"(sum2));
-                    asm("mov.b64 {%0, %1}, %2;" : "=f"(s2f), "=f"(s3) : "l"(sum3));
-                    l += (s0 + s1) + (s2f + s3);
-                }
-                if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(3);
-                tc_wait_st();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(p_full(w));
-                if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(4);
-            }
-            if ((warp & 3) == 0 && lane == 0) TRACE_FLUSH(w, n - 1);
-            if (ok) {
-                if (!mbar_wait(o_final(w), 0, abort_flag)) {
+            if (run && ok) {
+                if (!mbar_wait(o_final(w), done & 1, abort_flag)) {
                     record_timeout(p, 310 + w);
                     ok = false;
                 }
+                ++done;
             }
-            if (ok) {
+            if ((warp & 3) == 0 && lane == 0) TRACEB(k, w, 3);
+            if (run && ok) {
                 tc_fence_after();
-                if (threadIdx.x == 0) TRACE(0, 63, 5);
+                const WorkItem it = make_item(p, item_index(p, k));
+                const int row = it.r0 + w * kTileRows + row_in_tile, b = it.b, h = it.h;
                 const float inv = 1.0f / l;
                 const bool store = row < p.q_len;
                 __nv_bfloat16 *op = reinterpret_cast<__nv_bfloat16 *>(p.o) + (long long)b * p.o_bs + (long long)h * p.o_hs +
@@ -540,8 +629,12 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     }
                 }
                 if (store) p.lse[((long long)b * p.q_heads + h) * p.lse_hs + row] = (m + log2f(l)) * kLn2;
-                if (threadIdx.x == 0) TRACE(0, 63, 6);
+                // the O columns are overwritten by the next item's first PV MMA, which is issued only after this
+                // thread's next hand-over of P: program order keeps the reads above ahead of it
+                tc_fence_before();
             }
+            if ((warp & 3) == 0 && lane == 0) TRACEB(k, w, 4);
+            if (next_lin < 0) break;
         }
     }
 
@@ -719,12 +812,15 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     if (const char *tp = getenv("FLAT_TRACE_PTR")) kp.trace = reinterpret_cast<long long *>(strtoull(tp, nullptr, 0));
 #endif
 
-    const long long grid = (long long)kp.q_blocks * p.batch * p.q_heads;
-    if (grid > 2147483647LL) return fail(ctx, FLAT_ERR_DISPATCH_LIMIT, "forward grid of %lld blocks is too large", grid);
+    // Persistent launch: one CTA per SM walks its share of the (query block, batch, head) items.
+    kp.total_items = (long long)kp.q_blocks * p.batch * p.q_heads;
+    if (kp.total_items > 2147483647LL)
+        return fail(ctx, FLAT_ERR_DISPATCH_LIMIT, "forward grid of %lld blocks is too large", kp.total_items);
+    const unsigned grid = (unsigned)std::min<long long>(kp.total_items, ctx->sm_count);
     auto run = [&](auto kernel, int smem_bytes) -> int {
         FLAT_CUDA_OK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         KernelTimer timer(ctx);
-        kernel<<<(unsigned)grid, kThreads, smem_bytes, ctx->stream>>>(kp);
+        kernel<<<grid, kThreads, smem_bytes, ctx->stream>>>(kp);
         return FLAT_OK;
     };
     if (D == 128) st = split ? run(fwd_sm100_kernel<128, true>, Cfg<128, true>::kSmemBytes)

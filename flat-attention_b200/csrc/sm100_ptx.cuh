@@ -57,18 +57,18 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t par
     return ok != 0;
 }
 
-// Bounded wait: gives up after `kWaitCycles` clock cycles, or as soon as another thread of the CTA
+// Bounded wait: gives up after `kWaitCycles` clock cycles (about a second), or as soon as another thread of the CTA
 // has given up (`*abort_flag != 0`).  Returns false on give-up; the caller records where and
 // leaves its loop, so the kernel always terminates and the context stays usable.
-constexpr long long kWaitCycles = 4000000000LL;  // about two seconds
-constexpr uint32_t kSuspendNs = 20000;           // one suspended poll lasts at most 20 us
+constexpr uint32_t kWaitCycles = 2000000000u;  // about one second (32-bit cycle counter, wrap-safe difference)
+constexpr uint32_t kSuspendNs = 20000;         // one suspended poll lasts at most 20 us
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
-    const long long start = clock64();
+    const uint32_t start = (uint32_t)clock();
     for (;;) {
         if (mbar_try_wait_suspend(bar, parity, kSuspendNs)) return true;
         if (*abort_flag != 0) return false;
-        if (clock64() - start > kWaitCycles) {
+        if ((uint32_t)clock() - start > kWaitCycles) {
             *abort_flag = 1;
             return false;
         }
@@ -129,6 +129,36 @@ __device__ __forceinline__ void mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_
         "setp.ne.b32 p, %4, 0;\n"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
         "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// The same with descriptor = base + offset formed inside the asm block (offset in 16-byte units, added to the
+// start-address field): an unrolled issue sequence then keeps only the base descriptors in registers.
+__device__ __forceinline__ void mma_ss_off(uint32_t d_tmem, uint64_t a_base, uint64_t b_base, uint32_t off16, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .b64 da, db, o;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "cvt.u64.u32 o, %5;\n"
+        "add.s64 da, %1, o;\n"
+        "add.s64 db, %2, o;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "l"(a_base), "l"(b_base), "r"(idesc), "r"(accumulate), "r"(off16)
+        : "memory");
+}
+__device__ __forceinline__ void mma_ts_off(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_base, uint32_t off16, uint32_t idesc,
+                                           uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        ".reg .b64 db, o;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "cvt.u64.u32 o, %5;\n"
+        "add.s64 db, %2, o;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %3, p;\n"
+        "}\n" ::"r"(d_tmem), "r"(a_tmem), "l"(b_base), "r"(idesc), "r"(accumulate), "r"(off16)
         : "memory");
 }
 
