@@ -69,7 +69,7 @@ template <int D> struct BCfg {
     static constexpr int kTileBytes = kBoxes * kBoxBytes;
     static constexpr int kStageBytes = 2 * kTileBytes + 1024;  // two tiles + 128 f32 lse + 128 f32 delta
     static constexpr int kStages = D == 128 ? 2 : 4;
-    static constexpr int kBars = 1 + 2 * kStages + 3;
+    static constexpr int kBars = 2 * kStages + 10;  // enough for either kernel's barrier set
     static constexpr int kSmemBytes = 2 * kTileBytes + kStages * kStageBytes + kBars * 8 + 16 + 1024;
 };
 
@@ -369,6 +369,306 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
     }
 }
 
+// Q-stationary dQ kernel, pipelined.  One CTA owns 128 queries of one (batch, q_head); (K_j, V_j) tiles stream
+// through a three-stage TMA ring.  Q is copied once from shared memory into TMEM and is the A operand of every
+// S MMA; dO stays in shared memory.  The bf16 dS tile has TMEM columns of its own, so the score buffers are
+// free again as soon as the elementwise warps have loaded them into registers, and the tensor pipe computes the
+// next tile's scores while those warps work on the current one:
+//   S = Q K_j^T (TS MMA), dP = dO V_j^T (SS MMA)  ->  dS = exp2(S c - lse) * (dP - delta) as bf16
+//   ->  dQ += dS K_j (TS MMA).
+// TMEM columns: Q [0, 64), S [64, 192), dP [192, 320), dS [320, 384), dQ [384, 384 + D).
+template <int D> struct DqCfg {
+    static constexpr int kBoxes = D / 64;
+    static constexpr int kBoxBytes = kTile * 128;
+    static constexpr int kTileBytes = kBoxes * kBoxBytes;
+    static constexpr int kStageBytes = 2 * kTileBytes;  // K tile + V tile
+    static constexpr int kStages = 3;
+    static constexpr int kBars = 2 * kStages + 7;
+    static constexpr int kSmemBytes = kTileBytes + kStages * kStageBytes + kBars * 8 + 16 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(kThreads, 1) bwd_dq_sm100_kernel(const __grid_constant__ BwdKernelParams p) {
+    using C = DqCfg<D>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t *do_s = smem;                   // dO tile
+    uint8_t *ring = smem + C::kTileBytes;   // the Q tile passes through the last stage's space on its way to TMEM
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ring + C::kStages * C::kStageBytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + C::kBars);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    auto stage_ptr = [&](int s) { return ring + s * C::kStageBytes; };
+    uint8_t *q_s = stage_ptr(C::kStages - 1);
+
+    const uint32_t bar0 = smem_u32(bars);
+    const uint32_t st_full = bar0;
+    auto rg_full = [&](int s) { return bar0 + 8u * (1 + s); };
+    auto rg_empty = [&](int s) { return bar0 + 8u * (1 + C::kStages + s); };
+    const uint32_t xy_full = bar0 + 8u * (1 + 2 * C::kStages);   // S and dP of a tile are in TMEM
+    const uint32_t xy_taken = bar0 + 8u * (2 + 2 * C::kStages);  // ... and have been loaded into registers
+    const uint32_t ds_full = bar0 + 8u * (3 + 2 * C::kStages);   // bf16 dS written
+    const uint32_t ds_free = bar0 + 8u * (4 + 2 * C::kStages);   // ... and consumed by the dQ MMAs
+    const uint32_t acc_final = bar0 + 8u * (5 + 2 * C::kStages);
+    const uint32_t a_ready = bar0 + 8u * (6 + 2 * C::kStages);   // Q is in TMEM
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // block -> (query tile, head, batch); late query tiles see the most keys and go first
+    const int lin = blockIdx.x;
+    const int tile_rank = lin / (p.q_heads * p.batch);
+    const int bh = lin % (p.q_heads * p.batch);
+    const int b = bh / p.q_heads, h = bh % p.q_heads;
+    const int t_own = p.causal ? p.n_tiles - 1 - tile_rank : tile_rank;
+    const int n_iter = p.causal ? t_own + 1 : p.n_tiles;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        mbar_init(st_full, 1);
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(rg_full(s), 1);
+            mbar_init(rg_empty(s), 1);
+        }
+        mbar_init(xy_full, 1);
+        mbar_init(xy_taken, 8);
+        mbar_init(ds_full, 8);
+        mbar_init(ds_free, 1);
+        mbar_init(acc_final, 1);
+        mbar_init(a_ready, 8);
+        mbar_fence_init();
+        fence_proxy_async();
+    }
+    if (warp == kMmaWarp) {
+        tmem_alloc(smem_u32(tmem_slot), 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    constexpr uint32_t kColQ = 0, kColX = 64, kColY = 192, kColDS = 320, kColAcc = 384;
+
+    if (warp >= 8) {
+        // 72 x 128 + 216 x 256 registers: exactly the CTA's launch allocation of 168 x 384
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
+        if (warp == kProducerWarp && lane == 0) {
+            // ================= TMA producer =================
+            mbar_expect_tx(st_full, 2 * C::kTileBytes);
+            for (int kb = 0; kb < C::kBoxes; ++kb) {
+                tma_load_4d(smem_u32(q_s + kb * C::kBoxBytes), &p.map_q, kb * 64, t_own * kTile, h, b, st_full);
+                tma_load_4d(smem_u32(do_s + kb * C::kBoxBytes), &p.map_do, kb * 64, t_own * kTile, h, b, st_full);
+            }
+            const int hs = h / p.group;
+            for (int it = 0; it < n_iter; ++it) {
+                const int s = it % C::kStages;
+                const uint32_t phase = (it / C::kStages) & 1;
+                if (!mbar_wait(rg_empty(s), phase ^ 1, abort_flag)) {
+                    timeout(p, 100 + s);
+                    break;
+                }
+                if (it == C::kStages - 1 && !mbar_wait(a_ready, 0, abort_flag)) {  // the Q tile has left this space
+                    timeout(p, 110);
+                    break;
+                }
+                uint8_t *stage = stage_ptr(s);
+                mbar_expect_tx(rg_full(s), C::kStageBytes);
+                for (int kb = 0; kb < C::kBoxes; ++kb) {
+                    tma_load_4d(smem_u32(stage + kb * C::kBoxBytes), &p.map_k, kb * 64, it * kTile, hs, b, rg_full(s));
+                    tma_load_4d(smem_u32(stage + C::kTileBytes + kb * C::kBoxBytes), &p.map_v, kb * 64, it * kTile, hs, b,
+                                rg_full(s));
+                }
+            }
+        } else if (warp == kMmaWarp && lane == 0) {
+            // ================= MMA issuer =================
+            bool ok = true;
+            auto wait = [&](uint32_t bar, uint32_t parity, int where) {
+                if (!ok) return;
+                if (!mbar_wait(bar, parity, abort_flag)) {
+                    timeout(p, where);
+                    ok = false;
+                }
+            };
+            const uint64_t do_desc = make_smem_desc(smem_u32(do_s), 0, 1024);
+            auto issue_xy = [&](const uint8_t *stage) {
+                const uint64_t bk = make_smem_desc(smem_u32(stage), 0, 1024);
+                const uint64_t bv = make_smem_desc(smem_u32(stage + C::kTileBytes), 0, 1024);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk)  // S = Q K^T, A from TMEM
+                    mma_ts_off(tmem_base + kColX, tmem_base + kColQ + kk * 8, bk,
+                               (kk >> 2) * (C::kBoxBytes >> 4) + (kk & 3) * 2, p.idesc_k, kk > 0);
+#pragma unroll
+                for (int kk = 0; kk < D / 16; ++kk)  // dP = dO V^T, both operands K-major tiles in shared memory
+                    mma_ss_off(tmem_base + kColY, do_desc, bv, (kk >> 2) * (C::kBoxBytes >> 4) + (kk & 3) * 2, p.idesc_k,
+                               kk > 0);
+            };
+            // dQ (+)= dS[tmem, 128 x 128 bf16] * K[smem tile as MN-major B, 128 x D]
+            auto issue_acc = [&](const uint8_t *stage, bool accumulate) {
+                const uint64_t bk = make_smem_desc(smem_u32(stage), C::kBoxBytes, 1024);
+#pragma unroll
+                for (int kk = 0; kk < kTile / 16; ++kk)
+                    mma_ts_off(tmem_base + kColAcc, tmem_base + kColDS + kk * 8, bk, kk * (16 * 128 >> 4), p.idesc_mn,
+                               (accumulate || kk > 0));
+            };
+            wait(a_ready, 0, 200);
+            wait(rg_full(0), 0, 210);
+            if (ok) {
+                tc_fence_after();
+                issue_xy(stage_ptr(0));
+                tc_commit(xy_full);
+            }
+            for (int it = 0; ok && it < n_iter; ++it) {
+                const int s = it % C::kStages;
+                TRACE(2, it, 0);
+                if (it + 1 < n_iter) {
+                    // the next tile's scores, as soon as the current ones sit in the elementwise warps' registers
+                    const int sn = (it + 1) % C::kStages;
+                    wait(xy_taken, it & 1, 220);
+                    wait(rg_full(sn), ((it + 1) / C::kStages) & 1, 230);
+                    if (!ok) break;
+                    TRACE(2, it, 1);
+                    tc_fence_after();
+                    issue_xy(stage_ptr(sn));
+                    tc_commit(xy_full);
+                    TRACE(2, it, 2);
+                }
+                wait(ds_full, it & 1, 240);
+                if (!ok) break;
+                TRACE(2, it, 3);
+                tc_fence_after();
+                issue_acc(stage_ptr(s), it > 0);
+                tc_commit(ds_free);
+                tc_commit(rg_empty(s));
+                TRACE(2, it, 4);
+            }
+            if (ok) tc_commit(acc_final);
+        }
+    } else {
+        // ================= elementwise warps + epilogue =================
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        const int half = warp >> 2;                  // which 64 of the tile's 128 key columns
+        const int lane_base = (warp & 3) * 32;
+        const int row_local = lane_base + lane;      // TMEM lane = query
+        const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16);
+        bool ok = true;
+
+        // Q rows from the swizzled TMA tile into TMEM: lane = row, 32-bit column c holds elements 2c, 2c + 1 (the
+        // layout of an A operand); warp group `half` copies the 64-element box `half`
+        if (!mbar_wait(st_full, 0, abort_flag)) {
+            timeout(p, 290);
+            ok = false;
+        }
+        if (ok && half < C::kBoxes) {
+            uint32_t v[32];
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(q_s + half * C::kBoxBytes + row_local * 128 +
+                                                                   ((ch ^ (row_local & 7)) << 4));
+                v[ch * 4] = raw.x; v[ch * 4 + 1] = raw.y; v[ch * 4 + 2] = raw.z; v[ch * 4 + 3] = raw.w;
+            }
+            tmem_st32(t_lane + kColQ + half * 32, v);
+            tc_wait_st();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(a_ready);
+
+        uint64_t c2, nl2, dl2;
+        {
+            const long long row = ((long long)b * p.q_heads + h) * p.seq_len + (long long)t_own * kTile + row_local;
+            const float my_neg_lse2 = p.neg_lse2[row], my_delta = p.delta[row];
+            asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(p.scale_log2));
+            asm("mov.b64 %0, {%1, %1};" : "=l"(nl2) : "f"(my_neg_lse2));
+            asm("mov.b64 %0, {%1, %1};" : "=l"(dl2) : "f"(my_delta));
+        }
+        const uint32_t t_x = t_lane + kColX + half * 64, t_y = t_lane + kColY + half * 64;
+        for (int it = 0; ok && it < n_iter; ++it) {
+            if (!mbar_wait(xy_full, it & 1, abort_flag)) {
+                timeout(p, 310);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            if (warp == 0 && lane == 0) TRACE(0, it, 0);
+            const bool diag = p.causal && it == t_own;
+            uint32_t x[64], y[64];
+            tmem_ld32(t_x, x);
+            tmem_ld32(t_x + 32, x + 32);
+            tmem_ld32(t_y, y);
+            tmem_ld32(t_y + 32, y + 32);
+            tc_wait_ld();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(xy_taken);  // the score buffers may be overwritten
+            if (warp == 0 && lane == 0) TRACE(0, it, 1);
+            uint32_t ds[32];
+#pragma unroll
+            for (int i = 0; i < 64; i += 2) {
+                uint64_t s2, t2, y2, d2;
+                asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(x[i]), "r"(x[i + 1]));
+                asm("mov.b64 %0, {%1, %2};" : "=l"(y2) : "r"(y[i]), "r"(y[i + 1]));
+                asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(t2) : "l"(s2), "l"(c2), "l"(nl2));
+                asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d2) : "l"(y2), "l"(dl2));
+                float t0, t1, e0, e1;
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(t0), "=f"(t1) : "l"(t2));
+                asm("mov.b64 {%0, %1}, %2;" : "=f"(e0), "=f"(e1) : "l"(d2));
+                float p0 = ex2(t0), p1 = ex2(t1);
+                if (diag) {  // visible iff key <= query: row = query, column = key
+                    const int c0 = half * 64 + i;
+                    if (c0 > row_local) p0 = 0.f;
+                    if (c0 + 1 > row_local) p1 = 0.f;
+                }
+                const __nv_bfloat162 dsb = __floats2bfloat162_rn(p0 * e0, p1 * e1);
+                ds[i >> 1] = *reinterpret_cast<const uint32_t *>(&dsb);
+            }
+            if (warp == 0 && lane == 0) TRACE(0, it, 2);
+            if (it > 0 && !mbar_wait(ds_free, (it - 1) & 1, abort_flag)) {  // the dQ MMAs of the previous tile read dS
+                timeout(p, 315);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            tmem_st32(t_lane + kColDS + half * 32, ds);  // this group's 64 keys = 32 columns
+            tc_wait_st();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ds_full);
+            if (warp == 0 && lane == 0) TRACE(0, it, 3);
+        }
+        if (ok && !mbar_wait(acc_final, 0, abort_flag)) {
+            timeout(p, 320);
+            ok = false;
+        }
+        if (ok) {
+            tc_fence_after();
+            // each warp group writes half of the head dimension of the accumulator rows
+            const long long out_row = ((long long)b * p.q_heads + h) * p.seq_len + (long long)t_own * kTile + row_local;
+            constexpr int kColsPerHalf = D / 2;
+            float *op = reinterpret_cast<float *>(p.out0) + out_row * D + half * kColsPerHalf;
+            const uint32_t t_acc = t_lane + kColAcc + half * kColsPerHalf;
+#pragma unroll
+            for (int c = 0; c < kColsPerHalf / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(t_acc + c * 32, r);
+                tc_wait_ld();
+                float4 *dst = reinterpret_cast<float4 *>(op + c * 32);
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4)
+                    dst[q4] = make_float4(__uint_as_float(r[q4 * 4]) * p.scale, __uint_as_float(r[q4 * 4 + 1]) * p.scale,
+                                          __uint_as_float(r[q4 * 4 + 2]) * p.scale, __uint_as_float(r[q4 * 4 + 3]) * p.scale);
+            }
+        }
+    }
+
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);  // let copies in flight land before the CTA exits
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
 // delta = dO . O and -LSE*log2(e), one warp per row
 __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16 *__restrict__ d_out,
                                                        const __nv_bfloat16 *__restrict__ out, const float *__restrict__ lse,
@@ -456,8 +756,8 @@ int launch_backward_sm100(flat_ctx *ctx, const BwdParams &p) {
     if (st) return st;
     kp.out0 = p.dq;
     kp.out1 = nullptr;
-    if (D == 128) st = run(bwd_sm100_kernel<128, false>, BCfg<128>::kSmemBytes, grid_q);
-    else st = run(bwd_sm100_kernel<64, false>, BCfg<64>::kSmemBytes, grid_q);
+    if (D == 128) st = run(bwd_dq_sm100_kernel<128>, DqCfg<128>::kSmemBytes, grid_q);
+    else st = run(bwd_dq_sm100_kernel<64>, DqCfg<64>::kSmemBytes, grid_q);
     if (st) return st;
     ctx->launches += 2;
     FLAT_CUDA_OK(ctx, cudaGetLastError());
