@@ -384,7 +384,12 @@ template <int D> struct DqCfg {
     static constexpr int kStageBytes = 2 * kTileBytes;  // K tile + V tile
     static constexpr int kStages = 3;
     static constexpr int kBars = 2 * kStages + 7;
-    static constexpr int kSmemBytes = kTileBytes + kStages * kStageBytes + kBars * 8 + 16 + 1024;
+#ifdef FLAT_TRACE
+    static constexpr int kTraceBytes = 32 * 8 * 4;
+#else
+    static constexpr int kTraceBytes = 0;
+#endif
+    static constexpr int kSmemBytes = kTileBytes + kStages * kStageBytes + kBars * 8 + 16 + kTraceBytes + 1024;
 };
 
 template <int D>
@@ -397,6 +402,12 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_sm100_kernel(const __grid_
     uint64_t *bars = reinterpret_cast<uint64_t *>(ring + C::kStages * C::kStageBytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + C::kBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+#ifdef FLAT_TRACE
+    volatile uint32_t *tr_s = reinterpret_cast<volatile uint32_t *>(tmem_slot + 4);
+#define TRS(it, slot) do { if ((it) < 32) tr_s[(it) * 8 + (slot)] = (uint32_t)clock(); } while (0)
+#else
+#define TRS(it, slot) do { } while (0)
+#endif
     auto stage_ptr = [&](int s) { return ring + s * C::kStageBytes; };
     uint8_t *q_s = stage_ptr(C::kStages - 1);
 
@@ -491,14 +502,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_sm100_kernel(const __grid_
             auto issue_xy = [&](const uint8_t *stage) {
                 const uint64_t bk = make_smem_desc(smem_u32(stage), 0, 1024);
                 const uint64_t bv = make_smem_desc(smem_u32(stage + C::kTileBytes), 0, 1024);
+                // the two products alternate, so that consecutive MMAs never wait on the same accumulator
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk)  // S = Q K^T, A from TMEM
-                    mma_ts_off(tmem_base + kColX, tmem_base + kColQ + kk * 8, bk,
-                               (kk >> 2) * (C::kBoxBytes >> 4) + (kk & 3) * 2, p.idesc_k, kk > 0);
-#pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk)  // dP = dO V^T, both operands K-major tiles in shared memory
-                    mma_ss_off(tmem_base + kColY, do_desc, bv, (kk >> 2) * (C::kBoxBytes >> 4) + (kk & 3) * 2, p.idesc_k,
-                               kk > 0);
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off16 = (kk >> 2) * (C::kBoxBytes >> 4) + (kk & 3) * 2;
+                    mma_ts_off(tmem_base + kColX, tmem_base + kColQ + kk * 8, bk, off16, p.idesc_k, kk > 0);  // S = Q K^T
+                    mma_ss_off(tmem_base + kColY, do_desc, bv, off16, p.idesc_k, kk > 0);                      // dP = dO V^T
+                }
             };
             // dQ (+)= dS[tmem, 128 x 128 bf16] * K[smem tile as MN-major B, 128 x D]
             auto issue_acc = [&](const uint8_t *stage, bool accumulate) {
@@ -517,27 +527,27 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_sm100_kernel(const __grid_
             }
             for (int it = 0; ok && it < n_iter; ++it) {
                 const int s = it % C::kStages;
-                TRACE(2, it, 0);
+                TRS(it, 0);
                 if (it + 1 < n_iter) {
                     // the next tile's scores, as soon as the current ones sit in the elementwise warps' registers
                     const int sn = (it + 1) % C::kStages;
                     wait(xy_taken, it & 1, 220);
                     wait(rg_full(sn), ((it + 1) / C::kStages) & 1, 230);
                     if (!ok) break;
-                    TRACE(2, it, 1);
+                    TRS(it, 1);
                     tc_fence_after();
                     issue_xy(stage_ptr(sn));
                     tc_commit(xy_full);
-                    TRACE(2, it, 2);
+                    TRS(it, 2);
                 }
                 wait(ds_full, it & 1, 240);
                 if (!ok) break;
-                TRACE(2, it, 3);
+                TRS(it, 3);
                 tc_fence_after();
                 issue_acc(stage_ptr(s), it > 0);
                 tc_commit(ds_free);
                 tc_commit(rg_empty(s));
-                TRACE(2, it, 4);
+                TRS(it, 4);
             }
             if (ok) tc_commit(acc_final);
         }
@@ -663,11 +673,16 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_sm100_kernel(const __grid_
     }
     tc_fence_before();
     __syncthreads();
+#ifdef FLAT_TRACE
+    if (p.trace && blockIdx.x == 0)
+        for (int i = threadIdx.x; i < 32 * 8; i += kThreads) p.trace[2 * 64 * 8 + i] = tr_s[i];
+#endif
     if (warp == kMmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
 }
+#undef TRS
 
 // delta = dO . O and -LSE*log2(e), one warp per row
 __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16 *__restrict__ d_out,
