@@ -6,7 +6,7 @@
 //   warps 0-3  softmax of Q tile 0 : thread t owns query row t (TMEM lane t), no shuffles
 //   warps 4-7  softmax of Q tile 1
 //   warp  8    TMA producer        : Q tiles once, then K_j, V_j through an mbarrier ring
-//   warps 9,10 MMA issuers         : one thread per Q tile issues its tcgen05.mma and tcgen05.commit
+//   warp  9    MMA issuer          : one thread issues every tcgen05.mma and tcgen05.commit
 // Per KV tile j and Q tile w:  S_w = Q_w K_j^T (SS MMA, f32 in TMEM)  ->  softmax warps read S_w
 // from TMEM, track the running max (rescaling O_w in TMEM only when the max grows by more than
 // 2^8), write P_w = exp2(S_w*c - m) as bf16 over S_w  ->  O_w += P_w V_j (A operand from TMEM).
@@ -191,7 +191,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
         }
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(kv_full(s), 1);
-            mbar_init(kv_empty(s), 2);  // one arrival per Q slot
+            mbar_init(kv_empty(s), 1);
         }
         mbar_fence_init();
         fence_proxy_async();
@@ -207,8 +207,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    auto col_s = [](int w) { return 128u * (uint32_t)w; };             // S / P of slot w
-    auto col_o = [](int w) { return 256u + (uint32_t)D * (uint32_t)w; };  // O of slot w
+    const uint32_t col_s[2] = {0u, 128u};
+    const uint32_t col_o[2] = {256u, 256u + D};
 
     // Register rebalancing: a softmax thread holds a whole 128-column score row in registers.  The pool that
     // setmaxnreg.inc draws from is what the CTA was launched with (168 registers x 384 threads), not the whole
@@ -272,14 +272,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                 }
             }
         }
-    } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
-        // ================= MMA issuers =================
-        // One issuing thread per Q slot (warp 9 lane 0: slot 0, warp 10 lane 0: slot 1).  Each walks its slot's
-        // tiles in order; the tensor pipe serialises the two instruction streams.  The slots are coupled only
-        // through the K/V ring: an entry is free after two arrivals, one per slot (tcgen05.commit after the slot's
-        // last MMA on it, or a plain arrive when the slot does not visit the tile).
+    } else if (warp == kMmaWarp) {
+        // ================= MMA issuer =================
         if (lane == 0) {
-            const int w = warp - kMmaWarp;
             bool ok = true;
             auto wait = [&](uint32_t bar, uint32_t parity, int where) {
                 if (!ok) return;
@@ -291,7 +286,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             // The issue loops are unrolled (a rolled loop's dependent instructions cost 100+ cycles per MMA on this
             // single thread, more than the tensor pipe needs), and each descriptor is the tile's base descriptor plus
             // a compile-time constant, which keeps the thread inside its small register budget.
-            auto issue_s = [&](int stage) {
+            auto issue_s = [&](int w, int stage) {
                 const uint64_t b_desc = make_smem_desc(smem_u32(kv_s + stage * C::kTileBytes), 0, 1024);
 #pragma unroll
                 for (int part = 0; part < C::kQParts; ++part) {
@@ -299,20 +294,20 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
 #pragma unroll
                     for (int kk = 0; kk < D / 16; ++kk) {
                         const uint32_t off16 = (kk >> 2) * (C::kBoxBytes >> 4) + (kk & 3) * 2;  // byte offset / 16
-                        mma_ss_off(tmem_base + col_s(w), a_desc, b_desc, off16, p.idesc_qk, (part > 0 || kk > 0));
+                        mma_ss_off(tmem_base + col_s[w], a_desc, b_desc, off16, p.idesc_qk, (part > 0 || kk > 0));
                     }
                 }
             };
-            auto issue_pv = [&](int stage, int j) {
+            auto issue_pv = [&](int w, int stage, int j) {
                 const uint64_t b_desc = make_smem_desc(smem_u32(kv_s + stage * C::kTileBytes), C::kBoxBytes, 1024);
 #pragma unroll
                 for (int kk = 0; kk < kTileRows / 16; ++kk)
-                    mma_ts_off(tmem_base + col_o(w), tmem_base + col_s(w) + kk * 8, b_desc, kk * (16 * 128 >> 4), p.idesc_pv,
+                    mma_ts_off(tmem_base + col_o[w], tmem_base + col_s[w] + kk * 8, b_desc, kk * (16 * 128 >> 4), p.idesc_pv,
                                (j > 0 || kk > 0));
             };
-            uint32_t ring0 = 0;   // ring entry of K_0 of the current item
-            uint32_t q_uses = 0;  // Q tiles of this slot consumed so far
-            uint32_t p_waits = 0; // P hand-overs consumed so far
+            uint32_t ring0 = 0;           // ring entry of K_0 of the current item
+            uint32_t q_uses[2] = {0, 0};  // Q tiles consumed so far, per slot
+            uint32_t p_waits[2] = {0, 0}; // P hand-overs consumed so far, per slot
             auto stage_of = [&](uint32_t i) { return (int)((ring0 + i) % C::kStages); };
             auto phase_of = [&](uint32_t i) { return (uint32_t)(((ring0 + i) / C::kStages) & 1); };
 
@@ -320,54 +315,64 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                 const int lin = item_index(p, k);
                 if (lin < 0) break;
                 const WorkItem it = make_item(p, lin);
-                const int n = it.n_tiles[w];
-                const uint32_t entries = 2u * (uint32_t)max(it.n_tiles[0], it.n_tiles[1]);
+                const int n_max = max(it.n_tiles[0], it.n_tiles[1]);
                 const bool trace_item = k == 0;
                 (void)trace_item;
-                if (n > 0) {
-                    TRACEB(k, 2, w * 4 + 0);
-                    wait(p.rope_q_table ? q_ready(w) : q_full(w), q_uses & 1, 200 + w);
-                    ++q_uses;
-                    TRACEB(k, 2, w * 4 + 1);
-                    wait(kv_full(stage_of(0)), phase_of(0), 210);
+                TRACEB(k, 2, 0);
+                // prologue: S_w(0) as soon as the slot's Q tile is ready (the other slot may still be finishing the
+                // previous item)
+                bool k0_ready = false;
+                for (int w = 0; w < 2 && ok; ++w) {
+                    if (it.n_tiles[w] == 0) continue;
+                    wait(p.rope_q_table ? q_ready(w) : q_full(w), q_uses[w] & 1, 200 + w);
+                    ++q_uses[w];
+                    TRACEB(k, 2, 1 + w);
+                    if (!k0_ready) {
+                        wait(kv_full(stage_of(0)), phase_of(0), 210);
+                        k0_ready = true;
+                    }
                     if (!ok) break;
                     tc_fence_after();
-                    issue_s(stage_of(0));
+                    issue_s(w, stage_of(0));
                     tc_commit(s_full(w));
-                    if (n == 1) tc_commit(q_empty(w));  // the slot's last S of this item
+                    if (it.n_tiles[w] == 1) tc_commit(q_empty(w));  // the slot's last S of this item
+                }
+                if (ok) {
                     tc_commit(kv_empty(stage_of(0)));
-                    for (int j = 0; ok && j < n; ++j) {
-                        const uint32_t iv = 2 * j + 1, ik = 2 * j + 2;
-                        wait(kv_full(stage_of(iv)), phase_of(iv), 220);
-                        wait(p_full(w), p_waits & 1, 230 + w);
+                    TRACEB(k, 2, 3);
+                }
+                for (int j = 0; ok && j < n_max; ++j) {
+                    const uint32_t iv = 2 * j + 1, ik = 2 * j + 2;
+                    wait(kv_full(stage_of(iv)), phase_of(iv), 220);
+                    bool k_ready = false;
+                    for (int w = 0; w < 2 && ok; ++w) {
+                        if (j >= it.n_tiles[w]) continue;
+                        wait(p_full(w), p_waits[w] & 1, 230 + w);
                         if (!ok) break;
-                        ++p_waits;
+                        ++p_waits[w];
                         TRACE(2, j, w * 4 + 0);
                         tc_fence_after();
-                        issue_pv(stage_of(iv), j);
-                        tc_commit(kv_empty(stage_of(iv)));
+                        issue_pv(w, stage_of(iv), j);
                         TRACE(2, j, w * 4 + 1);
-                        if (j + 1 < n) {
-                            wait(kv_full(stage_of(ik)), phase_of(ik), 240);
-                            if (!ok) break;
-                            tc_fence_after();
-                            issue_s(stage_of(ik));
+                        if (w == 1 || j >= it.n_tiles[1]) tc_commit(kv_empty(stage_of(iv)));  // last reader of V_j
+                        if (j + 1 < it.n_tiles[w]) {
+                            if (!k_ready) {
+                                wait(kv_full(stage_of(ik)), phase_of(ik), 240);
+                                if (!ok) break;
+                                tc_fence_after();
+                                k_ready = true;
+                            }
+                            issue_s(w, stage_of(ik));
                             tc_commit(s_full(w));
-                            if (j + 2 == n) tc_commit(q_empty(w));  // the slot's last S of this item
-                            tc_commit(kv_empty(stage_of(ik)));
+                            if (j + 2 == it.n_tiles[w]) tc_commit(q_empty(w));  // the slot's last S of this item
                             TRACE(2, j, w * 4 + 2);
+                            if (w == 1 || j + 1 >= it.n_tiles[1]) tc_commit(kv_empty(stage_of(ik)));  // last reader of K_{j+1}
                         } else {
                             tc_commit(o_final(w));
                         }
                     }
                 }
-                // tiles only the other slot visits: this slot has nothing to read, but arrives only once the entry is
-                // loaded, so that it never runs a whole ring ahead of the other slot
-                for (uint32_t e = 2u * (uint32_t)n; ok && e < entries; ++e) {
-                    wait(kv_full(stage_of(e)), phase_of(e), 250);
-                    if (ok) mbar_arrive(kv_empty(stage_of(e)));
-                }
-                ring0 += entries;
+                ring0 += 2 * n_max;
             }
         }
     }
@@ -379,8 +384,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
         const int lane_base = (warp & 3) * 32;
         const int row_in_tile = lane_base + lane;
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16);
-        const uint32_t t_s = t_lane + col_s(w);
-        const uint32_t t_o = t_lane + col_o(w);
+        const uint32_t t_s = t_lane + col_s[w];
+        const uint32_t t_o = t_lane + col_o[w];
         bool ok = true;
         uint32_t done = 0;     // finished items of this slot (its tile was inside q_len)
         uint32_t s_waits = 0;  // score tiles of this slot consumed so far
