@@ -51,6 +51,33 @@ def test_grouped_rope_bf16(B, Hq, Hkv, N, D, theta, off):
         check(o, l, eo, el)
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,N,D,rope", [(2, 48, 8, 300, 128, True), (3, 64, 8, 130, 64, True), (2, 40, 8, 520, 128, False)])
+def test_persistent_grid_walks_several_items_per_cta(B, Hq, Hkv, N, D, rope):
+    """More (query block, batch, head) items than SMs: every CTA of the persistent forward kernel walks several
+    items, with ragged last blocks (an item whose second 128-row tile lies past q_len) in between.  Sampled rows
+    (first / last rows, tile borders, random ones) of every head are checked against the oracle."""
+    q, k, v = randn(B * Hq * N * D, 1), randn(B * Hkv * N * D, 2), randn(B * Hkv * N * D, 3)
+    theta, off = 5e5, 17
+    shp = fa.shape(B, Hq, Hkv, N, N, D)
+    if rope:
+        o, l = run_forward("grouped_rope", fa.BF16, shp, fa.config(True), q, k, v, rot=fa.rotary(theta, off))
+        rq = ob.rotate_rows(q, D, np.tile(np.arange(N, dtype=np.uint64) + off, B * Hq), theta)
+        rk = ob.rotate_rows(k, D, np.tile(np.arange(N, dtype=np.uint64) + off, B * Hkv), theta)
+    else:
+        o, l = run_forward("grouped", fa.BF16, shp, fa.config(True), q, k, v)
+        rq, rk = q, k
+    rng = np.random.default_rng(5)
+    picks = sorted({0, 1, 127, 128, 255, 256, N - 1} & set(range(N)))
+    rows = [(b, h, r) for b in range(B) for h in range(Hq) for r in picks + list(rng.integers(0, N, 3))]
+    eo, el = ob.forward_rows(rq, rk, v, ob._shape(B, Hq, Hkv, N, N, D, 0), ob.HEAD_MAJOR, rows, True, threads=8)
+    o = o.reshape(B, Hq, N, D)
+    l = l.reshape(B, Hq, N)
+    go = np.stack([o[b, h, r] for b, h, r in rows]).reshape(-1)
+    gl = np.array([l[b, h, r] for b, h, r in rows])
+    check(go, gl, eo, el)
+    assert ctx().device_status() == 0
+
+
 @pytest.mark.parametrize("B,Hq,Hkv,Nq,Nkv,D,causal,coff,qr,kr,rotate_k", [
     (1, 4, 2, 256, 256, 128, True, 0, 7, 7, True),
     (2, 4, 2, 100, 300, 128, True, 200, 200, 0, True),
