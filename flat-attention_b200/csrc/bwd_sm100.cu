@@ -70,7 +70,12 @@ template <int D> struct BCfg {
     static constexpr int kStageBytes = 2 * kTileBytes + 1024;  // two tiles + 128 f32 lse + 128 f32 delta
     static constexpr int kStages = D == 128 ? 2 : 4;
     static constexpr int kBars = 2 * kStages + 10;  // enough for either kernel's barrier set
-    static constexpr int kSmemBytes = 2 * kTileBytes + kStages * kStageBytes + kBars * 8 + 16 + 1024;
+#ifdef FLAT_TRACE
+    static constexpr int kTraceBytes = 32 * 8 * 4;
+#else
+    static constexpr int kTraceBytes = 0;
+#endif
+    static constexpr int kSmemBytes = 2 * kTileBytes + kStages * kStageBytes + kBars * 8 + 16 + kTraceBytes + 1024;
 };
 
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
@@ -86,42 +91,52 @@ __device__ __forceinline__ void timeout(const BwdKernelParams &p, int where) {
     }
 }
 
-// KV == true: stationary (K, V), streamed (Q, dO), outputs dV (out0) and dK (out1).
-// KV == false: stationary (Q, dO), streamed (K, V), output dQ (out0).
-template <int D, bool KV>
+// KV-stationary kernel: stationary (K, V), streamed (Q_i, dO_i), outputs dV (out0) and dK (out1).
+// Per streamed tile the work is split so that the tensor pipe and the elementwise warps overlap:
+//   S^T = K Q_i^T                      -> phase 1: P^T = exp2(S^T c - lse) as bf16 over S^T (P stays in registers)
+//   dP^T = V dO_i^T (runs under phase 1)
+//   dV += P^T dO_i, S^T of tile i + 1  -> phase 2: dS^T = P^T (dP^T - delta) as bf16 over dP^T
+//   dK += dS^T Q_i, dP^T of tile i + 1
+template <int D>
 __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_constant__ BwdKernelParams p) {
     using C = BCfg<D>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t *st0 = smem;                    // stationary tile 0 (K or Q)
-    uint8_t *st1 = smem + C::kTileBytes;    // stationary tile 1 (V or dO)
+    uint8_t *st0 = smem;                    // K tile
+    uint8_t *st1 = smem + C::kTileBytes;    // V tile
     uint8_t *ring = smem + 2 * C::kTileBytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(ring + C::kStages * C::kStageBytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + C::kBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+#ifdef FLAT_TRACE
+    volatile uint32_t *tr_s = reinterpret_cast<volatile uint32_t *>(tmem_slot + 4);
+#define TRS(it, slot) do { if ((it) < 32) tr_s[(it) * 8 + (slot)] = (uint32_t)clock(); } while (0)
+#else
+#define TRS(it, slot) do { } while (0)
+#endif
 
     const uint32_t bar0 = smem_u32(bars);
     const uint32_t st_full = bar0;
     auto rg_full = [&](int s) { return bar0 + 8u * (1 + s); };
     auto rg_empty = [&](int s) { return bar0 + 8u * (1 + C::kStages + s); };
-    const uint32_t xy_full = bar0 + 8u * (1 + 2 * C::kStages);   // both score products in TMEM
-    const uint32_t ds_full = bar0 + 8u * (2 + 2 * C::kStages);   // bf16 P / dS written
-    const uint32_t acc_final = bar0 + 8u * (3 + 2 * C::kStages);
+    const uint32_t x_full = bar0 + 8u * (1 + 2 * C::kStages);     // S^T in TMEM
+    const uint32_t y_full = bar0 + 8u * (2 + 2 * C::kStages);     // dP^T in TMEM
+    const uint32_t p_ready = bar0 + 8u * (3 + 2 * C::kStages);    // bf16 P^T written
+    const uint32_t ds_ready = bar0 + 8u * (4 + 2 * C::kStages);   // bf16 dS^T written
+    const uint32_t acc_final = bar0 + 8u * (5 + 2 * C::kStages);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    // block -> (tile, head, batch); blocks with more work first
-    const int heads = KV ? p.kv_heads : p.q_heads;
+    // block -> (key tile, kv head, batch); early key tiles see the most queries and go first
+    const int heads = p.kv_heads;
     const int lin = blockIdx.x;
     const int tile_rank = lin / (heads * p.batch);
     const int bh = lin % (heads * p.batch);
     const int b = bh / heads, h = bh % heads;
-    // KV-stationary: early key tiles see the most queries; Q-stationary: late query tiles see the most keys
-    const int t_own = p.causal ? (KV ? tile_rank : p.n_tiles - 1 - tile_rank) : tile_rank;
-    const int first = p.causal ? (KV ? t_own : 0) : 0;
-    const int last = p.causal ? (KV ? p.n_tiles - 1 : t_own) : p.n_tiles - 1;
-    const int per_head = last - first + 1;
-    const int n_iter = KV ? per_head * p.group : per_head;
+    const int t_own = tile_rank;
+    const int first = p.causal ? t_own : 0;
+    const int per_head = p.n_tiles - first;
+    const int n_iter = per_head * p.group;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -130,8 +145,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
             mbar_init(rg_full(s), 1);
             mbar_init(rg_empty(s), 1);
         }
-        mbar_init(xy_full, 1);
-        mbar_init(ds_full, 8);
+        mbar_init(x_full, 1);
+        mbar_init(y_full, 1);
+        mbar_init(p_ready, 8);
+        mbar_init(ds_ready, 8);
         mbar_init(acc_final, 1);
         mbar_fence_init();
         fence_proxy_async();
@@ -147,15 +164,14 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
     constexpr uint32_t kColX = 0, kColY = 128, kColA0 = 256, kColA1 = 256 + D;
 
     if (warp >= 8) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+        // 72 x 128 + 216 x 256 registers: exactly the CTA's launch allocation of 168 x 384
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
         if (warp == kProducerWarp && lane == 0) {
             // ================= TMA producer =================
-            const CUtensorMap *m_st0 = KV ? &p.map_k : &p.map_q, *m_st1 = KV ? &p.map_v : &p.map_do;
-            const CUtensorMap *m_r0 = KV ? &p.map_q : &p.map_k, *m_r1 = KV ? &p.map_do : &p.map_v;
             mbar_expect_tx(st_full, 2 * C::kTileBytes);
             for (int kb = 0; kb < C::kBoxes; ++kb) {
-                tma_load_4d(smem_u32(st0 + kb * C::kBoxBytes), m_st0, kb * 64, t_own * kTile, h, b, st_full);
-                tma_load_4d(smem_u32(st1 + kb * C::kBoxBytes), m_st1, kb * 64, t_own * kTile, h, b, st_full);
+                tma_load_4d(smem_u32(st0 + kb * C::kBoxBytes), &p.map_k, kb * 64, t_own * kTile, h, b, st_full);
+                tma_load_4d(smem_u32(st1 + kb * C::kBoxBytes), &p.map_v, kb * 64, t_own * kTile, h, b, st_full);
             }
             for (int it = 0; it < n_iter; ++it) {
                 const int s = it % C::kStages;
@@ -165,19 +181,18 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                     break;
                 }
                 const int t = first + it % per_head;
-                const int hs = KV ? h * p.group + it / per_head : h / p.group;  // head of the streamed tensors
+                const int hs = h * p.group + it / per_head;  // query head of the streamed tensors
                 uint8_t *stage = ring + s * C::kStageBytes;
-                mbar_expect_tx(rg_full(s), KV ? C::kStageBytes : 2 * C::kTileBytes);
+                mbar_expect_tx(rg_full(s), C::kStageBytes);
                 for (int kb = 0; kb < C::kBoxes; ++kb) {
-                    tma_load_4d(smem_u32(stage + kb * C::kBoxBytes), m_r0, kb * 64, t * kTile, hs, b, rg_full(s));
-                    tma_load_4d(smem_u32(stage + C::kTileBytes + kb * C::kBoxBytes), m_r1, kb * 64, t * kTile, hs, b,
+                    tma_load_4d(smem_u32(stage + kb * C::kBoxBytes), &p.map_q, kb * 64, t * kTile, hs, b, rg_full(s));
+                    tma_load_4d(smem_u32(stage + C::kTileBytes + kb * C::kBoxBytes), &p.map_do, kb * 64, t * kTile, hs, b,
                                 rg_full(s));
                 }
-                if (KV) {  // per-query LSE and delta of the streamed query tile
-                    const long long row0 = ((long long)b * p.q_heads + hs) * p.seq_len + (long long)t * kTile;
-                    bulk_copy_g2s(smem_u32(stage + 2 * C::kTileBytes), p.neg_lse2 + row0, 512, rg_full(s));
-                    bulk_copy_g2s(smem_u32(stage + 2 * C::kTileBytes + 512), p.delta + row0, 512, rg_full(s));
-                }
+                // per-query LSE and delta of the streamed query tile
+                const long long row0 = ((long long)b * p.q_heads + hs) * p.seq_len + (long long)t * kTile;
+                bulk_copy_g2s(smem_u32(stage + 2 * C::kTileBytes), p.neg_lse2 + row0, 512, rg_full(s));
+                bulk_copy_g2s(smem_u32(stage + 2 * C::kTileBytes + 512), p.delta + row0, 512, rg_full(s));
             }
         } else if (warp == kMmaWarp && lane == 0) {
             // ================= MMA issuer =================
@@ -189,145 +204,153 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                     ok = false;
                 }
             };
-            // X = st0 * r0^T, Y = st1 * r1^T: both operands K-major tiles in shared memory
+            // scores = stationary * streamed^T: both operands K-major tiles in shared memory
             auto issue_xy = [&](uint32_t col, const uint8_t *a_tile, const uint8_t *b_tile) {
-                const uint32_t a0 = smem_u32(a_tile), b0 = smem_u32(b_tile);
+                const uint64_t a_desc = make_smem_desc(smem_u32(a_tile), 0, 1024);
+                const uint64_t b_desc = make_smem_desc(smem_u32(b_tile), 0, 1024);
 #pragma unroll
-                for (int kk = 0; kk < D / 16; ++kk) {
-                    const uint32_t off = (kk / 4) * C::kBoxBytes + (kk % 4) * 32;
-                    mma_ss(tmem_base + col, make_smem_desc(a0 + off, 0, 1024), make_smem_desc(b0 + off, 0, 1024), p.idesc_k,
-                           kk > 0);
-                }
+                for (int kk = 0; kk < D / 16; ++kk)
+                    mma_ss_off(tmem_base + col, a_desc, b_desc, (kk >> 2) * (C::kBoxBytes >> 4) + (kk & 3) * 2, p.idesc_k, kk > 0);
             };
             // acc (+)= A[tmem, 128 x 128 bf16 in two 32-column halves] * B[smem tile as MN-major, 128 x D]
             auto issue_acc = [&](uint32_t col_acc, uint32_t col_a, const uint8_t *b_tile, bool accumulate) {
-                const uint32_t b0 = smem_u32(b_tile);
+                const uint64_t b_desc = make_smem_desc(smem_u32(b_tile), C::kBoxBytes, 1024);
 #pragma unroll
                 for (int kk = 0; kk < kTile / 16; ++kk) {
                     const uint32_t a_col = col_a + (kk < 4 ? kk * 8 : 64 + (kk - 4) * 8);
-                    mma_ts(tmem_base + col_acc, tmem_base + a_col, make_smem_desc(b0 + kk * 16 * 128, C::kBoxBytes, 1024),
-                           p.idesc_mn, (accumulate || kk > 0));
+                    mma_ts_off(tmem_base + col_acc, tmem_base + a_col, b_desc, kk * (16 * 128 >> 4), p.idesc_mn,
+                               (accumulate || kk > 0));
                 }
             };
             wait(st_full, 0, 200);
+            wait(rg_full(0), 0, 210);
+            if (ok) {
+                tc_fence_after();
+                issue_xy(kColX, st0, ring);                  // S^T(0) = K Q_0^T
+                tc_commit(x_full);
+                issue_xy(kColY, st1, ring + C::kTileBytes);  // dP^T(0) = V dO_0^T
+                tc_commit(y_full);
+            }
             for (int it = 0; ok && it < n_iter; ++it) {
                 const int s = it % C::kStages;
                 const uint8_t *stage = ring + s * C::kStageBytes;
-                wait(rg_full(s), (it / C::kStages) & 1, 210);
+                const uint8_t *stage_n = ring + ((it + 1) % C::kStages) * C::kStageBytes;
+                const bool more = it + 1 < n_iter;
+                TRS(it, 0);
+                wait(p_ready, it & 1, 220);
                 if (!ok) break;
-                TRACE(2, it, 0);
+                TRS(it, 1);
                 tc_fence_after();
-                issue_xy(kColX, st0, stage);
-                issue_xy(kColY, st1, stage + C::kTileBytes);
-                tc_commit(xy_full);
-                TRACE(2, it, 1);
-                wait(ds_full, it & 1, 220);
-                if (!ok) break;
-                TRACE(2, it, 2);
-                tc_fence_after();
-                if (KV) {
-                    issue_acc(kColA0, kColX, stage + C::kTileBytes, it > 0);  // dV += P^T dO
-                    issue_acc(kColA1, kColY, stage, it > 0);                  // dK += dS^T Q
-                } else {
-                    issue_acc(kColA0, kColX, stage, it > 0);                  // dQ += dS K
+                issue_acc(kColA0, kColX, stage + C::kTileBytes, it > 0);  // dV += P^T dO
+                if (more) {
+                    wait(rg_full((it + 1) % C::kStages), ((it + 1) / C::kStages) & 1, 230);
+                    if (!ok) break;
+                    tc_fence_after();
+                    issue_xy(kColX, st0, stage_n);                        // S^T of the next tile over P^T
+                    tc_commit(x_full);
                 }
+                TRS(it, 2);
+                wait(ds_ready, it & 1, 240);
+                if (!ok) break;
+                TRS(it, 3);
+                tc_fence_after();
+                issue_acc(kColA1, kColY, stage, it > 0);                  // dK += dS^T Q
                 tc_commit(rg_empty(s));
-                TRACE(2, it, 3);
+                if (more) {
+                    issue_xy(kColY, st1, stage_n + C::kTileBytes);        // dP^T of the next tile over dS^T
+                    tc_commit(y_full);
+                }
+                TRS(it, 4);
             }
             if (ok) tc_commit(acc_final);
         }
     } else {
         // ================= elementwise warps + epilogue =================
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
-        const int half = warp >> 2;                  // which 64 columns of the 128
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        const int half = warp >> 2;                  // which 64 query columns of the 128
         const int lane_base = (warp & 3) * 32;
-        const int row_local = lane_base + lane;      // TMEM lane: key (KV) or query (Q-stationary)
+        const int row_local = lane_base + lane;      // TMEM lane = key
         const uint32_t t_lane = tmem_base + (static_cast<uint32_t>(lane_base) << 16);
         const uint32_t t_x = t_lane + kColX + half * 64, t_y = t_lane + kColY + half * 64;
-        uint64_t c2;
-        asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(p.scale_log2));
-        float my_neg_lse2 = 0.f, my_delta = 0.f;
-        if (!KV) {
-            const long long row = ((long long)b * p.q_heads + h) * p.seq_len + (long long)t_own * kTile + row_local;
-            my_neg_lse2 = p.neg_lse2[row];
-            my_delta = p.delta[row];
-        }
         bool ok = true;
         for (int it = 0; ok && it < n_iter; ++it) {
             const int s = it % C::kStages;
             const uint8_t *stage = ring + s * C::kStageBytes;
-            if (KV && !mbar_wait(rg_full(s), (it / C::kStages) & 1, abort_flag)) {  // LSE / delta of this stage
+            if (!mbar_wait(rg_full(s), (it / C::kStages) & 1, abort_flag)) {  // LSE / delta of this stage
                 timeout(p, 300);
                 ok = false;
                 break;
             }
-            if (!mbar_wait(xy_full, it & 1, abort_flag)) {
+            const float *lse_s = reinterpret_cast<const float *>(stage + 2 * C::kTileBytes) + half * 64;
+            const float *delta_s = lse_s + 128;
+            const int t = first + it % per_head;
+            const bool diag = p.causal && t == t_own;
+            // ---- phase 1: P^T ----
+            if (!mbar_wait(x_full, it & 1, abort_flag)) {
                 timeout(p, 310);
                 ok = false;
                 break;
             }
             tc_fence_after();
-            if (warp == 0 && lane == 0) TRACE(0, it, 0);
-            const int t = first + it % per_head;
-            const bool diag = p.causal && t == t_own;
-            uint32_t x[64], y[64];
+            uint32_t x[64];  // scores, then P in f32 (kept for phase 2)
             tmem_ld32(t_x, x);
             tmem_ld32(t_x + 32, x + 32);
-            tmem_ld32(t_y, y);
-            tmem_ld32(t_y + 32, y + 32);
             tc_wait_ld();
-            if (warp == 0 && lane == 0) TRACE(0, it, 1);
-            const float *lse_s = reinterpret_cast<const float *>(stage + 2 * C::kTileBytes) + half * 64;
-            const float *delta_s = lse_s + 128;
-            uint32_t pp[32], ds[32];
+            {
+                uint64_t c2;
+                asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(p.scale_log2));
+                uint32_t pp[32];
 #pragma unroll
-            for (int i = 0; i < 64; i += 2) {
-                uint64_t s2, nl2, dl2, t2, y2, d2;
-                asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(x[i]), "r"(x[i + 1]));
-                asm("mov.b64 %0, {%1, %2};" : "=l"(y2) : "r"(y[i]), "r"(y[i + 1]));
-                if (KV) {
+                for (int i = 0; i < 64; i += 2) {
+                    uint64_t s2, nl2, t2;
                     const float2 nl = *reinterpret_cast<const float2 *>(lse_s + i);
-                    const float2 dl = *reinterpret_cast<const float2 *>(delta_s + i);
+                    asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(x[i]), "r"(x[i + 1]));
                     asm("mov.b64 %0, {%1, %2};" : "=l"(nl2) : "f"(nl.x), "f"(nl.y));
-                    asm("mov.b64 %0, {%1, %2};" : "=l"(dl2) : "f"(dl.x), "f"(dl.y));
-                } else {
-                    asm("mov.b64 %0, {%1, %1};" : "=l"(nl2) : "f"(my_neg_lse2));
-                    asm("mov.b64 %0, {%1, %1};" : "=l"(dl2) : "f"(my_delta));
-                }
-                asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(t2) : "l"(s2), "l"(c2), "l"(nl2));
-                asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(d2) : "l"(y2), "l"(dl2));
-                float t0, t1, e0, e1;
-                asm("mov.b64 {%0, %1}, %2;" : "=f"(t0), "=f"(t1) : "l"(t2));
-                asm("mov.b64 {%0, %1}, %2;" : "=f"(e0), "=f"(e1) : "l"(d2));
-                float p0 = ex2(t0), p1 = ex2(t1);
-                if (diag) {
-                    // visible iff key <= query.  KV: row = key, column = query.  Q-stationary: row = query, column = key.
-                    const int c0 = half * 64 + i;
-                    const bool v0 = KV ? (row_local <= c0) : (c0 <= row_local);
-                    const bool v1 = KV ? (row_local <= c0 + 1) : (c0 + 1 <= row_local);
-                    if (!v0) p0 = 0.f;
-                    if (!v1) p1 = 0.f;
-                }
-                const __nv_bfloat162 dsb = __floats2bfloat162_rn(p0 * e0, p1 * e1);
-                ds[i >> 1] = *reinterpret_cast<const uint32_t *>(&dsb);
-                if (KV) {
+                    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(t2) : "l"(s2), "l"(c2), "l"(nl2));
+                    float t0, t1;
+                    asm("mov.b64 {%0, %1}, %2;" : "=f"(t0), "=f"(t1) : "l"(t2));
+                    float p0 = ex2(t0), p1 = ex2(t1);
+                    if (diag) {  // visible iff key <= query: row = key, column = query
+                        const int c0 = half * 64 + i;
+                        if (row_local > c0) p0 = 0.f;
+                        if (row_local > c0 + 1) p1 = 0.f;
+                    }
+                    x[i] = __float_as_uint(p0);
+                    x[i + 1] = __float_as_uint(p1);
                     const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
                     pp[i >> 1] = *reinterpret_cast<const uint32_t *>(&pb);
                 }
+                tmem_st32(t_x, pp);  // bf16 P^T in the first 32 columns of this warp group's 64-column range
+                tc_wait_st();
             }
-            if (warp == 0 && lane == 0) TRACE(0, it, 2);
-            // bf16 results go to the first 32 columns of this warp group's own 64-column range
-            if (KV) {
-                tmem_st32(t_x, pp);   // P^T over S^T
-                tmem_st32(t_y, ds);   // dS^T over dP^T
-            } else {
-                tmem_st32(t_x, ds);   // dS over S
-            }
-            tc_wait_st();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(ds_full);
-            if (warp == 0 && lane == 0) TRACE(0, it, 3);
+            if (lane == 0) mbar_arrive(p_ready);
+            // ---- phase 2: dS^T ----
+            if (!mbar_wait(y_full, it & 1, abort_flag)) {
+                timeout(p, 315);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            {
+                uint32_t y[64], ds[32];
+                tmem_ld32(t_y, y);
+                tmem_ld32(t_y + 32, y + 32);
+                tc_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 64; i += 2) {
+                    const float2 dl = *reinterpret_cast<const float2 *>(delta_s + i);
+                    const float e0 = __uint_as_float(y[i]) - dl.x, e1 = __uint_as_float(y[i + 1]) - dl.y;
+                    const __nv_bfloat162 dsb = __floats2bfloat162_rn(__uint_as_float(x[i]) * e0, __uint_as_float(x[i + 1]) * e1);
+                    ds[i >> 1] = *reinterpret_cast<const uint32_t *>(&dsb);
+                }
+                tmem_st32(t_y, ds);  // bf16 dS^T over dP^T
+                tc_wait_st();
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(ds_ready);
         }
         if (ok && !mbar_wait(acc_final, 0, abort_flag)) {
             timeout(p, 320);
@@ -339,8 +362,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
             const long long out_row = ((long long)b * heads + h) * p.seq_len + (long long)t_own * kTile + row_local;
             constexpr int kColsPerHalf = D / 2;
 #pragma unroll
-            for (int a = 0; a < (KV ? 2 : 1); ++a) {
-                const float mul = (KV && a == 0) ? 1.0f : p.scale;  // dV unscaled; dK and dQ carry the softmax scale
+            for (int a = 0; a < 2; ++a) {
+                const float mul = a == 0 ? 1.0f : p.scale;  // dV unscaled; dK carries the softmax scale
                 float *op = reinterpret_cast<float *>(a == 0 ? p.out0 : p.out1) + out_row * D + half * kColsPerHalf;
                 const uint32_t t_acc = t_lane + (a == 0 ? kColA0 : kColA1) + half * kColsPerHalf;
 #pragma unroll
@@ -363,11 +386,16 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
     }
     tc_fence_before();
     __syncthreads();
+#ifdef FLAT_TRACE
+    if (p.trace && blockIdx.x == 0)
+        for (int i = threadIdx.x; i < 32 * 8; i += kThreads) p.trace[2 * 64 * 8 + i] = tr_s[i];
+#endif
     if (warp == kMmaWarp) {
         tc_fence_after();
         tmem_dealloc(tmem_base, 512);
     }
 }
+#undef TRS
 
 // Q-stationary dQ kernel, pipelined.  One CTA owns 128 queries of one (batch, q_head); (K_j, V_j) tiles stream
 // through a three-stage TMA ring.  Q is copied once from shared memory into TMEM and is the A operand of every
@@ -766,8 +794,8 @@ int launch_backward_sm100(flat_ctx *ctx, const BwdParams &p) {
     const long long grid_q = (long long)kp.n_tiles * p.q_heads * p.batch;
     kp.out0 = p.dv;
     kp.out1 = p.dk;
-    if (D == 128) st = run(bwd_sm100_kernel<128, true>, BCfg<128>::kSmemBytes, grid_kv);
-    else st = run(bwd_sm100_kernel<64, true>, BCfg<64>::kSmemBytes, grid_kv);
+    if (D == 128) st = run(bwd_sm100_kernel<128>, BCfg<128>::kSmemBytes, grid_kv);
+    else st = run(bwd_sm100_kernel<64>, BCfg<64>::kSmemBytes, grid_kv);
     if (st) return st;
     kp.out0 = p.dq;
     kp.out1 = nullptr;
