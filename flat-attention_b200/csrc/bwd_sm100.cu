@@ -236,10 +236,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                 const uint8_t *stage = ring + s * C::kStageBytes;
                 const uint8_t *stage_n = ring + ((it + 1) % C::kStages) * C::kStageBytes;
                 const bool more = it + 1 < n_iter;
-                TRS(it, 0);
+                if (it < 16) TRS(it, 0);
                 wait(p_ready, it & 1, 220);
                 if (!ok) break;
-                TRS(it, 1);
+                if (it < 16) TRS(it, 1);
                 tc_fence_after();
                 issue_acc(kColA0, kColX, stage + C::kTileBytes, it > 0);  // dV += P^T dO
                 if (more) {
@@ -249,10 +249,10 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                     issue_xy(kColX, st0, stage_n);                        // S^T of the next tile over P^T
                     tc_commit(x_full);
                 }
-                TRS(it, 2);
+                if (it < 16) TRS(it, 2);
                 wait(ds_ready, it & 1, 240);
                 if (!ok) break;
-                TRS(it, 3);
+                if (it < 16) TRS(it, 3);
                 tc_fence_after();
                 issue_acc(kColA1, kColY, stage, it > 0);                  // dK += dS^T Q
                 tc_commit(rg_empty(s));
@@ -260,7 +260,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                     issue_xy(kColY, st1, stage_n + C::kTileBytes);        // dP^T of the next tile over dS^T
                     tc_commit(y_full);
                 }
-                TRS(it, 4);
+                if (it < 16) TRS(it, 4);
             }
             if (ok) tc_commit(acc_final);
         }
@@ -292,40 +292,55 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                 break;
             }
             tc_fence_after();
+            if (warp == 0 && lane == 0 && it < 16) TRS(it, 5);
             uint32_t x[64];  // scores, then P in f32 (kept for phase 2)
             tmem_ld32(t_x, x);
             tmem_ld32(t_x + 32, x + 32);
             tc_wait_ld();
+            if (warp == 0 && lane == 0 && it < 16) TRS(16 + it, 0);
             {
-                uint64_t c2;
-                asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(p.scale_log2));
+                const float c = p.scale_log2;
                 uint32_t pp[32];
+                if (!diag) {
+                    // three passes over the registers: the 64 independent exp2 keep the special-function unit full
 #pragma unroll
-                for (int i = 0; i < 64; i += 2) {
-                    uint64_t s2, nl2, t2;
-                    const float2 nl = *reinterpret_cast<const float2 *>(lse_s + i);
-                    asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(x[i]), "r"(x[i + 1]));
-                    asm("mov.b64 %0, {%1, %2};" : "=l"(nl2) : "f"(nl.x), "f"(nl.y));
-                    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(t2) : "l"(s2), "l"(c2), "l"(nl2));
-                    float t0, t1;
-                    asm("mov.b64 {%0, %1}, %2;" : "=f"(t0), "=f"(t1) : "l"(t2));
-                    float p0 = ex2(t0), p1 = ex2(t1);
-                    if (diag) {  // visible iff key <= query: row = key, column = query
+                    for (int i = 0; i < 64; i += 2) {
+                        const float2 nl = *reinterpret_cast<const float2 *>(lse_s + i);
+                        x[i] = __float_as_uint(fmaf(__uint_as_float(x[i]), c, nl.x));
+                        x[i + 1] = __float_as_uint(fmaf(__uint_as_float(x[i + 1]), c, nl.y));
+                    }
+#pragma unroll
+                    for (int i = 0; i < 64; ++i) x[i] = __float_as_uint(ex2(__uint_as_float(x[i])));
+#pragma unroll
+                    for (int i = 0; i < 64; i += 2) {
+                        const __nv_bfloat162 pb = __floats2bfloat162_rn(__uint_as_float(x[i]), __uint_as_float(x[i + 1]));
+                        pp[i >> 1] = *reinterpret_cast<const uint32_t *>(&pb);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 64; i += 2) {
+                        const float2 nl = *reinterpret_cast<const float2 *>(lse_s + i);
+                        float p0 = ex2(fmaf(__uint_as_float(x[i]), c, nl.x));
+                        float p1 = ex2(fmaf(__uint_as_float(x[i + 1]), c, nl.y));
+                        // visible iff key <= query: row = key, column = query
                         const int c0 = half * 64 + i;
                         if (row_local > c0) p0 = 0.f;
                         if (row_local > c0 + 1) p1 = 0.f;
+                        x[i] = __float_as_uint(p0);
+                        x[i + 1] = __float_as_uint(p1);
+                        const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
+                        pp[i >> 1] = *reinterpret_cast<const uint32_t *>(&pb);
                     }
-                    x[i] = __float_as_uint(p0);
-                    x[i + 1] = __float_as_uint(p1);
-                    const __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
-                    pp[i >> 1] = *reinterpret_cast<const uint32_t *>(&pb);
                 }
+                if (warp == 0 && lane == 0 && it < 16) TRS(16 + it, 1);
                 tmem_st32(t_x, pp);  // bf16 P^T in the first 32 columns of this warp group's 64-column range
                 tc_wait_st();
+                if (warp == 0 && lane == 0 && it < 16) TRS(16 + it, 2);
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(p_ready);
+            if (warp == 0 && lane == 0 && it < 16) TRS(it, 6);
             // ---- phase 2: dS^T ----
             if (!mbar_wait(y_full, it & 1, abort_flag)) {
                 timeout(p, 315);
@@ -333,11 +348,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                 break;
             }
             tc_fence_after();
+            if (warp == 0 && lane == 0 && it < 16) TRS(16 + it, 3);
             {
                 uint32_t y[64], ds[32];
                 tmem_ld32(t_y, y);
                 tmem_ld32(t_y + 32, y + 32);
                 tc_wait_ld();
+                if (warp == 0 && lane == 0 && it < 16) TRS(16 + it, 4);
 #pragma unroll
                 for (int i = 0; i < 64; i += 2) {
                     const float2 dl = *reinterpret_cast<const float2 *>(delta_s + i);
@@ -345,12 +362,14 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                     const __nv_bfloat162 dsb = __floats2bfloat162_rn(__uint_as_float(x[i]) * e0, __uint_as_float(x[i + 1]) * e1);
                     ds[i >> 1] = *reinterpret_cast<const uint32_t *>(&dsb);
                 }
+                if (warp == 0 && lane == 0 && it < 16) TRS(16 + it, 5);
                 tmem_st32(t_y, ds);  // bf16 dS^T over dP^T
                 tc_wait_st();
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(ds_ready);
+            if (warp == 0 && lane == 0 && it < 16) TRS(it, 7);
         }
         if (ok && !mbar_wait(acc_final, 0, abort_flag)) {
             timeout(p, 320);
@@ -388,7 +407,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
     __syncthreads();
 #ifdef FLAT_TRACE
     if (p.trace && blockIdx.x == 0)
-        for (int i = threadIdx.x; i < 32 * 8; i += kThreads) p.trace[2 * 64 * 8 + i] = tr_s[i];
+        for (int i = threadIdx.x; i < 32 * 8; i += kThreads) p.trace[1 * 64 * 8 + i] = tr_s[i];
 #endif
     if (warp == kMmaWarp) {
         tc_fence_after();
