@@ -46,6 +46,26 @@ def prefill_flops(c):
     return 4 * c["B"] * c["Hq"] * c["N"] * c["N"] * c["D"] // 2
 
 
+def bind_to_gpu_cpus(local_rank):
+    """Pin this rank's process to the host cores next to its GPU (NVML's ideal CPU set), before any pinned host
+    buffer is allocated: the end-to-end leg moves hundreds of MB per step over PCIe, and with eight ranks on a
+    two-socket host, buffers on the far socket would cross the inter-socket link.  Reads NVML only; changes no GPU
+    setting.  Returns the number of cores bound, or None if NVML or the affinity call is unavailable."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(local_rank)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        cpus = {64 * w + b for w, word in enumerate(words) for b in range(64) if (word >> b) & 1}
+        cpus &= os.sched_getaffinity(0)
+        if cpus:
+            os.sched_setaffinity(0, cpus)
+            return len(cpus)
+    except Exception:
+        pass
+    return None
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -417,6 +437,7 @@ def main():
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
     torch.cuda.set_device(local_rank)
+    numa = bind_to_gpu_cpus(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
@@ -493,7 +514,8 @@ def main():
         "config": {"workload": "C2 GQA+RoPE causal prefill (Llama-3-8B shape): B=4 per GPU, Hq=32, Hkv=8, N=4096, D=128, "
                                "bf16, theta=5e5, O + f32 LSE", "flop_per_step_per_gpu": flops,
                    "inputs": "seeded N(0,1) rounded to bf16; 192 MiB of Q/K/V + 160 MiB rotated operands per step "
-                             "exceed the 126 MB L2", "sharding": "independent batches per rank, no collective"},
+                             "exceed the 126 MB L2", "sharding": "independent batches per rank, no collective",
+                   "host_cores_bound": numa},
         "e2e": {"value": world * flops / (ms_e2e / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": int(hq.numel() + hk.numel() + hv.numel()) * 2, "d2h_bytes_per_step": int(out.numel()),
                 "ms_per_step": ms_e2e / e2e_steps},
