@@ -7,6 +7,7 @@
 //   warps 4-7  softmax of Q tile 1
 //   warp  8    TMA producer        : Q tiles once, then K_j, V_j through an mbarrier ring
 //   warp  9    MMA issuer          : one thread issues every tcgen05.mma and tcgen05.commit
+//   warps 10-11 K converters       : bf16 -> fp16 of each K tile in place (only when Q is rotated against bf16 K)
 // Per KV tile j and Q tile w:  S_w = Q_w K_j^T (SS MMA, f32 in TMEM)  ->  softmax warps read S_w
 // from TMEM, track the running max (rescaling O_w in TMEM only when the max grows by more than
 // 2^8), write P_w = exp2(S_w*c - m) as bf16 over S_w  ->  O_w += P_w V_j (A operand from TMEM).
@@ -20,8 +21,9 @@
 // rotated once per call by a small prologue kernel into fp16 scratch (every K tile is read by
 // many CTAs, so rotating it in-kernel would repeat the work 32 times).  When the cache already
 // holds rotated bf16 K (rotate_k = 0) only Q is rotated; tcgen05.mma kind::f16 takes A and B of
-// one format only, so rotated Q is then written as two bf16 tiles hi + lo (lo = bf16(q - hi)) and
-// S = Q_hi K^T + Q_lo K^T costs one extra QK MMA pass.
+// one format only, so each bf16 K tile is then converted to fp16 in place in shared memory by two
+// otherwise idle warps (CONVK; exact for |k| in the normal fp16 range, saturating beyond 65504)
+// before the MMA warp may use it.
 // Semantics: Appendix of the forward contract (src/projection_asymmetric.rs:97-238): key k is
 // visible to local row q iff !causal || k <= query_position_offset + q; LSE = max + ln(sum).
 #include <cuda.h>
@@ -100,15 +102,14 @@ struct KernelParams {
     long long *trace;
 };
 
-// SPLIT: Q arrives as bf16 hi + lo parts (two smem tiles per Q tile).
-template <int D, bool SPLIT> struct Cfg {
+// CONVK: K tiles are bf16 in memory and are converted to fp16 in shared memory (Q is rotated to fp16).
+template <int D, bool CONVK> struct Cfg {
     static constexpr int kBoxes = D / 64;                  // 64-element (128-byte) column boxes per row
     static constexpr int kBoxBytes = kTileRows * 128;      // 128 rows x 128 B
     static constexpr int kTileBytes = kBoxes * kBoxBytes;  // one Q / K / V tile
-    static constexpr int kQParts = SPLIT ? 2 : 1;
-    static constexpr int kStages = D == 128 ? (SPLIT ? 3 : 4) : 8;  // K/V ring entries
-    static constexpr int kBars = 2 + 2 * kStages + 10;
-    static constexpr int kSmemBytes = (2 * kQParts + kStages) * kTileBytes + kBars * 8 + 16 + 1024;
+    static constexpr int kStages = D == 128 ? 4 : 8;  // K/V ring entries
+    static constexpr int kBars = 2 + 3 * kStages + 10;
+    static constexpr int kSmemBytes = (2 + kStages) * kTileBytes + kBars * 8 + 16 + 1024;
 };
 
 __device__ __forceinline__ void record_timeout(const KernelParams &p, int where) {
@@ -155,13 +156,13 @@ __device__ __forceinline__ int item_index(const KernelParams &p, int k) {
     return idx < p.total_items ? (int)idx : -1;
 }
 
-template <int D, bool SPLIT>
+template <int D, bool CONVK>
 __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_constant__ KernelParams p) {
-    using C = Cfg<D, SPLIT>;
+    using C = Cfg<D, CONVK>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *q_s = smem;
-    uint8_t *kv_s = smem + 2 * C::kQParts * C::kTileBytes;
+    uint8_t *kv_s = smem + 2 * C::kTileBytes;
     uint64_t *bars = reinterpret_cast<uint64_t *>(kv_s + C::kStages * C::kTileBytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + C::kBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -175,6 +176,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     auto o_final = [&](int w) { return bar0 + 8u * (6 + 2 * C::kStages + w); };
     auto q_ready = [&](int w) { return bar0 + 8u * (8 + 2 * C::kStages + w); };
     auto q_empty = [&](int w) { return bar0 + 8u * (10 + 2 * C::kStages + w); };
+    auto k_ready = [&](int s) { return bar0 + 8u * (12 + 2 * C::kStages + s); };  // K tile converted (CONVK)
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -192,6 +194,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(kv_full(s), 1);
             mbar_init(kv_empty(s), 1);
+            mbar_init(k_ready(s), 2);  // one arrival per converter warp
         }
         mbar_fence_init();
         fence_proxy_async();
@@ -213,16 +216,17 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     // Register rebalancing: a softmax thread holds a whole 128-column score row in registers.  The pool that
     // setmaxnreg.inc draws from is what the CTA was launched with (168 registers x 384 threads), not the whole
     // register file: 56 x 128 + 224 x 256 uses exactly that, and a larger request would block for ever.
-    static_assert(56 * 128 + 224 * 256 <= 168 * kThreads && 72 * 128 + 216 * 256 <= 168 * kThreads,
-                  "setmaxnreg split exceeds the CTA's register allocation");
+    static_assert(56 * 128 + 224 * 256 <= 168 * kThreads, "setmaxnreg split exceeds the CTA's register allocation");
     if (warp >= 8) {
-    if constexpr (SPLIT) asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");  // two Q parts: a longer issue sequence
-    else asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
     if (warp == kProducerWarp) {
         // ================= TMA producer =================
-        if (lane == 0) {
+        // The whole warp walks the loop (waits are uniform); lane 0 issues the contiguous loads, and with a page
+        // table lane i fetches the id of page i of the tile and issues that page's boxes, so that the page-table
+        // reads of a tile are one parallel access instead of a chain of dependent loads in one thread.
+        {
             bool ok = true;
-            uint32_t ring = 0;         // K/V ring entries requested so far
+            uint32_t ring = 0;             // K/V ring entries requested so far
             uint32_t q_loads[2] = {0, 0};  // Q tiles requested so far, per slot
             for (int k = 0; ok; ++k) {
                 const int lin = item_index(p, k);
@@ -233,39 +237,47 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     if (it.n_tiles[w] == 0) continue;
                     // the slot is free once every S MMA of its previous tile has completed
                     if (q_loads[w] > 0 && !mbar_wait(q_empty(w), (q_loads[w] - 1) & 1, abort_flag)) {
-                        record_timeout(p, 110 + w);
+                        if (lane == 0) record_timeout(p, 110 + w);
                         ok = false;
-                        break;
                     }
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
                     ++q_loads[w];
-                    mbar_expect_tx(q_full(w), C::kTileBytes);
-                    for (int kb = 0; kb < C::kBoxes; ++kb)
-                        tma_load_4d(smem_u32(q_s + w * C::kQParts * C::kTileBytes + kb * C::kBoxBytes), &p.map_q, kb * 64,
-                                    it.r0 + w * kTileRows, it.h, it.b, q_full(w));
+                    if (lane == 0) {
+                        mbar_expect_tx(q_full(w), C::kTileBytes);
+                        for (int kb = 0; kb < C::kBoxes; ++kb)
+                            tma_load_4d(smem_u32(q_s + w * C::kTileBytes + kb * C::kBoxBytes), &p.map_q, kb * 64,
+                                        it.r0 + w * kTileRows, it.h, it.b, q_full(w));
+                    }
                 }
+                int page = 0;  // this lane's page of the current KV tile (paged mode), fetched with the K entry
                 for (int i = 0; ok && i < 2 * n_max; ++i, ++ring) {
                     const int s = ring % C::kStages;
                     const uint32_t phase = (ring / C::kStages) & 1;
                     if (!mbar_wait(kv_empty(s), phase ^ 1, abort_flag)) {
-                        record_timeout(p, 100 + s);
+                        if (lane == 0) record_timeout(p, 100 + s);
                         ok = false;
-                        break;
                     }
+                    ok = __all_sync(0xffffffffu, ok);
+                    if (!ok) break;
                     const int j = i >> 1;
                     const CUtensorMap *map = (i & 1) ? &p.map_v : &p.map_k;
                     const uint32_t dst = smem_u32(kv_s + s * C::kTileBytes);
-                    mbar_expect_tx(kv_full(s), C::kTileBytes);
+                    if (lane == 0) mbar_expect_tx(kv_full(s), C::kTileBytes);
                     if (p.page_table) {
                         const int pages_per_tile = kTileRows / p.page_size;
-                        for (int pg = 0; pg < pages_per_tile; ++pg) {
-                            const int tok = j * kTileRows + pg * p.page_size;
-                            const int page = tok < p.kv_len ? p.page_table[(long long)it.b * p.max_pages + tok / p.page_size]
-                                                            : p.physical_pages;  // out of range: zero fill
+                        if ((i & 1) == 0 && lane < pages_per_tile) {
+                            const int tok = j * kTileRows + lane * p.page_size;
+                            page = tok < p.kv_len ? p.page_table[(long long)it.b * p.max_pages + tok / p.page_size]
+                                                  : p.physical_pages;  // out of range: zero fill
+                        }
+                        __syncwarp();  // the expect_tx above precedes every load of the entry
+                        if (lane < pages_per_tile) {
                             for (int kb = 0; kb < C::kBoxes; ++kb)
-                                tma_load_4d(dst + kb * C::kBoxBytes + pg * p.page_size * 128, map, kb * 64, 0, it.kvh, page,
+                                tma_load_4d(dst + kb * C::kBoxBytes + lane * p.page_size * 128, map, kb * 64, 0, it.kvh, page,
                                             kv_full(s));
                         }
-                    } else {
+                    } else if (lane == 0) {
                         for (int kb = 0; kb < C::kBoxes; ++kb)
                             tma_load_4d(dst + kb * C::kBoxBytes, map, kb * 64, j * kTileRows, it.kvh, it.b, kv_full(s));
                     }
@@ -288,14 +300,11 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             // a compile-time constant, which keeps the thread inside its small register budget.
             auto issue_s = [&](int w, int stage) {
                 const uint64_t b_desc = make_smem_desc(smem_u32(kv_s + stage * C::kTileBytes), 0, 1024);
+                const uint64_t a_desc = make_smem_desc(smem_u32(q_s + w * C::kTileBytes), 0, 1024);
 #pragma unroll
-                for (int part = 0; part < C::kQParts; ++part) {
-                    const uint64_t a_desc = make_smem_desc(smem_u32(q_s + (w * C::kQParts + part) * C::kTileBytes), 0, 1024);
-#pragma unroll
-                    for (int kk = 0; kk < D / 16; ++kk) {
-                        const uint32_t off16 = (kk >> 2) * (C::kBoxBytes >> 4) + (kk & 3) * 2;  // byte offset / 16
-                        mma_ss_off(tmem_base + col_s[w], a_desc, b_desc, off16, p.idesc_qk, (part > 0 || kk > 0));
-                    }
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    const uint32_t off16 = (kk >> 2) * (C::kBoxBytes >> 4) + (kk & 3) * 2;  // byte offset / 16
+                    mma_ss_off(tmem_base + col_s[w], a_desc, b_desc, off16, p.idesc_qk, kk > 0);
                 }
             };
             auto issue_pv = [&](int w, int stage, int j) {
@@ -328,7 +337,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     ++q_uses[w];
                     TRACEB(k, 2, 1 + w);
                     if (!k0_ready) {
-                        wait(kv_full(stage_of(0)), phase_of(0), 210);
+                        wait(CONVK ? k_ready(stage_of(0)) : kv_full(stage_of(0)), phase_of(0), 210);
                         k0_ready = true;
                     }
                     if (!ok) break;
@@ -344,7 +353,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                 for (int j = 0; ok && j < n_max; ++j) {
                     const uint32_t iv = 2 * j + 1, ik = 2 * j + 2;
                     wait(kv_full(stage_of(iv)), phase_of(iv), 220);
-                    bool k_ready = false;
+                    bool k_next = false;
                     for (int w = 0; w < 2 && ok; ++w) {
                         if (j >= it.n_tiles[w]) continue;
                         wait(p_full(w), p_waits[w] & 1, 230 + w);
@@ -356,11 +365,11 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                         TRACE(2, j, w * 4 + 1);
                         if (w == 1 || j >= it.n_tiles[1]) tc_commit(kv_empty(stage_of(iv)));  // last reader of V_j
                         if (j + 1 < it.n_tiles[w]) {
-                            if (!k_ready) {
-                                wait(kv_full(stage_of(ik)), phase_of(ik), 240);
+                            if (!k_next) {
+                                wait(CONVK ? k_ready(stage_of(ik)) : kv_full(stage_of(ik)), phase_of(ik), 240);
                                 if (!ok) break;
                                 tc_fence_after();
-                                k_ready = true;
+                                k_next = true;
                             }
                             issue_s(w, stage_of(ik));
                             tc_commit(s_full(w));
@@ -375,11 +384,51 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                 ring0 += 2 * n_max;
             }
         }
+    } else if (CONVK) {
+        // ================= K converters (warps 10, 11) =================
+        // Each K tile of the ring is rewritten in place from bf16 to fp16 (the values are bf16 numbers, so the
+        // conversion is exact inside the normal fp16 range and saturates beyond it); warp 10 takes rows 0-63,
+        // warp 11 rows 64-127.  K tiles sit at the even ring entries.
+        const int cw = warp - (kMmaWarp + 1);
+        bool ok = true;
+        uint32_t ring = 0;
+        for (int k = 0; ok; ++k) {
+            const int lin = item_index(p, k);
+            if (lin < 0) break;
+            const WorkItem it = make_item(p, lin);
+            const int n_max = max(it.n_tiles[0], it.n_tiles[1]);
+            for (int j = 0; ok && j < n_max; ++j, ring += 2) {
+                const int s = ring % C::kStages;
+                if (!mbar_wait(kv_full(s), (ring / C::kStages) & 1, abort_flag)) {
+                    record_timeout(p, 400 + s);
+                    ok = false;
+                    break;
+                }
+                uint8_t *tile = kv_s + s * C::kTileBytes;
+                // a warp covers 64 rows x (D / 8) 16-byte chunks; consecutive lanes take consecutive chunks of a row
+                constexpr int kChunks = 64 * (D / 8);
+#pragma unroll 4
+                for (int c = lane; c < kChunks; c += 32) {
+                    const int row = 64 * cw + c / (D / 8), ch = c % (D / 8);
+                    uint4 *ptr = reinterpret_cast<uint4 *>(tile + (ch >> 3) * C::kBoxBytes + row * 128 + ((ch & 7) << 4));
+                    uint4 v = *ptr;
+                    uint32_t in[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float lo = __uint_as_float(in[e] << 16), hi = __uint_as_float(in[e] & 0xffff0000u);
+                        asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(in[e]) : "f"(hi), "f"(lo));
+                    }
+                    *ptr = make_uint4(in[0], in[1], in[2], in[3]);
+                }
+                fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
+                __syncwarp();
+                if (lane == 0) mbar_arrive(k_ready(s));
+            }
+        }
     }
     } else {
         // ================= softmax + epilogue =================
-        if constexpr (SPLIT) asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
-        else asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         const int w = warp >> 2;
         const int lane_base = (warp & 3) * 32;
         const int row_in_tile = lane_base + lane;
@@ -513,7 +562,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             if (p.rope_q_table && next_lin >= 0 && ok) {
                 const WorkItem nx = make_item(p, next_lin);
                 if (nx.n_tiles[w] > 0) {
-                    // Rotate the Q tile in place (fp16), or into bf16 hi / lo tiles.  A warp rotates its 32 rows; lane l
+                    // Rotate the Q tile in place (bf16 in, fp16 out).  A warp rotates its 32 rows; lane l
                     // takes the 16-byte chunk (l mod CH) of row (step * RPS + l / CH), so that the (cos, sin) table is
                     // read in contiguous row segments.
                     constexpr int CH = D / 8;     // 16-byte chunks (8 elements, 4 pairs) per row
@@ -523,7 +572,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     // (cos, sin) of the lane's first row come from the table; each further step advances the angle by
                     // RPS positions with the rotation (cos, sin)(RPS * inv_freq), which keeps the table traffic at two
                     // 16-byte loads per thread.  The recurrence error (a few 1e-7 over CH steps) is far below the
-                    // rounding of the fp16 / bf16 result.
+                    // rounding of the fp16 result.
                     float cc[4], ss[4], cstep[4], sstep[4];
                     {
                         const int rr = min(first_row + lane_base + lane / CH, p.q_len - 1);
@@ -545,7 +594,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     }
                     if ((warp & 3) == 0 && lane == 0) TRACEB(k, w, 1);
                     if (ok) {
-                        uint8_t *tile = q_s + w * C::kQParts * C::kTileBytes;
+                        uint8_t *tile = q_s + w * C::kTileBytes;
 #pragma unroll
                         for (int st = 0; st < CH; ++st) {
                             const int rt = lane_base + st * RPS + lane / CH;  // row in tile
@@ -558,32 +607,18 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                                     cc[e] = c1;
                                 }
                             }
-                            if (first_row + rt >= p.q_len) {
-                                // rows past q_len were zero-filled by TMA in the hi tile; the lo tile has to be zero too
-                                if (SPLIT) *reinterpret_cast<uint4 *>(tile + C::kTileBytes + off) = make_uint4(0, 0, 0, 0);
-                                continue;
-                            }
+                            if (first_row + rt >= p.q_len) continue;  // rows past q_len were zero-filled by TMA
                             const uint4 raw = *reinterpret_cast<const uint4 *>(tile + off);
                             const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
-                            uint32_t hi[4], lo[4];
+                            uint32_t hi[4];
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
                                 const float x = __uint_as_float(in[e] << 16), y = __uint_as_float(in[e] & 0xffff0000u);
                                 const float rx = x * cc[e] - y * ss[e], ry = x * ss[e] + y * cc[e];
-                                if (SPLIT) {
-                                    const __nv_bfloat162 h2 = __floats2bfloat162_rn(rx, ry);
-                                    const float2 hf = __bfloat1622float2(h2);
-                                    const __nv_bfloat162 l2 = __floats2bfloat162_rn(rx - hf.x, ry - hf.y);
-                                    hi[e] = *reinterpret_cast<const uint32_t *>(&h2);
-                                    lo[e] = *reinterpret_cast<const uint32_t *>(&l2);
-                                } else {
-                                    const __half2 h2 = __floats2half2_rn(rx, ry);
-                                    hi[e] = *reinterpret_cast<const uint32_t *>(&h2);
-                                }
+                                const __half2 h2 = __floats2half2_rn(rx, ry);
+                                hi[e] = *reinterpret_cast<const uint32_t *>(&h2);
                             }
                             *reinterpret_cast<uint4 *>(tile + off) = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-                            if (SPLIT)
-                                *reinterpret_cast<uint4 *>(tile + C::kTileBytes + off) = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                         }
                     }
                     fence_proxy_async();  // generic-proxy writes -> visible to the tensor core's async proxy
@@ -736,8 +771,8 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     const void *k_ptr = p.k;
     int64_t k_rs = p.kv_rs, k_hs = p.kv_hs, k_bs = p.kv_bs;
     bool k_f16 = false;
-    const bool split = p.rope_q && !p.rope_k;  // Q rotated against a cache of already rotated bf16 K
-    const bool q_f16 = p.rope_q && !split;
+    const bool convk = p.rope_q && !p.rope_k;  // Q rotated against already rotated bf16 K: K tiles become fp16 in smem
+    const bool q_f16 = p.rope_q;
     char *scratch = scratch_ptr(ctx);
     const float2 *q_table = nullptr;
     if (p.rope_q) {
@@ -791,7 +826,7 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     kp.causal = p.causal;
     kp.causal_off = p.causal_off;
     kp.scale_log2 = p.scale * kLog2e;
-    kp.idesc_qk = make_idesc(q_f16 ? kFmtF16 : kFmtBF16, k_f16 ? kFmtF16 : kFmtBF16, 0, 0, 128, 128);
+    kp.idesc_qk = make_idesc(q_f16 ? kFmtF16 : kFmtBF16, (k_f16 || convk) ? kFmtF16 : kFmtBF16, 0, 0, 128, 128);
     kp.idesc_pv = make_idesc(kFmtBF16, kFmtBF16, 0, 1, 128, (uint32_t)D);
     kp.page_table = p.page_table;
     kp.page_size = p.page_size;
@@ -823,9 +858,9 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
         kernel<<<grid, kThreads, smem_bytes, ctx->stream>>>(kp);
         return FLAT_OK;
     };
-    if (D == 128) st = split ? run(fwd_sm100_kernel<128, true>, Cfg<128, true>::kSmemBytes)
+    if (D == 128) st = convk ? run(fwd_sm100_kernel<128, true>, Cfg<128, true>::kSmemBytes)
                              : run(fwd_sm100_kernel<128, false>, Cfg<128, false>::kSmemBytes);
-    else st = split ? run(fwd_sm100_kernel<64, true>, Cfg<64, true>::kSmemBytes)
+    else st = convk ? run(fwd_sm100_kernel<64, true>, Cfg<64, true>::kSmemBytes)
                     : run(fwd_sm100_kernel<64, false>, Cfg<64, false>::kSmemBytes);
     if (st) return st;
     ctx->launches += 1;
