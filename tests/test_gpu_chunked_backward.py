@@ -34,7 +34,9 @@ def test_chunked_prefill_equals_contiguous(B, Hq, Hkv, N, D, causal, chunk):
 
 
 @pytest.mark.parametrize("dtype,Hq,Hkv,D,N,chunk,ps", [(fa.F32, 4, 2, 32, 23, 5, 4), (fa.F32, 8, 1, 64, 40, 16, 16),
-                                                        (fa.BF16, 8, 2, 128, 300, 128, 16), (fa.BF16, 4, 4, 64, 90, 32, 16)])
+                                                        (fa.BF16, 8, 2, 128, 300, 128, 16), (fa.BF16, 4, 4, 64, 90, 32, 16),
+                                                        # more (query block, head) items than SMs, ragged last block
+                                                        (fa.BF16, 64, 8, 64, 700, 640, 16)])
 def test_chunked_prefill_into_growing_paged_cache(dtype, Hq, Hkv, D, N, chunk, ps):
     """Each chunk appends rotated K and V to the paged cache, then attends causally to the whole
     cache.  Oracle: the cache contents as stored (pre-rotated K), Q rotation materialised."""

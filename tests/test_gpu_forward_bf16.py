@@ -83,7 +83,8 @@ def test_persistent_grid_walks_several_items_per_cta(B, Hq, Hkv, N, D, rope):
     (2, 4, 2, 100, 300, 128, True, 200, 200, 0, True),
     (1, 8, 2, 130, 517, 64, True, 387, 400, 13, True),
     (1, 4, 1, 64, 400, 128, False, 0, 50, 3, True),
-    (1, 4, 2, 128, 384, 128, True, 256, 256, 0, False),   # pre-rotated K: fp16 Q x bf16 K
+    (1, 4, 2, 128, 384, 128, True, 256, 256, 0, False),   # pre-rotated bf16 K: converted to fp16 in shared memory
+    (1, 8, 2, 130, 517, 64, True, 387, 400, 13, False),
 ])
 def test_projection_rope_asymmetric_bf16(B, Hq, Hkv, Nq, Nkv, D, causal, coff, qr, kr, rotate_k):
     theta = 5e5
