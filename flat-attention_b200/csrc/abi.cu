@@ -501,6 +501,8 @@ void flat_ctx_destroy(flat_ctx *ctx) {
     }
     if (ctx->workspace) cudaFree(ctx->workspace);
     if (ctx->host_stage) cudaFree(ctx->host_stage);
+    for (auto &t : ctx->rope_tables)
+        if (t.dev) cudaFree(t.dev);
     for (cudaEvent_t e : ctx->pipe_events) cudaEventDestroy(e);
     if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
     if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
@@ -510,6 +512,12 @@ void flat_ctx_destroy(flat_ctx *ctx) {
 
 int32_t flat_ctx_set_stream(flat_ctx *ctx, void *stream) {
     if (!ctx) return FLAT_ERR_NULL_POINTER;
+    if (ctx->stream != static_cast<cudaStream_t>(stream)) {
+        // cached RoPE tables were written on the old stream; later calls read them on the new one
+        bool cached = false;
+        for (auto &t : ctx->rope_tables) cached = cached || t.rows > 0;
+        if (cached) FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    }
     ctx->stream = static_cast<cudaStream_t>(stream);
     return FLAT_OK;
 }

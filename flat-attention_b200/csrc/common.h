@@ -40,6 +40,18 @@ struct flat_ctx {
     uint64_t host_stage_bytes = 0;
     cudaStream_t copy_in = nullptr, copy_out = nullptr;  // upload / download streams of the host-slice entry points
     std::vector<cudaEvent_t> pipe_events;
+    // (cos, sin) tables of recent RoPE calls, kept on the device: a serving or training loop calls with the same
+    // theta, head_dim and positions every step, and the table is then computed once instead of per call
+    struct RopeTable {
+        void *dev = nullptr;
+        uint64_t bytes = 0;
+        float inv_freq[64] = {};
+        int half_dim = 0, rows = 0;
+        int64_t pos_off = 0;
+        uint64_t last_use = 0;
+    };
+    RopeTable rope_tables[2];
+    uint64_t rope_clock = 0;
     // optional timing of the dominant kernel of each call (CUDA events on the launch stream)
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;

@@ -735,6 +735,40 @@ __global__ void __launch_bounds__(256) rotate_to_f16_kernel(const __nv_bfloat16 
 
 bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// (cos, sin) table of `rows` positions starting at pos_off, from the context's cache or computed now on its stream.
+int rope_table(flat_ctx *ctx, const InvFreq &f, int half_dim, int rows, int64_t pos_off, const float2 **out) {
+    flat_ctx::RopeTable *slot = nullptr;
+    for (auto &t : ctx->rope_tables) {
+        if (t.rows >= rows && t.half_dim == half_dim && t.pos_off == pos_off &&
+            std::memcmp(t.inv_freq, f.f, sizeof(float) * half_dim) == 0) {
+            t.last_use = ++ctx->rope_clock;
+            *out = static_cast<const float2 *>(t.dev);
+            return FLAT_OK;
+        }
+        if (!slot || t.last_use < slot->last_use) slot = &t;
+    }
+    const uint64_t bytes = (uint64_t)rows * half_dim * sizeof(float2);
+    if (slot->bytes < bytes) {
+        slot->rows = 0;
+        if (slot->dev) FLAT_CUDA_OK(ctx, cudaFree(slot->dev));  // waits for kernels that still read it
+        slot->dev = nullptr;
+        slot->bytes = 0;
+        FLAT_CUDA_OK(ctx, cudaMalloc(&slot->dev, bytes));
+        slot->bytes = bytes;
+    }
+    const int64_t n = (int64_t)rows * half_dim;
+    rope_table_kernel<<<(int)std::min<int64_t>((n + 255) / 256, 4096), 256, 0, ctx->stream>>>(
+        static_cast<float2 *>(slot->dev), rows, half_dim, pos_off, f);
+    ctx->launches += 1;
+    std::memcpy(slot->inv_freq, f.f, sizeof(float) * half_dim);
+    slot->half_dim = half_dim;
+    slot->rows = rows;
+    slot->pos_off = pos_off;
+    slot->last_use = ++ctx->rope_clock;
+    *out = static_cast<const float2 *>(slot->dev);
+    return FLAT_OK;
+}
+
 }  // namespace
 
 bool forward_sm100_supported(const FwdParams &p) {
@@ -755,12 +789,10 @@ bool forward_sm100_supported(const FwdParams &p) {
     return true;
 }
 
-// scratch: [rotated fp16 K (rope_k)] [Q (cos, sin) table (rope_q)] [K (cos, sin) table (rope_k)]
+// scratch: rotated fp16 K (rope_k); the (cos, sin) tables live in the context's table cache
 uint64_t forward_sm100_workspace_bytes(const FwdParams &p) {
     uint64_t bytes = 0;
     if (p.rope_k) bytes += ((uint64_t)p.batch * p.kv_heads * p.kv_len * p.head_dim * 2 + 255) & ~uint64_t(255);
-    if (p.rope_q) bytes += ((uint64_t)p.q_len * (p.head_dim / 2) * sizeof(float2) + 255) & ~uint64_t(255);
-    if (p.rope_k) bytes += ((uint64_t)p.kv_len * (p.head_dim / 2) * sizeof(float2) + 255) & ~uint64_t(255);
     return bytes;
 }
 
@@ -778,26 +810,16 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     if (p.rope_q) {
         InvFreq f;
         std::memcpy(f.f, p.inv_freq, sizeof f.f);
-        uint64_t off = 0;
         __half *rk = reinterpret_cast<__half *>(scratch);
-        if (p.rope_k) off += ((uint64_t)p.batch * p.kv_heads * p.kv_len * D * 2 + 255) & ~uint64_t(255);
-        float2 *qt = reinterpret_cast<float2 *>(scratch + off);
-        off += ((uint64_t)p.q_len * (D / 2) * sizeof(float2) + 255) & ~uint64_t(255);
-        float2 *kt = reinterpret_cast<float2 *>(scratch + off);
-        const int64_t qn = (int64_t)p.q_len * (D / 2);
-        rope_table_kernel<<<(int)std::min<int64_t>((qn + 255) / 256, 4096), 256, 0, ctx->stream>>>(qt, p.q_len, D / 2,
-                                                                                                  p.q_rope_off, f);
-        ctx->launches += 1;
-        q_table = qt;
+        if ((st = rope_table(ctx, f, D / 2, p.q_len, p.q_rope_off, &q_table))) return st;
         if (p.rope_k) {
-            const int64_t kn = (int64_t)p.kv_len * (D / 2);
-            rope_table_kernel<<<(int)std::min<int64_t>((kn + 255) / 256, 4096), 256, 0, ctx->stream>>>(kt, p.kv_len, D / 2,
-                                                                                                      p.k_rope_off, f);
+            const float2 *kt = nullptr;
+            if ((st = rope_table(ctx, f, D / 2, p.kv_len, p.k_rope_off, &kt))) return st;
             const int64_t kvecs = (int64_t)p.batch * p.kv_heads * p.kv_len * (D / 8);
             const int blocks = (int)std::min<int64_t>((kvecs + 255) / 256, (int64_t)ctx->sm_count * 16);
             rotate_to_f16_kernel<<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const __nv_bfloat16 *>(p.k), rk, kt,
                                                                   p.kv_heads, p.kv_len, D, p.kv_bs, p.kv_hs, p.kv_rs, kvecs);
-            ctx->launches += 2;
+            ctx->launches += 1;
             k_ptr = rk;
             k_rs = D; k_hs = (int64_t)p.kv_len * D; k_bs = k_hs * p.kv_heads;
             k_f16 = true;
