@@ -731,24 +731,29 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_sm100_kernel(const __grid_
 }
 #undef TRS
 
-// delta = dO . O and -LSE*log2(e), one warp per row
+// delta = dO . O and -LSE*log2(e).  A thread takes 8 elements (16 bytes) of a row of each tensor, head_dim / 8
+// neighbouring lanes share a row, so a warp covers 256 / head_dim rows with full-width loads.
 __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16 *__restrict__ d_out,
                                                        const __nv_bfloat16 *__restrict__ out, const float *__restrict__ lse,
                                                        float *__restrict__ delta, float *__restrict__ neg_lse2, int64_t rows,
                                                        int head_dim) {
-    const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-    if (row >= rows) return;
+    const int lanes_per_row = head_dim / 8;  // 8 or 16
+    const int rows_per_block = 256 / lanes_per_row;
+    const int sub = threadIdx.x % lanes_per_row;
+    const int64_t row = (int64_t)blockIdx.x * rows_per_block + threadIdx.x / lanes_per_row;
     float acc = 0.f;
-    for (int d = lane * 2; d < head_dim; d += 64) {
-        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(d_out + row * head_dim + d));
-        const float2 o = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(out + row * head_dim + d));
-        acc = fmaf(a.x, o.x, acc);
-        acc = fmaf(a.y, o.y, acc);
-    }
+    if (row < rows) {
+        const uint4 a = __ldg(reinterpret_cast<const uint4 *>(d_out + row * head_dim) + sub);
+        const uint4 o = __ldg(reinterpret_cast<const uint4 *>(out + row * head_dim) + sub);
+        const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, ow[4] = {o.x, o.y, o.z, o.w};
 #pragma unroll
-    for (int w = 16; w >= 1; w >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
-    if (lane == 0) {
+        for (int e = 0; e < 4; ++e) {
+            acc = fmaf(__uint_as_float(aw[e] << 16), __uint_as_float(ow[e] << 16), acc);
+            acc = fmaf(__uint_as_float(aw[e] & 0xffff0000u), __uint_as_float(ow[e] & 0xffff0000u), acc);
+        }
+    }
+    for (int w = lanes_per_row / 2; w >= 1; w >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
+    if (sub == 0 && row < rows) {
         delta[row] = acc;
         neg_lse2[row] = -lse[row] * kLog2e;
     }
@@ -778,7 +783,8 @@ int launch_backward_sm100(flat_ctx *ctx, const BwdParams &p) {
     const int64_t rows = (int64_t)p.batch * p.q_heads * N;
     float *delta = reinterpret_cast<float *>(scratch_ptr(ctx));
     float *neg_lse2 = delta + rows;
-    bwd_prep_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, ctx->stream>>>(
+    const int prep_rows_per_block = 256 / (D / 8);
+    bwd_prep_kernel<<<(unsigned)((rows + prep_rows_per_block - 1) / prep_rows_per_block), 256, 0, ctx->stream>>>(
         static_cast<const __nv_bfloat16 *>(p.d_out), static_cast<const __nv_bfloat16 *>(p.out), p.lse, delta, neg_lse2, rows, D);
     ctx->launches += 1;
 
