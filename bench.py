@@ -513,7 +513,7 @@ def main():
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": "C2 GQA+RoPE causal prefill (Llama-3-8B shape): B=4 per GPU, Hq=32, Hkv=8, N=4096, D=128, "
                                "bf16, theta=5e5, O + f32 LSE", "flop_per_step_per_gpu": flops,
-                   "inputs": "seeded N(0,1) rounded to bf16; 192 MiB of Q/K/V + 160 MiB rotated operands per step "
+                   "inputs": "seeded N(0,1) rounded to bf16; 192 MiB of Q/K/V + 32 MiB of rotated K + 136 MiB of O and LSE per step "
                              "exceed the 126 MB L2", "sharding": "independent batches per rank, no collective",
                    "host_cores_bound": numa},
         "e2e": {"value": world * flops / (ms_e2e / e2e_steps * 1e-3) / 1e12, "unit": "TFLOP/s",

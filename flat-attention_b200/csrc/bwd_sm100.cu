@@ -11,8 +11,10 @@
 //    the query columns; LSE and delta are per-column values read from shared memory), then
 //    dV += P^T dO_i and dK += dS^T Q_i (A operand from TMEM) accumulate in TMEM over all tiles and
 //    all heads of the group: the GQA reduction never leaves the SM.
+//    The elementwise work is split in two phases (P^T, then dS^T) that overlap the MMAs.
 //  * Q-stationary (dQ): one CTA owns 128 queries of one (batch, q_head); (K_j, V_j) stream;
-//    S = Q K_j^T, dP = dO V_j^T, dS in place, dQ += dS K_j in TMEM.
+//    S = Q K_j^T (Q as TMEM A operand), dP = dO V_j^T, dS in TMEM columns of its own, dQ += dS K_j
+//    in TMEM; the next tile's products are issued while the elementwise warps work.
 //
 // The score recompute is done twice (7 GEMM units instead of 5); in exchange nothing is accumulated
 // through global memory.  A prologue kernel writes delta and -LSE*log2(e) to context scratch.
@@ -54,7 +56,7 @@ struct BwdKernelParams {
     CUtensorMap map_q, map_k, map_v, map_do;
     const float *neg_lse2;  // -LSE * log2(e), [B, Hq, N]
     const float *delta;     // dO . O, [B, Hq, N]
-    void *out0, *out1;      // f32 outputs.  KV-stationary: dV, dK; Q-stationary: dQ, unused
+    void *out0, *out1;      // f32 outputs.  KV-stationary kernel: dV, dK; dQ kernel: dQ, null
     int batch, q_heads, kv_heads, seq_len, group, n_tiles;
     int causal;
     float scale, scale_log2;
