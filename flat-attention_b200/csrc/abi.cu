@@ -225,10 +225,18 @@ int forward_common(flat_ctx *ctx, const ForwardCall &call, const flat_attention_
         if (bytes > kWorkspaceMeta)
             return fail(ctx, FLAT_ERR_DISPATCH_LIMIT, "variable-length batch of %llu exceeds %llu sequences",
                         (unsigned long long)shape->batch, (unsigned long long)(kWorkspaceMeta / sizeof(flat_varlen_sequence)));
-        if ((st = ensure_workspace(ctx, kWorkspaceMeta))) return st;
+        p.varlen_rope_min = p.varlen_rope_max = call.varlen_host[0].query_rope_offset;
+        for (uint64_t b = 1; b < shape->batch; ++b) {
+            p.varlen_rope_min = std::min<int64_t>(p.varlen_rope_min, call.varlen_host[b].query_rope_offset);
+            p.varlen_rope_max = std::max<int64_t>(p.varlen_rope_max, call.varlen_host[b].query_rope_offset);
+        }
+        // the metadata sits at the start of the workspace: size it for the kernel first, a later growth would move it
+        p.varlen = reinterpret_cast<const flat_varlen_sequence *>(call.varlen_host);  // non-null for the capability test
+        const bool tensor_path = call.dtype == FLAT_BF16 && forward_sm100_supported(p);
+        if ((st = ensure_workspace(ctx, kWorkspaceMeta + (tensor_path ? forward_sm100_workspace_bytes(p) : 0)))) return st;
         FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ctx->workspace, call.varlen_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
         p.varlen = static_cast<const flat_varlen_sequence *>(ctx->workspace);
-        return launch_forward_simt(ctx, call.dtype, p);
+        return tensor_path ? launch_forward_sm100(ctx, p) : launch_forward_simt(ctx, call.dtype, p);
     }
     if (params_out) {
         *params_out = p;

@@ -122,6 +122,7 @@ struct FwdParams {
     int rope_q, rope_k;
     int64_t q_rope_off, k_rope_off;
     const flat_varlen_sequence *varlen;  // device, [batch] or null
+    int64_t varlen_rope_min, varlen_rope_max;  // smallest / largest query_rope_offset of the batch (host-side copy)
     const int32_t *page_table;           // device, [batch, max_pages] or null
     int page_size, max_pages;
     int64_t page_row_stride;             // elements per physical row (kv_heads*head_dim)

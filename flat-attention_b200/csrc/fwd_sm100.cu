@@ -97,6 +97,8 @@ struct KernelParams {
     int q_blocks;
     long long total_items;  // q_blocks * batch * q_heads
     DeviceStatus *status;
+    const flat_varlen_sequence *varlen;  // per batch element: active lengths, causal and RoPE offsets; null = uniform
+    long long rope_table_base;           // varlen: position of the table's first row (the smallest query_rope_offset)
     const float2 *rope_q_table;  // (cos, sin) of row r, pair j at [r * D/2 + j]; null = Q is used as loaded
     float2 rope_step[kMaxHeadDim / 2];  // (cos, sin)(rows_per_step * inv_freq[j]): advances a row's rotation
     long long *trace;
@@ -123,6 +125,9 @@ __device__ __forceinline__ void record_timeout(const KernelParams &p, int where)
 struct WorkItem {
     int b, h, kvh, r0;
     int n_tiles[2];  // KV tiles each of the two Q tiles visits (0 = the tile starts past q_len)
+    int q_len, kv_len;     // this batch element's live rows (the call's lengths unless it is a variable-length batch)
+    long long causal_off;  // key k is visible to local row q iff k <= causal_off + q
+    int table_row0;        // row of the (cos, sin) table that belongs to local query row 0
 };
 
 __device__ __forceinline__ WorkItem make_item(const KernelParams &p, int lin) {
@@ -135,15 +140,26 @@ __device__ __forceinline__ WorkItem make_item(const KernelParams &p, int lin) {
     it.h = bh % p.q_heads;
     it.kvh = it.h / p.group;
     it.r0 = qb * 2 * kTileRows;
+    it.q_len = p.q_len;
+    it.kv_len = p.kv_len;
+    it.causal_off = p.causal_off;
+    it.table_row0 = 0;
+    if (p.varlen) {  // padded batch: src/wgpu_external_variable.rs:21-33
+        const flat_varlen_sequence m = p.varlen[it.b];
+        it.q_len = (int)m.active_query_len;
+        it.kv_len = (int)m.active_kv_len;
+        it.causal_off = m.causal_query_offset;
+        it.table_row0 = (int)((long long)m.query_rope_offset - p.rope_table_base);
+    }
 #pragma unroll
     for (int w = 0; w < 2; ++w) {
         const int first = it.r0 + w * kTileRows;
-        long long visible = p.kv_len;
+        long long visible = it.kv_len;
         if (p.causal) {
-            const long long last_row = min(first + kTileRows - 1, p.q_len - 1);
-            visible = min((long long)p.kv_len, p.causal_off + last_row + 1);
+            const long long last_row = min(first + kTileRows - 1, it.q_len - 1);
+            visible = min((long long)it.kv_len, it.causal_off + last_row + 1);
         }
-        it.n_tiles[w] = first < p.q_len ? (int)((visible + kTileRows - 1) / kTileRows) : 0;
+        it.n_tiles[w] = first < it.q_len ? (int)((visible + kTileRows - 1) / kTileRows) : 0;
     }
     return it;
 }
@@ -452,12 +468,12 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                 const WorkItem it = make_item(p, item_index(p, k));
                 run = it.n_tiles[w] > 0;
                 const int n = it.n_tiles[w];
-                int lim = p.kv_len - 1;  // last visible key of this row
+                int lim = it.kv_len - 1;  // last visible key of this row
                 int lim_first = lim;     // ... and of the tile's first row: tiles below it need no mask at all
                 if (p.causal) {
                     const int first = it.r0 + w * kTileRows;
-                    lim = (int)min((long long)lim, p.causal_off + first + row_in_tile);
-                    lim_first = (int)min((long long)lim_first, p.causal_off + first);
+                    lim = (int)min((long long)lim, it.causal_off + first + row_in_tile);
+                    lim_first = (int)min((long long)lim_first, it.causal_off + first);
                 }
 
                 // Online softmax, log2 domain, one thread per row; the whole 128-column score row sits in
@@ -575,7 +591,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     // rounding of the fp16 result.
                     float cc[4], ss[4], cstep[4], sstep[4];
                     {
-                        const int rr = min(first_row + lane_base + lane / CH, p.q_len - 1);
+                        const int rr = nx.table_row0 + min(first_row + lane_base + lane / CH, nx.q_len - 1);
                         const float4 *tp = reinterpret_cast<const float4 *>(p.rope_q_table + (long long)rr * (D / 2)) + 2 * ch;
                         const float4 cs0 = __ldg(tp), cs1 = __ldg(tp + 1);  // (c, s, c, s) x 2
                         cc[0] = cs0.x; ss[0] = cs0.y; cc[1] = cs0.z; ss[1] = cs0.w;
@@ -607,7 +623,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                                     cc[e] = c1;
                                 }
                             }
-                            if (first_row + rt >= p.q_len) continue;  // rows past q_len were zero-filled by TMA
+                            if (first_row + rt >= nx.q_len) continue;  // rows past q_len are not used
                             const uint4 raw = *reinterpret_cast<const uint4 *>(tile + off);
                             const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
                             uint32_t hi[4];
@@ -641,7 +657,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                 const WorkItem it = make_item(p, item_index(p, k));
                 const int row = it.r0 + w * kTileRows + row_in_tile, b = it.b, h = it.h;
                 const float inv = 1.0f / l;
-                const bool store = row < p.q_len;
+                const bool store = row < it.q_len;
                 __nv_bfloat16 *op = reinterpret_cast<__nv_bfloat16 *>(p.o) + (long long)b * p.o_bs + (long long)h * p.o_hs +
                                     (long long)row * p.o_rs;
                 uint32_t r[32];
@@ -701,6 +717,10 @@ __global__ void __launch_bounds__(256) rope_table_kernel(float2 *__restrict__ ta
         sincosf(angle, &s, &c);
         table[i] = make_float2(c, s);
     }
+}
+
+__global__ void __launch_bounds__(256) fill_u32_kernel(uint32_t *__restrict__ dst, uint32_t value, int64_t n) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) dst[i] = value;
 }
 
 // K rotation prologue: x (bf16, strided) -> y (fp16, compact [B, H, N, D]) with interleaved pairs
@@ -773,7 +793,12 @@ int rope_table(flat_ctx *ctx, const InvFreq &f, int half_dim, int rows, int64_t 
 
 bool forward_sm100_supported(const FwdParams &p) {
     if (p.head_dim != 64 && p.head_dim != 128) return false;
-    if (p.varlen) return false;
+    if (p.varlen) {
+        // padded variable-length batch: one (cos, sin) table spans every sequence's query positions
+        if (p.page_table || !p.rope_q) return false;
+        const int64_t rows = p.varlen_rope_max - p.varlen_rope_min + p.q_len;
+        if (rows * (p.head_dim / 2) * (int64_t)sizeof(float2) > (64ll << 20)) return false;
+    }
     if (p.q_len < 32 || p.kv_len < 32) return false;  // tiny shapes: the generic kernel is the better fit
     if (!aligned16(p.q) || !aligned16(p.k) || !aligned16(p.v) || !aligned16(p.o)) return false;
     const int64_t strides[] = {p.q_bs, p.q_hs, p.q_rs, p.kv_bs, p.kv_hs, p.kv_rs, p.o_bs, p.o_hs, p.o_rs};
@@ -811,7 +836,12 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
         InvFreq f;
         std::memcpy(f.f, p.inv_freq, sizeof f.f);
         __half *rk = reinterpret_cast<__half *>(scratch);
-        if ((st = rope_table(ctx, f, D / 2, p.q_len, p.q_rope_off, &q_table))) return st;
+        if (p.varlen) {
+            const int rows = (int)(p.varlen_rope_max - p.varlen_rope_min) + p.q_len;
+            if ((st = rope_table(ctx, f, D / 2, rows, p.varlen_rope_min, &q_table))) return st;
+        } else if ((st = rope_table(ctx, f, D / 2, p.q_len, p.q_rope_off, &q_table))) {
+            return st;
+        }
         if (p.rope_k) {
             const float2 *kt = nullptr;
             if ((st = rope_table(ctx, f, D / 2, p.kv_len, p.k_rope_off, &kt))) return st;
@@ -857,6 +887,17 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     kp.q_blocks = (p.q_len + 2 * kTileRows - 1) / (2 * kTileRows);
     kp.status = ctx->dev_status;
     kp.rope_q_table = q_table;
+    kp.varlen = p.varlen;
+    kp.rope_table_base = p.varlen ? p.varlen_rope_min : 0;
+    if (p.varlen) {
+        // padded query rows: O = 0, LSE = -inf (src/asymmetric_grouped.rs:103-104); the kernel writes only live rows.
+        // The projection layout of this entry point makes O one contiguous block.
+        const int64_t o_elems = (int64_t)p.batch * p.q_len * p.q_heads * D, lse_elems = (int64_t)p.batch * p.q_heads * p.q_len;
+        FLAT_CUDA_OK(ctx, cudaMemsetAsync(p.o, 0, o_elems * 2, ctx->stream));
+        fill_u32_kernel<<<(unsigned)std::min<int64_t>((lse_elems + 255) / 256, 4096), 256, 0, ctx->stream>>>(
+            reinterpret_cast<uint32_t *>(p.lse), 0xff800000u, lse_elems);
+        ctx->launches += 1;
+    }
     if (q_table) {
         const double rows_per_step = 32.0 / (D / 8);
         for (int j = 0; j < D / 2; ++j) {

@@ -172,3 +172,36 @@ def test_host_slice_forward_pipelined_over_batch_matches_resident_call():
         dev_out2 = c.create_output_buffer(dtype, shp)
         c.forward_projection_rope(dtype, shp, fa.config(True), rot, qp.cuda(), kp.cuda(), vp.cuda(), dev_out2)
         assert torch.equal(host_out2, dev_out2.cpu())
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Nq,Nkv,D,causal,kvoff,meta", [
+    (3, 8, 2, 300, 400, 128, True, 5, [(300, 400, 100, 105), (1, 33, 32, 37), (130, 129, 0, 900)]),
+    (2, 4, 4, 260, 260, 64, False, 0, [(129, 260, 0, 0), (260, 64, 0, 7)]),
+    (40, 4, 1, 256, 256, 128, True, 0, [(1 + (37 * i) % 256, 1 + (91 * i) % 256, 0, i) for i in range(40)]),
+])
+def test_variable_length_projection_bf16(B, Hq, Hkv, Nq, Nkv, D, causal, kvoff, meta):
+    """Padded variable-length batch (tests/wgpu_external_variable.rs:160-387) on the tensor-core path: per-sequence
+    active lengths, causal offsets and RoPE offsets; the padding is poisoned and must not leak; padded query rows
+    come back as O = 0, LSE = -inf."""
+    theta = 5e5
+    q = randn(B * Nq * Hq * D, 1).reshape(B, Nq, Hq * D).copy()
+    k = randn(B * Nkv * Hkv * D, 2).reshape(B, Nkv, Hkv * D).copy()
+    v = randn(B * Nkv * Hkv * D, 3).reshape(B, Nkv, Hkv * D).copy()
+    for b, (aq, akv, _, _) in enumerate(meta):
+        q[b, aq:] = bf16_round(np.float32(1.0e20))
+        k[b, akv:] = bf16_round(np.float32(-1.0e20))
+        v[b, akv:] = bf16_round(np.float32(1.0e20))
+    seqs = [fa.VarlenSequence(*m) for m in meta]
+    launches = ctx().launch_count()
+    o, l = run_forward("projection_rope_varlen", fa.BF16, fa.shape(B, Hq, Hkv, Nq, Nkv, D), fa.config(causal), q, k, v,
+                       rot=fa.rotary(theta, 0, kvoff), sequences=seqs)
+    # K rotation, padding fill and the tcgen05 kernel (plus the table kernels): the generic kernel is a single launch
+    assert ctx().launch_count() - launches >= 3
+    o, l = o.reshape(B, Nq, Hq, D), l.reshape(B, Hq, Nq)
+    for b, (aq, akv, coff, qr) in enumerate(meta):
+        eo, el = ob.forward_reference_projection_grouped_rope_asymmetric(
+            q[b, :aq], k[b, :akv], v[b, :akv], ob._shape(1, Hq, Hkv, aq, akv, D, coff), theta, qr, kvoff, causal)
+        check(o[b, :aq].reshape(-1), l[b, :, :aq].reshape(-1), eo, np.asarray(el).reshape(Hq, aq).reshape(-1), f"sequence {b}")
+        assert np.all(o[b, aq:] == 0.0)
+        assert np.all(l[b, :, aq:].view(np.uint32) == 0xFF800000)
+    assert ctx().device_status() == 0
