@@ -1,5 +1,5 @@
-// tcgen05 backward (LSE recompute) for bf16, head_dim 64 or 128, head-major, equal length,
-// seq_len a multiple of 128.  Math per visible (query q, key k) pair (src/backward_grouped.rs:56-88):
+// tcgen05 backward (LSE recompute) for bf16, head_dim 64 or 128, head-major, equal length, any
+// seq_len (rows past it are zero-filled by TMA, their LSE / delta slots are zero).  Math per visible (query q, key k) pair (src/backward_grouped.rs:56-88):
 //   P = exp(S*scale - LSE),  dP = dO.V,  dS = P*(dP - delta),  delta = dO.O
 //   dV[kv_head] += P^T dO,  dK[kv_head] += scale * dS^T Q,  dQ += scale * dS K
 // Two deterministic kernels, no atomics, results bitwise repeatable like the reference:
@@ -58,6 +58,7 @@ struct BwdKernelParams {
     const float *delta;     // dO . O, [B, Hq, N]
     void *out0, *out1;      // f32 outputs.  KV-stationary kernel: dV, dK; dQ kernel: dQ, null
     int batch, q_heads, kv_heads, seq_len, group, n_tiles;
+    int seq_pad;            // seq_len rounded up to whole tiles: row stride of neg_lse2 / delta
     int causal;
     float scale, scale_log2;
     uint32_t idesc_k, idesc_mn;
@@ -192,7 +193,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                                 rg_full(s));
                 }
                 // per-query LSE and delta of the streamed query tile
-                const long long row0 = ((long long)b * p.q_heads + hs) * p.seq_len + (long long)t * kTile;
+                const long long row0 = ((long long)b * p.q_heads + hs) * p.seq_pad + (long long)t * kTile;
                 bulk_copy_g2s(smem_u32(stage + 2 * C::kTileBytes), p.neg_lse2 + row0, 512, rg_full(s));
                 bulk_copy_g2s(smem_u32(stage + 2 * C::kTileBytes + 512), p.delta + row0, 512, rg_full(s));
             }
@@ -381,6 +382,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
             tc_fence_after();
             // each warp group writes half of the head dimension of the accumulator rows
             const long long out_row = ((long long)b * heads + h) * p.seq_len + (long long)t_own * kTile + row_local;
+            const bool store = t_own * kTile + row_local < p.seq_len;  // keys past seq_len were zero-filled, not real
             constexpr int kColsPerHalf = D / 2;
 #pragma unroll
             for (int a = 0; a < 2; ++a) {
@@ -393,6 +395,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                     tmem_ld32(t_acc + c * 32, r);
                     tc_wait_ld();
                     float4 *dst = reinterpret_cast<float4 *>(op + c * 32);
+                    if (!store) continue;
 #pragma unroll
                     for (int q4 = 0; q4 < 8; ++q4)
                         dst[q4] = make_float4(__uint_as_float(r[q4 * 4]) * mul, __uint_as_float(r[q4 * 4 + 1]) * mul,
@@ -632,8 +635,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_sm100_kernel(const __grid_
 
         uint64_t c2, nl2, dl2;
         {
-            const long long row = ((long long)b * p.q_heads + h) * p.seq_len + (long long)t_own * kTile + row_local;
-            const float my_neg_lse2 = p.neg_lse2[row], my_delta = p.delta[row];
+            const long long row = ((long long)b * p.q_heads + h) * p.seq_pad + (long long)t_own * kTile + row_local;
+            const float my_neg_lse2 = p.neg_lse2[row], my_delta = p.delta[row];  // zero in the padding
             asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(p.scale_log2));
             asm("mov.b64 %0, {%1, %1};" : "=l"(nl2) : "f"(my_neg_lse2));
             asm("mov.b64 %0, {%1, %1};" : "=l"(dl2) : "f"(my_delta));
@@ -648,6 +651,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_sm100_kernel(const __grid_
             tc_fence_after();
             if (warp == 0 && lane == 0) TRACE(0, it, 0);
             const bool diag = p.causal && it == t_own;
+            const int live_keys = p.seq_len - it * kTile;  // < 128 only in the last key tile of a ragged sequence
+            const bool edge = diag || live_keys < kTile;
             uint32_t x[64], y[64];
             tmem_ld32(t_x, x);
             tmem_ld32(t_x + 32, x + 32);
@@ -670,10 +675,13 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_sm100_kernel(const __grid_
                 asm("mov.b64 {%0, %1}, %2;" : "=f"(t0), "=f"(t1) : "l"(t2));
                 asm("mov.b64 {%0, %1}, %2;" : "=f"(e0), "=f"(e1) : "l"(d2));
                 float p0 = ex2(t0), p1 = ex2(t1);
-                if (diag) {  // visible iff key <= query: row = query, column = key
+                if (edge) {
+                    // visible iff key <= query (diagonal tile: row = query, column = key) and the key exists: keys past
+                    // seq_len are zero rows, whose score 0 could still give a huge P against a very negative LSE
                     const int c0 = half * 64 + i;
-                    if (c0 > row_local) p0 = 0.f;
-                    if (c0 + 1 > row_local) p1 = 0.f;
+                    const int last = diag ? min(row_local, live_keys - 1) : live_keys - 1;
+                    if (c0 > last) p0 = 0.f;
+                    if (c0 + 1 > last) p1 = 0.f;
                 }
                 const __nv_bfloat162 dsb = __floats2bfloat162_rn(p0 * e0, p1 * e1);
                 ds[i >> 1] = *reinterpret_cast<const uint32_t *>(&dsb);
@@ -703,12 +711,14 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_sm100_kernel(const __grid_
             constexpr int kColsPerHalf = D / 2;
             float *op = reinterpret_cast<float *>(p.out0) + out_row * D + half * kColsPerHalf;
             const uint32_t t_acc = t_lane + kColAcc + half * kColsPerHalf;
+            const bool store = t_own * kTile + row_local < p.seq_len;  // queries past seq_len were zero-filled, not real
 #pragma unroll
             for (int c = 0; c < kColsPerHalf / 32; ++c) {
                 uint32_t r[32];
                 tmem_ld32(t_acc + c * 32, r);
                 tc_wait_ld();
                 float4 *dst = reinterpret_cast<float4 *>(op + c * 32);
+                if (!store) continue;
 #pragma unroll
                 for (int q4 = 0; q4 < 8; ++q4)
                     dst[q4] = make_float4(__uint_as_float(r[q4 * 4]) * p.scale, __uint_as_float(r[q4 * 4 + 1]) * p.scale,
@@ -738,7 +748,7 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_sm100_kernel(const __grid_
 __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16 *__restrict__ d_out,
                                                        const __nv_bfloat16 *__restrict__ out, const float *__restrict__ lse,
                                                        float *__restrict__ delta, float *__restrict__ neg_lse2, int64_t rows,
-                                                       int head_dim) {
+                                                       int head_dim, int seq_len, int seq_pad) {
     const int lanes_per_row = head_dim / 8;  // 8 or 16
     const int rows_per_block = 256 / lanes_per_row;
     const int sub = threadIdx.x % lanes_per_row;
@@ -756,8 +766,9 @@ __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16 *__re
     }
     for (int w = lanes_per_row / 2; w >= 1; w >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
     if (sub == 0 && row < rows) {
-        delta[row] = acc;
-        neg_lse2[row] = -lse[row] * kLog2e;
+        const int64_t dst = row / seq_len * seq_pad + row % seq_len;  // rows of a (batch, head) padded to whole tiles
+        delta[dst] = acc;
+        neg_lse2[dst] = -lse[row] * kLog2e;
     }
 }
 
@@ -767,7 +778,6 @@ bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 
 
 bool backward_sm100_supported(const BwdParams &p) {
     if (p.head_dim != 64 && p.head_dim != 128) return false;
-    if (p.seq_len % kTile != 0) return false;
     const void *ptrs[] = {p.q, p.k, p.v, p.d_out, p.out, p.dq, p.dk, p.dv};
     for (const void *x : ptrs)
         if (!aligned16(x)) return false;
@@ -775,7 +785,8 @@ bool backward_sm100_supported(const BwdParams &p) {
 }
 
 uint64_t backward_sm100_workspace_bytes(const BwdParams &p) {
-    return 2 * (uint64_t)p.batch * p.q_heads * p.seq_len * sizeof(float);
+    const uint64_t seq_pad = ((uint64_t)p.seq_len + kTile - 1) / kTile * kTile;
+    return 2 * (uint64_t)p.batch * p.q_heads * seq_pad * sizeof(float);
 }
 
 int launch_backward_sm100(flat_ctx *ctx, const BwdParams &p) {
@@ -783,11 +794,16 @@ int launch_backward_sm100(flat_ctx *ctx, const BwdParams &p) {
     if (st) return st;
     const int D = p.head_dim, N = p.seq_len;
     const int64_t rows = (int64_t)p.batch * p.q_heads * N;
+    const int seq_pad = (N + kTile - 1) / kTile * kTile;
+    const int64_t rows_pad = (int64_t)p.batch * p.q_heads * seq_pad;
     float *delta = reinterpret_cast<float *>(scratch_ptr(ctx));
-    float *neg_lse2 = delta + rows;
+    float *neg_lse2 = delta + rows_pad;
+    // the slots of rows past seq_len must hold finite values: with zeros the zero-filled Q / dO rows contribute nothing
+    if (seq_pad != N) FLAT_CUDA_OK(ctx, cudaMemsetAsync(delta, 0, 2 * rows_pad * sizeof(float), ctx->stream));
     const int prep_rows_per_block = 256 / (D / 8);
     bwd_prep_kernel<<<(unsigned)((rows + prep_rows_per_block - 1) / prep_rows_per_block), 256, 0, ctx->stream>>>(
-        static_cast<const __nv_bfloat16 *>(p.d_out), static_cast<const __nv_bfloat16 *>(p.out), p.lse, delta, neg_lse2, rows, D);
+        static_cast<const __nv_bfloat16 *>(p.d_out), static_cast<const __nv_bfloat16 *>(p.out), p.lse, delta, neg_lse2, rows, D,
+        N, seq_pad);
     ctx->launches += 1;
 
     BwdKernelParams kp{};
@@ -799,7 +815,8 @@ int launch_backward_sm100(flat_ctx *ctx, const BwdParams &p) {
     kp.neg_lse2 = neg_lse2;
     kp.delta = delta;
     kp.batch = p.batch; kp.q_heads = p.q_heads; kp.kv_heads = p.kv_heads; kp.seq_len = N; kp.group = p.group;
-    kp.n_tiles = N / kTile;
+    kp.n_tiles = seq_pad / kTile;
+    kp.seq_pad = seq_pad;
     kp.causal = p.causal;
     kp.scale = p.scale;
     kp.scale_log2 = p.scale * kLog2e;

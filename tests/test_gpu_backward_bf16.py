@@ -17,7 +17,9 @@ def randn(n, seed):
     return bf16_round(torch.randn(n, generator=torch.Generator().manual_seed(seed)).numpy())
 
 
-@pytest.mark.parametrize("B,Hq,Hkv,N,D", [(1, 4, 2, 256, 128), (2, 2, 2, 128, 64), (1, 8, 1, 384, 128), (1, 2, 1, 512, 64)])
+@pytest.mark.parametrize("B,Hq,Hkv,N,D", [(1, 4, 2, 256, 128), (2, 2, 2, 128, 64), (1, 8, 1, 384, 128), (1, 2, 1, 512, 64),
+                                          # sequence lengths that are not whole 128-row tiles
+                                          (2, 4, 2, 200, 128), (1, 4, 1, 333, 64), (1, 2, 2, 40, 128)])
 @pytest.mark.parametrize("causal", [True, False])
 def test_backward_bf16_small(B, Hq, Hkv, N, D, causal):
     q, k, v, do = randn(B * Hq * N * D, 1), randn(B * Hkv * N * D, 2), randn(B * Hkv * N * D, 3), randn(B * Hq * N * D, 4)
