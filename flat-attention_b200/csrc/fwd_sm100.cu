@@ -87,6 +87,7 @@ struct KernelParams {
     void *o;
     float *lse;
     int64_t o_bs, o_hs, o_rs, lse_hs;
+    int o_align32;  // every O row starts on a 32-byte boundary: 256-bit stores may be used
     int batch, q_heads, kv_heads, q_len, kv_len, group;
     int causal;
     long long causal_off;
@@ -673,10 +674,20 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                                 __floats2bfloat162_rn(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
                             pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                         }
-                        uint4 *dst = reinterpret_cast<uint4 *>(op + c * 32);
+                        if (p.o_align32) {
+                            // 32-byte stores: a lane fills whole 32-byte sectors of its row
 #pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4)
-                            dst[q4] = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+                            for (int q8 = 0; q8 < 2; ++q8)
+                                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(op + c * 32 + q8 * 16),
+                                             "r"(pk[q8 * 8]), "r"(pk[q8 * 8 + 1]), "r"(pk[q8 * 8 + 2]), "r"(pk[q8 * 8 + 3]),
+                                             "r"(pk[q8 * 8 + 4]), "r"(pk[q8 * 8 + 5]), "r"(pk[q8 * 8 + 6]), "r"(pk[q8 * 8 + 7])
+                                             : "memory");
+                        } else {
+                            uint4 *dst = reinterpret_cast<uint4 *>(op + c * 32);
+#pragma unroll
+                            for (int q4 = 0; q4 < 4; ++q4)
+                                dst[q4] = make_uint4(pk[q4 * 4], pk[q4 * 4 + 1], pk[q4 * 4 + 2], pk[q4 * 4 + 3]);
+                        }
                     }
                 }
                 if (store) p.lse[((long long)b * p.q_heads + h) * p.lse_hs + row] = (m + log2f(l)) * kLn2;
@@ -873,6 +884,7 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     kp.o = p.o;
     kp.lse = p.lse;
     kp.o_bs = p.o_bs; kp.o_hs = p.o_hs; kp.o_rs = p.o_rs; kp.lse_hs = p.lse_hs;
+    kp.o_align32 = (reinterpret_cast<uintptr_t>(p.o) % 32 == 0 && p.o_bs % 16 == 0 && p.o_hs % 16 == 0 && p.o_rs % 16 == 0) ? 1 : 0;
     kp.batch = p.batch; kp.q_heads = p.q_heads; kp.kv_heads = p.kv_heads; kp.q_len = p.q_len; kp.kv_len = p.kv_len;
     kp.group = p.group;
     kp.causal = p.causal;
