@@ -35,6 +35,32 @@ def test_backward_bf16_small(B, Hq, Hkv, N, D, causal):
     assert ctx().device_status() == 0
 
 
+def test_random_shapes_tensor_core_backward_against_f32_path():
+    """Differential sweep: the tcgen05 backward (bf16) against the generic f32 backward (pinned to the oracle at 1e-4)
+    on the same bf16-rounded inputs and the same forward results, over seeded random shapes (ragged lengths, both
+    head dims, GQA groups, causal and not)."""
+    from tests.gpu_util import run_forward
+    rng = np.random.default_rng(77)
+    for case in range(12):
+        D = int(rng.choice([64, 128]))
+        Hkv = int(rng.choice([1, 2]))
+        Hq = Hkv * int(rng.choice([1, 2, 4]))
+        B = int(rng.integers(1, 3))
+        N = int(rng.integers(20, 600))
+        causal = bool(rng.integers(0, 2))
+        q, k, v, do = (randn(B * Hq * N * D, 10 + case), randn(B * Hkv * N * D, 30 + case), randn(B * Hkv * N * D, 50 + case),
+                       randn(B * Hq * N * D, 70 + case))
+        fo, fl = run_forward("grouped", fa.F32, fa.shape(B, Hq, Hkv, N, N, D), fa.config(causal), q, k, v)
+        fo = bf16_round(fo)
+        what = f"case {case}: B={B} Hq={Hq} Hkv={Hkv} N={N} D={D} causal={causal}"
+        got = run_backward(fa.BF16, B, Hq, Hkv, N, D, causal, None, q, k, v, do, fo, fl)
+        exp = run_backward(fa.F32, B, Hq, Hkv, N, D, causal, None, q, k, v, do, fo, fl)
+        for name, a, e in zip(("dQ", "dK", "dV"), got, exp):
+            assert np.isfinite(a).all(), (what, name)
+            assert np.abs(a - e).max() <= TOL, (what, name, float(np.abs(a - e).max()))
+        assert ctx().device_status() == 0, what
+
+
 def test_config5_grouped_backward_sampled_rows():
     """B=2, Hq=32, Hkv=8, N=8192, D=128, causal: forward on the device, backward on the device, oracle
     on sampled dQ rows and dK/dV rows (first/last rows, tile boundaries, random)."""

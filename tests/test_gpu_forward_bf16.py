@@ -205,3 +205,34 @@ def test_variable_length_projection_bf16(B, Hq, Hkv, Nq, Nkv, D, causal, kvoff, 
         assert np.all(o[b, aq:] == 0.0)
         assert np.all(l[b, :, aq:].view(np.uint32) == 0xFF800000)
     assert ctx().device_status() == 0
+
+
+def test_random_shapes_tensor_core_path_against_f32_path():
+    """Differential sweep: the tcgen05 kernel (bf16) against the generic f32 kernel (itself pinned to the oracle at
+    1e-4) on the same bf16-rounded inputs, over seeded random shapes: ragged and rectangular lengths, causal offsets,
+    RoPE offsets, both head dims, rotated and pre-rotated K, GQA groups, batches that give a CTA several items."""
+    rng = np.random.default_rng(20240607)
+    for case in range(24):
+        D = int(rng.choice([64, 128]))
+        Hkv = int(rng.choice([1, 2, 4]))
+        Hq = Hkv * int(rng.choice([1, 2, 4]))
+        B = int(rng.integers(1, 4))
+        Nq = int(rng.integers(32, 700))
+        extra = int(rng.integers(0, 500))
+        Nkv = Nq + extra
+        causal = bool(rng.integers(0, 2))
+        coff = extra if causal else 0          # the last query row sees every key
+        theta = float(rng.choice([1e4, 5e5]))
+        qr, kr = int(rng.integers(0, 5000)), int(rng.integers(0, 5000))
+        rotate_k = bool(rng.integers(0, 2))
+        q, k, v = randn(B * Nq * Hq * D, 100 + case), randn(B * Nkv * Hkv * D, 200 + case), randn(B * Nkv * Hkv * D, 300 + case)
+        if not rotate_k:  # the cache convention: K rotated once and stored in bf16
+            kpos = np.repeat(np.tile(np.arange(Nkv, dtype=np.uint64) + kr, B), Hkv)
+            k = bf16_round(ob.rotate_rows(k, D, kpos, theta))
+        shp = fa.shape(B, Hq, Hkv, Nq, Nkv, D, coff)
+        rot = fa.rotary(theta, qr, kr, rotate_k=rotate_k)
+        what = f"case {case}: B={B} Hq={Hq} Hkv={Hkv} Nq={Nq} Nkv={Nkv} D={D} causal={causal} rotate_k={rotate_k}"
+        o, l = run_forward("projection_rope_asymmetric", fa.BF16, shp, fa.config(causal), q, k, v, rot=rot)
+        eo, el = run_forward("projection_rope_asymmetric", fa.F32, shp, fa.config(causal), q, k, v, rot=rot)
+        check(o, l, eo, el, what)
+        assert ctx().device_status() == 0, what
