@@ -139,6 +139,33 @@ def forward_reference_projection_grouped_rope_asymmetric(q, k, v, shape: Shape, 
     return out[:q.size], lse
 
 
+def forward_reference_projection_grouped_rope_asymmetric_biased(q, k, v, shape: Shape, theta,
+                                                                query_rope_offset, kv_rope_offset,
+                                                                causal=False, softmax_scale=None, dense=None,
+                                                                alibi=None):
+    """src/attention_bias.rs:193-339.  `dense` is the [batch, q_heads, query_len, kv_len] bias;
+    `alibi` is (slopes, query_position_offset, kv_position_offset); neither means AttentionBias::None."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    out = np.empty(max(q.size, 1), np.float32)
+    lse = np.empty(max(shape.batch * shape.q_heads * shape.query_len, 1), np.float32)
+    cfg = make_config(causal, softmax_scale)
+    mode, values, q_off, kv_off = 0, np.zeros(1, np.float32), 0, 0
+    n = 0
+    if dense is not None:
+        mode, values = 1, _f32(dense)
+        n = values.size
+    elif alibi is not None:
+        mode, values, q_off, kv_off = 2, _f32(alibi[0]), alibi[1], alibi[2]
+        n = values.size
+    if values.size == 0:
+        values = np.zeros(1, np.float32)
+    _check(lib().flat_oracle_forward_projection_rope_asymmetric_biased(
+        _p(q), C.c_uint64(q.size), _p(k), C.c_uint64(k.size), _p(v), C.c_uint64(v.size), C.byref(shape),
+        C.byref(cfg), C.c_float(theta), C.c_uint64(query_rope_offset), C.c_uint64(kv_rope_offset),
+        C.c_int32(mode), _p(values), C.c_uint64(n), C.c_uint64(q_off), C.c_uint64(kv_off), _p(out), _p(lse)))
+    return out[:q.size], lse
+
+
 def forward_reference_projection_grouped_rope(q, k, v, batch, q_heads, kv_heads, seq_len, head_dim,
                                               theta, position_offset, causal=False,
                                               softmax_scale=None):

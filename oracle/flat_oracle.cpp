@@ -123,13 +123,30 @@ struct Rope {
     usize kv_offset = 0;    // rotary position of key 0
 };
 
+// AttentionBias::score (src/attention_bias.rs:61-97) for one (batch, q_head, query row): dense values of that row,
+// or slope * (key_position - query_position) with the difference formed in f64 and rounded to f32.
+struct RowBias {
+    int mode = 0;                 // 0 none, 1 dense, 2 ALiBi
+    const float *dense = nullptr; // [kv_len] values of this row
+    float slope = 0.0f;
+    usize query_position = 0, kv_offset = 0;
+    float at(usize key_pos) const {
+        if (mode == 1) return dense[key_pos];
+        if (mode == 2) {
+            double delta = (double)(kv_offset + key_pos) - (double)query_position;
+            return slope * (float)delta;
+        }
+        return 0.0f;
+    }
+};
+
 // One query row of the online-softmax update shared by every forward oracle:
 // src/lib.rs:478-516, src/grouped.rs:110-147, src/asymmetric_grouped.rs:260-298,
 // src/rotary_grouped.rs:92-150, src/projection_asymmetric.rs:120-232.
 // q_row/out_row address head_dim contiguous floats; key j lives at k0 + j*kv_stride.
 void attend_row(const float *q_row, const float *k0, const float *v0, usize kv_stride,
                 usize key_count, usize head_dim, float scale, const Rope &rope, float *out_row,
-                float *lse_out) {
+                float *lse_out, const RowBias *bias = nullptr) {
     float running_max = -std::numeric_limits<float>::infinity();
     float running_sum = 0.0f;
     for (usize d = 0; d < head_dim; ++d) out_row[d] = 0.0f;
@@ -153,6 +170,7 @@ void attend_row(const float *q_row, const float *k0, const float *v0, usize kv_s
             for (usize d = 0; d < head_dim; ++d) dot += q_row[d] * k_row[d];
         }
         float score = dot * scale;
+        if (bias) score = dot * scale + bias->at(key_pos);  // src/attention_bias.rs:282-283
         float new_max = fmaxf(running_max, score);
         float alpha = std::isinf(running_max) ? 0.0f : expf(running_max - new_max);
         float p = expf(score - new_max);
@@ -317,6 +335,65 @@ int32_t flat_oracle_forward_projection_rope_asymmetric(
     if (st) return st;
     ForwardArgs a{q, k, v, s, FLAT_LAYOUT_PROJECTION, cfg->causal, scale, true, theta, query_rope_offset, kv_rope_offset};
     return forward_full(a, out, lse);
+}
+
+// forward_reference_projection_grouped_rope_asymmetric_biased (src/attention_bias.rs:193-339).
+// bias_mode 0: none; 1: dense [batch, q_heads, query_len, kv_len] in `bias` (bias_n elements);
+// 2: ALiBi, `bias` holds q_heads slopes, positions start at bias_q_offset / bias_kv_offset.
+int32_t flat_oracle_forward_projection_rope_asymmetric_biased(
+    const float *q, uint64_t q_n, const float *k, uint64_t k_n, const float *v, uint64_t v_n,
+    const flat_attention_shape *shape, const flat_attention_config *cfg, float theta,
+    uint64_t query_rope_offset, uint64_t kv_rope_offset, int32_t bias_mode, const float *bias, uint64_t bias_n,
+    uint64_t bias_q_offset, uint64_t bias_kv_offset, float *out, float *lse) {
+    Shape s = to_shape(shape);
+    int st = validate_shape(s);
+    if (st) return st;
+    if ((st = validate_rotary(theta, query_rope_offset, s.head_dim, s.query_len))) return st;
+    if ((st = validate_rotary(theta, kv_rope_offset, s.head_dim, s.kv_len))) return st;
+    // AttentionBias::validate (src/attention_bias.rs:31-58) comes before the tensors are looked at
+    if (bias_mode == 1) {
+        usize expected;
+        if (!checked_mul(s.batch, s.q_heads, &expected) || !checked_mul(expected, s.query_len, &expected) ||
+            !checked_mul(expected, s.kv_len, &expected))
+            return FLAT_ERR_SHAPE_OVERFLOW;
+        if ((st = validate_input("attention bias", bias, bias_n, expected))) return st;
+    } else if (bias_mode == 2) {
+        if ((st = validate_input("ALiBi slopes", bias, bias_n, s.q_heads))) return st;
+        usize t;
+        if (!checked_add(bias_q_offset, s.query_len - 1, &t) || !checked_add(bias_kv_offset, s.kv_len - 1, &t))
+            return FLAT_ERR_POSITION_OVERFLOW;
+    }
+    float scale;
+    if ((st = prepare(s, q, q_n, k, k_n, v, v_n, cfg, true, theta, query_rope_offset, kv_rope_offset, &scale))) return st;
+    const usize group = s.q_heads / s.kv_heads, kv_stride = s.kv_heads * s.head_dim;
+    for (usize batch = 0; batch < s.batch; ++batch)
+        for (usize q_head = 0; q_head < s.q_heads; ++q_head)
+            for (usize query_pos = 0; query_pos < s.query_len; ++query_pos) {
+                usize kv_head = q_head / group;
+                usize key_count = s.kv_len, absolute = s.query_position_offset + query_pos;
+                if (cfg->causal && absolute + 1 < key_count) key_count = absolute + 1;
+                Rope rope;
+                rope.on = true;
+                rope.theta = theta;
+                rope.q_position = query_rope_offset + query_pos;
+                rope.kv_offset = kv_rope_offset;
+                RowBias rb;
+                rb.mode = bias_mode;
+                if (bias_mode == 1) rb.dense = bias + ((batch * s.q_heads + q_head) * s.query_len + query_pos) * s.kv_len;
+                if (bias_mode == 2) {
+                    rb.slope = bias[q_head];
+                    rb.query_position = bias_q_offset + query_pos;
+                    rb.kv_offset = bias_kv_offset;
+                }
+                const float *q_row = q + row_base(FLAT_LAYOUT_PROJECTION, batch, q_head, query_pos, s.q_heads, s.query_len, s.head_dim);
+                const float *k0 = k + row_base(FLAT_LAYOUT_PROJECTION, batch, kv_head, 0, s.kv_heads, s.kv_len, s.head_dim);
+                const float *v0 = v + row_base(FLAT_LAYOUT_PROJECTION, batch, kv_head, 0, s.kv_heads, s.kv_len, s.head_dim);
+                float *out_row = out + row_base(FLAT_LAYOUT_PROJECTION, batch, q_head, query_pos, s.q_heads, s.query_len, s.head_dim);
+                float *lse_out = lse + (batch * s.q_heads + q_head) * s.query_len + query_pos;
+                attend_row(q_row, k0, v0, kv_stride, key_count, s.head_dim, scale, rope, out_row, lse_out,
+                           bias_mode ? &rb : nullptr);
+            }
+    return FLAT_OK;
 }
 
 // AsymmetricGroupedAttentionShape::forward_reference_variable_lengths
