@@ -290,6 +290,15 @@ class Context:
     def forward_projection_rope_asymmetric(self, dtype, shp, cfg, rot, q, k, v, out):
         self._fwd("flat_forward_projection_rope_asymmetric", dtype, shp, cfg, rot, q, k, v, out)
 
+    def forward_projection_rope_asymmetric_alibi(self, dtype, shp, cfg, rot, slopes, bias_query_offset,
+                                                 bias_kv_offset, q, k, v, out):
+        """encode_alibi / encode_pre_rotated_k_alibi (src/wgpu_external_asymmetric.rs:245-282); `slopes` is a
+        host sequence of one f32 per query head, rot.rotate_k selects raw or pre-rotated K."""
+        arr = (C.c_float * max(len(slopes), 1))(*[float(x) for x in slopes])
+        self.check(lib().flat_forward_projection_rope_asymmetric_alibi(
+            self.h, C.c_int32(dtype), C.byref(shp), C.byref(cfg), C.byref(rot), arr, C.c_uint64(len(slopes)),
+            C.c_uint64(bias_query_offset), C.c_uint64(bias_kv_offset), buf(q), buf(k), buf(v), buf(out)))
+
     def forward_projection_rope_varlen(self, dtype, shp, cfg, rot, sequences: Sequence[VarlenSequence], q, k, v, out):
         arr = (VarlenSequence * max(len(sequences), 1))(*sequences)
         self.check(lib().flat_forward_projection_rope_varlen(self.h, C.c_int32(dtype), C.byref(shp), C.byref(cfg),

@@ -128,6 +128,8 @@ struct ForwardCall {
     const flat_varlen_sequence *varlen_host;
     uint64_t varlen_count;
     bool varlen;
+    const float *alibi_slopes = nullptr;  // host, [alibi_count]; null = no bias
+    uint64_t alibi_count = 0, alibi_q_off = 0, alibi_kv_off = 0;
 };
 
 int launch_forward(flat_ctx *ctx, int dtype, const FwdParams &p) {
@@ -179,6 +181,24 @@ int forward_common(flat_ctx *ctx, const ForwardCall &call, const flat_attention_
                 (uint64_t)m.query_rope_offset + m.active_query_len - 1 > lim)
                 return fail(ctx, FLAT_ERR_POSITION_OVERFLOW, "sequence %llu position overflows u32", (unsigned long long)b);
         }
+    }
+    if (call.alibi_slopes) {
+        // validate_alibi (src/wgpu_external_asymmetric.rs:512-545)
+        if (call.alibi_count != shape->q_heads)
+            return fail(ctx, FLAT_ERR_LENGTH_MISMATCH, "tensor ALiBi slopes contains %llu elements, expected %llu",
+                        (unsigned long long)call.alibi_count, (unsigned long long)shape->q_heads);
+        for (uint64_t i = 0; i < call.alibi_count; ++i)
+            if (!std::isfinite(call.alibi_slopes[i]))
+                return fail(ctx, FLAT_ERR_NON_FINITE_INPUT, "tensor ALiBi slopes contains a non-finite value at index %llu",
+                            (unsigned long long)i);
+        if (shape->q_heads > FLAT_ALIBI_MAX_HEADS)
+            return fail(ctx, FLAT_ERR_INDEX_SPACE_EXCEEDED, "ALiBi supports at most %d query heads, got %llu",
+                        FLAT_ALIBI_MAX_HEADS, (unsigned long long)shape->q_heads);
+        const uint64_t lim = std::numeric_limits<uint32_t>::max();
+        uint64_t q_final, kv_final;
+        if (__builtin_add_overflow(call.alibi_q_off, shape->query_len - 1, &q_final) ||
+            __builtin_add_overflow(call.alibi_kv_off, shape->kv_len - 1, &kv_final) || q_final > lim || kv_final > lim)
+            return fail(ctx, FLAT_ERR_POSITION_OVERFLOW, "ALiBi position offset overflows u32");
     }
     const uint64_t es = dtype_size(call.dtype);
     const uint64_t lse_off = lse_offset_bytes(call.dtype, d.q_elements);
@@ -236,6 +256,18 @@ int forward_common(flat_ctx *ctx, const ForwardCall &call, const flat_attention_
         if ((st = ensure_workspace(ctx, kWorkspaceMeta + (tensor_path ? forward_sm100_workspace_bytes(p) : 0)))) return st;
         FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ctx->workspace, call.varlen_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
         p.varlen = static_cast<const flat_varlen_sequence *>(ctx->workspace);
+        return tensor_path ? launch_forward_sm100(ctx, p) : launch_forward_simt(ctx, call.dtype, p);
+    }
+    if (call.alibi_slopes) {
+        // the slopes take the start of the workspace; size it for the kernel first, a later growth would move them
+        p.alibi_slopes = call.alibi_slopes;  // non-null for the capability test
+        p.alibi_q_off = (int64_t)call.alibi_q_off;
+        p.alibi_kv_off = (int64_t)call.alibi_kv_off;
+        const bool tensor_path = call.dtype == FLAT_BF16 && forward_sm100_supported(p);
+        if ((st = ensure_workspace(ctx, kWorkspaceMeta + (tensor_path ? forward_sm100_workspace_bytes(p) : 0)))) return st;
+        FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ctx->workspace, call.alibi_slopes, call.alibi_count * sizeof(float),
+                                          cudaMemcpyHostToDevice, ctx->stream));
+        p.alibi_slopes = static_cast<const float *>(ctx->workspace);
         return tensor_path ? launch_forward_sm100(ctx, p) : launch_forward_simt(ctx, call.dtype, p);
     }
     if (params_out) {
@@ -701,6 +733,22 @@ int32_t flat_forward_projection_rope_asymmetric(flat_ctx *ctx, int32_t dtype, co
                                                 const flat_rotary_config *rotary, flat_buffer q, flat_buffer k,
                                                 flat_buffer v, flat_buffer out_and_lse) {
     ForwardCall c{dtype, FLAT_LAYOUT_PROJECTION, true, rotary, nullptr, 0, false};
+    return forward_common(ctx, c, shape, config, q, k, v, out_and_lse);
+}
+
+int32_t flat_forward_projection_rope_asymmetric_alibi(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
+                                                      const flat_attention_config *config,
+                                                      const flat_rotary_config *rotary, const float *slopes,
+                                                      uint64_t slope_count, uint64_t bias_query_offset,
+                                                      uint64_t bias_kv_offset, flat_buffer q, flat_buffer k,
+                                                      flat_buffer v, flat_buffer out_and_lse) {
+    if (!ctx) return FLAT_ERR_NULL_POINTER;
+    if (!slopes) return fail(ctx, FLAT_ERR_NULL_POINTER, "ALiBi slopes is null");
+    ForwardCall c{dtype, FLAT_LAYOUT_PROJECTION, true, rotary, nullptr, 0, false};
+    c.alibi_slopes = slopes;
+    c.alibi_count = slope_count;
+    c.alibi_q_off = bias_query_offset;
+    c.alibi_kv_off = bias_kv_offset;
     return forward_common(ctx, c, shape, config, q, k, v, out_and_lse);
 }
 

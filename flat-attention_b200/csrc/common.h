@@ -127,6 +127,9 @@ struct FwdParams {
     int page_size, max_pages;
     int64_t page_row_stride;             // elements per physical row (kv_heads*head_dim)
     float inv_freq[kMaxHeadDim / 2];     // theta^(-2j/D), host-computed in f32
+    // ALiBi (src/attention_bias.rs:82-95): score += slopes[q_head] * ((kv_off + key) - (q_off + query row))
+    const float *alibi_slopes;           // device, [q_heads] or null
+    int64_t alibi_q_off, alibi_kv_off;
 };
 
 // Generic SIMT forward (f32 arithmetic; T = float or __nv_bfloat16 storage).

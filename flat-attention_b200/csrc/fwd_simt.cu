@@ -106,6 +106,10 @@ __global__ void __launch_bounds__(kThreads) fwd_simt_kernel(const __grid_constan
 
     float m = -INFINITY, l = 0.f;
     const T *kbase = (const T *)p.k, *vbase = (const T *)p.v;
+    // ALiBi: the position difference is formed in integers and rounded to f32 once, like the f64 difference of
+    // src/attention_bias.rs:93-94
+    const float slope = p.alibi_slopes ? p.alibi_slopes[q_head] : 0.f;
+    const int64_t bias_delta0 = p.alibi_kv_off - p.alibi_q_off - row;
 
     for (int64_t k0 = 0; k0 < cta_limit; k0 += kKeys) {
         __syncthreads();
@@ -148,7 +152,9 @@ __global__ void __launch_bounds__(kThreads) fwd_simt_kernel(const __grid_constan
             }
             acc += __shfl_xor_sync(0xffffffffu, acc, 1);
             acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-            float sc = (valid && (k0 + j) < limit) ? acc * p.scale : -INFINITY;
+            float sc = acc * p.scale;
+            if (p.alibi_slopes) sc = __fadd_rn(sc, __fmul_rn(slope, (float)(bias_delta0 + k0 + j)));
+            if (!(valid && (k0 + j) < limit)) sc = -INFINITY;
             s[j] = sc;
             tile_max = fmaxf(tile_max, sc);
         }

@@ -102,6 +102,8 @@ struct KernelParams {
     long long rope_table_base;           // varlen: position of the table's first row (the smallest query_rope_offset)
     const float2 *rope_q_table;  // (cos, sin) of row r, pair j at [r * D/2 + j]; null = Q is used as loaded
     float2 rope_step[kMaxHeadDim / 2];  // (cos, sin)(rows_per_step * inv_freq[j]): advances a row's rotation
+    const float *alibi_slopes;  // ALIBI kernels: one slope per query head (device)
+    int alibi_delta;            // ALIBI kernels: bias position of key 0 minus bias position of query row 0
     long long *trace;
 };
 
@@ -173,7 +175,9 @@ __device__ __forceinline__ int item_index(const KernelParams &p, int k) {
     return idx < p.total_items ? (int)idx : -1;
 }
 
-template <int D, bool CONVK>
+// ALIBI: the softmax warps add slope[q_head] * (key position - query position) to every scaled score
+// (src/attention_bias.rs:82-95) before the running maximum is taken.
+template <int D, bool CONVK, bool ALIBI>
 __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_constant__ KernelParams p) {
     using C = Cfg<D, CONVK>;
     extern __shared__ uint8_t smem_raw[];
@@ -476,6 +480,13 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     lim = (int)min((long long)lim, it.causal_off + first + row_in_tile);
                     lim_first = (int)min((long long)lim_first, it.causal_off + first);
                 }
+                // ALiBi in the log2 domain.  Positions stay below 2^24 in magnitude (checked on the host), so the
+                // float position arithmetic below is exact and each bias is rounded once, inside the FMA.
+                float slope_l2 = 0.f, bias_pos0 = 0.f;
+                if constexpr (ALIBI) {
+                    slope_l2 = __ldg(p.alibi_slopes + it.h) * kLog2e;
+                    bias_pos0 = (float)(p.alibi_delta - (it.r0 + w * kTileRows + row_in_tile));
+                }
 
                 // Online softmax, log2 domain, one thread per row; the whole 128-column score row sits in
                 // registers.  O in TMEM is rescaled only when the running max grew by more than 2^8.
@@ -495,12 +506,30 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     const int key0 = j * kTileRows;
                     const bool tile_masked = key0 + kTileRows - 1 > lim_first;  // uniform over the Q tile
                     const int vis = min(kTileRows, lim - key0 + 1);             // visible columns of this row
-                    const float c_log2 = p.scale_log2;
+                    const float c_log2 = ALIBI ? 1.0f : p.scale_log2;
                     uint32_t r[128];  // four loads in flight, one wait
 #pragma unroll
                     for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, r + c * 32);
                     tc_wait_ld();
                     if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(1);
+                    if constexpr (ALIBI) {
+                        // r[i] <- s_i * c + slope * (position difference of column i); the passes below then use c = 1
+                        uint64_t pos2, two2, sl2, cc2;
+                        const float x0 = bias_pos0 + (float)key0;
+                        asm("mov.b64 %0, {%1, %2};" : "=l"(pos2) : "f"(x0), "f"(x0 + 1.0f));
+                        asm("mov.b64 %0, {%1, %1};" : "=l"(two2) : "f"(2.0f));
+                        asm("mov.b64 %0, {%1, %1};" : "=l"(sl2) : "f"(slope_l2));
+                        asm("mov.b64 %0, {%1, %1};" : "=l"(cc2) : "f"(p.scale_log2));
+#pragma unroll
+                        for (int i = 0; i < 128; i += 2) {
+                            uint64_t s2, b2;
+                            asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(r[i]), "r"(r[i + 1]));
+                            asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(b2) : "l"(s2), "l"(cc2));
+                            asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(s2) : "l"(pos2), "l"(sl2), "l"(b2));
+                            asm("mov.b64 {%0, %1}, %2;" : "=r"(r[i]), "=r"(r[i + 1]) : "l"(s2));
+                            asm("add.rn.f32x2 %0, %0, %1;" : "+l"(pos2) : "l"(two2));
+                        }
+                    }
                     if (tile_masked) {
 #pragma unroll
                         for (int i = 0; i < 128; ++i)
@@ -822,6 +851,12 @@ bool forward_sm100_supported(const FwdParams &p) {
         if (!(ps == 8 || ps == 16 || ps == 32 || ps == 64 || ps == 128)) return false;
     }
     if (p.rope_k && !p.rope_q) return false;
+    if (p.alibi_slopes) {
+        // the kernel forms bias positions in f32: they must stay exact
+        if (p.varlen || p.page_table) return false;
+        const int64_t delta = p.alibi_kv_off - p.alibi_q_off;
+        if ((delta < 0 ? -delta : delta) + std::max(p.q_len, p.kv_len) >= (1 << 24)) return false;
+    }
     return true;
 }
 
@@ -933,10 +968,17 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
         kernel<<<grid, kThreads, smem_bytes, ctx->stream>>>(kp);
         return FLAT_OK;
     };
-    if (D == 128) st = convk ? run(fwd_sm100_kernel<128, true>, Cfg<128, true>::kSmemBytes)
-                             : run(fwd_sm100_kernel<128, false>, Cfg<128, false>::kSmemBytes);
-    else st = convk ? run(fwd_sm100_kernel<64, true>, Cfg<64, true>::kSmemBytes)
-                    : run(fwd_sm100_kernel<64, false>, Cfg<64, false>::kSmemBytes);
+    kp.alibi_slopes = p.alibi_slopes;
+    kp.alibi_delta = (int)(p.alibi_kv_off - p.alibi_q_off);
+    if (p.alibi_slopes) {
+        if (D == 128) st = convk ? run(fwd_sm100_kernel<128, true, true>, Cfg<128, true>::kSmemBytes)
+                                 : run(fwd_sm100_kernel<128, false, true>, Cfg<128, false>::kSmemBytes);
+        else st = convk ? run(fwd_sm100_kernel<64, true, true>, Cfg<64, true>::kSmemBytes)
+                        : run(fwd_sm100_kernel<64, false, true>, Cfg<64, false>::kSmemBytes);
+    } else if (D == 128) st = convk ? run(fwd_sm100_kernel<128, true, false>, Cfg<128, true>::kSmemBytes)
+                                    : run(fwd_sm100_kernel<128, false, false>, Cfg<128, false>::kSmemBytes);
+    else st = convk ? run(fwd_sm100_kernel<64, true, false>, Cfg<64, true>::kSmemBytes)
+                    : run(fwd_sm100_kernel<64, false, false>, Cfg<64, false>::kSmemBytes);
     if (st) return st;
     ctx->launches += 1;
     FLAT_CUDA_OK(ctx, cudaGetLastError());

@@ -153,8 +153,28 @@ class CudaExternalAsymmetricProjectionRotaryGroupedPipeline {
     CudaExternalAsymmetricProjectionRotaryGroupedPipeline(const Context &ctx, DType dtype) : ctx_(ctx), dtype_(dtype) {}
     flat_forward_layout encode(const ForwardPass &pass) const { return run(pass, true); }
     flat_forward_layout encode_pre_rotated_k(const ForwardPass &pass) const { return run(pass, false); }
+    // encode_alibi / encode_pre_rotated_k_alibi (src/wgpu_external_asymmetric.rs:245-282)
+    flat_forward_layout encode_alibi(const ForwardPass &pass, const std::vector<float> &slopes, uint64_t query_position_offset,
+                                     uint64_t kv_position_offset) const {
+        return run_alibi(pass, true, slopes, query_position_offset, kv_position_offset);
+    }
+    flat_forward_layout encode_pre_rotated_k_alibi(const ForwardPass &pass, const std::vector<float> &slopes,
+                                                   uint64_t query_position_offset, uint64_t kv_position_offset) const {
+        return run_alibi(pass, false, slopes, query_position_offset, kv_position_offset);
+    }
 
   private:
+    flat_forward_layout run_alibi(const ForwardPass &pass, bool rotate_k, const std::vector<float> &slopes, uint64_t q_off,
+                                  uint64_t kv_off) const {
+        auto cfg = pass.config.raw();
+        auto rot = pass.rotary.raw();
+        rot.rotate_k = rotate_k ? 1 : 0;
+        static const float none = 0.f;  // an empty vector still reaches the length check, not the null check
+        ctx_.check(flat_forward_projection_rope_asymmetric_alibi(ctx_.raw(), static_cast<int32_t>(dtype_), &pass.shape, &cfg,
+                                                                 &rot, slopes.empty() ? &none : slopes.data(), slopes.size(),
+                                                                 q_off, kv_off, pass.q, pass.k, pass.v, pass.out_and_lse));
+        return forward_layout(dtype_, pass.shape);
+    }
     flat_forward_layout run(const ForwardPass &pass, bool rotate_k) const {
         auto cfg = pass.config.raw();
         auto rot = pass.rotary.raw();

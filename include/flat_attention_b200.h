@@ -256,6 +256,27 @@ int32_t flat_forward_projection_rope_asymmetric(flat_ctx *ctx, int32_t dtype,
                                                 flat_buffer k, flat_buffer v,
                                                 flat_buffer out_and_lse);
 
+/* ExternalAsymmetricProjectionRotaryGroupedPipeline::encode_alibi / encode_pre_rotated_k_alibi
+ * (src/wgpu_external_asymmetric.rs:245-282; rotary->rotate_k selects which): the rectangular
+ * projection-layout forward with an additive ALiBi score bias,
+ *   score = dot * scale + slopes[q_head] * ((bias_kv_offset + key) - (bias_query_offset + query)),
+ * added before the online-softmax update (src/attention_bias.rs:82-95, 284-285).
+ * `slopes` is a HOST array of slope_count f32 values, one per query head (validated, then copied
+ * to the device).  Errors follow validate_alibi (src/wgpu_external_asymmetric.rs:512-545):
+ * LENGTH_MISMATCH "ALiBi slopes", NON_FINITE_INPUT with the first bad index,
+ * INDEX_SPACE_EXCEEDED above FLAT_ALIBI_MAX_HEADS query heads, POSITION_OVERFLOW when the last
+ * query or key position leaves u32. */
+#define FLAT_ALIBI_MAX_HEADS 256
+int32_t flat_forward_projection_rope_asymmetric_alibi(flat_ctx *ctx, int32_t dtype,
+                                                      const flat_attention_shape *shape,
+                                                      const flat_attention_config *config,
+                                                      const flat_rotary_config *rotary,
+                                                      const float *slopes, uint64_t slope_count,
+                                                      uint64_t bias_query_offset,
+                                                      uint64_t bias_kv_offset, flat_buffer q,
+                                                      flat_buffer k, flat_buffer v,
+                                                      flat_buffer out_and_lse);
+
 /* ExternalVariableProjectionRotaryGroupedPipeline::encode
  * (src/wgpu_external_variable.rs:190-223): padded variable-length batch; `sequences` is a
  * HOST array of shape->batch entries (validated, then copied to the device); padded query
