@@ -263,6 +263,8 @@ int forward_common(flat_ctx *ctx, const ForwardCall &call, const flat_attention_
         p.alibi_slopes = call.alibi_slopes;  // non-null for the capability test
         p.alibi_q_off = (int64_t)call.alibi_q_off;
         p.alibi_kv_off = (int64_t)call.alibi_kv_off;
+        for (uint64_t i = 0; i < call.alibi_count; ++i)
+            p.alibi_max_abs_slope = std::max(p.alibi_max_abs_slope, std::fabs(call.alibi_slopes[i]));
         const bool tensor_path = call.dtype == FLAT_BF16 && forward_sm100_supported(p);
         if ((st = ensure_workspace(ctx, kWorkspaceMeta + (tensor_path ? forward_sm100_workspace_bytes(p) : 0)))) return st;
         FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ctx->workspace, call.alibi_slopes, call.alibi_count * sizeof(float),

@@ -130,6 +130,7 @@ struct FwdParams {
     // ALiBi (src/attention_bias.rs:82-95): score += slopes[q_head] * ((kv_off + key) - (q_off + query row))
     const float *alibi_slopes;           // device, [q_heads] or null
     int64_t alibi_q_off, alibi_kv_off;
+    float alibi_max_abs_slope;           // host-side copy of max |slope|
 };
 
 // Generic SIMT forward (f32 arithmetic; T = float or __nv_bfloat16 storage).

@@ -104,6 +104,7 @@ struct KernelParams {
     float2 rope_step[kMaxHeadDim / 2];  // (cos, sin)(rows_per_step * inv_freq[j]): advances a row's rotation
     const float *alibi_slopes;  // ALIBI kernels: one slope per query head (device)
     int alibi_delta;            // ALIBI kernels: bias position of key 0 minus bias position of query row 0
+    float alibi_inv_scale;      // ALIBI kernels: 1 / softmax scale
     long long *trace;
 };
 
@@ -480,11 +481,12 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     lim = (int)min((long long)lim, it.causal_off + first + row_in_tile);
                     lim_first = (int)min((long long)lim_first, it.causal_off + first);
                 }
-                // ALiBi in the log2 domain.  Positions stay below 2^24 in magnitude (checked on the host), so the
-                // float position arithmetic below is exact and each bias is rounded once, inside the FMA.
-                float slope_l2 = 0.f, bias_pos0 = 0.f;
+                // ALiBi is added to the raw score as (slope / scale) * position difference, so that the scaling of the
+                // softmax passes covers it.  Positions stay below 2^24 in magnitude (checked on the host): the float
+                // position arithmetic is exact and each bias is rounded once, inside the FMA.
+                float slope_rel = 0.f, bias_pos0 = 0.f;
                 if constexpr (ALIBI) {
-                    slope_l2 = __ldg(p.alibi_slopes + it.h) * kLog2e;
+                    slope_rel = __ldg(p.alibi_slopes + it.h) * p.alibi_inv_scale;
                     bias_pos0 = (float)(p.alibi_delta - (it.r0 + w * kTileRows + row_in_tile));
                 }
 
@@ -506,26 +508,24 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     const int key0 = j * kTileRows;
                     const bool tile_masked = key0 + kTileRows - 1 > lim_first;  // uniform over the Q tile
                     const int vis = min(kTileRows, lim - key0 + 1);             // visible columns of this row
-                    const float c_log2 = ALIBI ? 1.0f : p.scale_log2;
+                    const float c_log2 = p.scale_log2;
                     uint32_t r[128];  // four loads in flight, one wait
 #pragma unroll
                     for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, r + c * 32);
                     tc_wait_ld();
                     if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(1);
                     if constexpr (ALIBI) {
-                        // r[i] <- s_i * c + slope * (position difference of column i); the passes below then use c = 1
-                        uint64_t pos2, two2, sl2, cc2;
+                        // r[i] <- s_i + (slope / c) * (position difference of column i): the passes below scale by c
+                        uint64_t pos2, two2, sl2;
                         const float x0 = bias_pos0 + (float)key0;
                         asm("mov.b64 %0, {%1, %2};" : "=l"(pos2) : "f"(x0), "f"(x0 + 1.0f));
                         asm("mov.b64 %0, {%1, %1};" : "=l"(two2) : "f"(2.0f));
-                        asm("mov.b64 %0, {%1, %1};" : "=l"(sl2) : "f"(slope_l2));
-                        asm("mov.b64 %0, {%1, %1};" : "=l"(cc2) : "f"(p.scale_log2));
+                        asm("mov.b64 %0, {%1, %1};" : "=l"(sl2) : "f"(slope_rel));
 #pragma unroll
                         for (int i = 0; i < 128; i += 2) {
-                            uint64_t s2, b2;
+                            uint64_t s2;
                             asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(r[i]), "r"(r[i + 1]));
-                            asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(b2) : "l"(s2), "l"(cc2));
-                            asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(s2) : "l"(pos2), "l"(sl2), "l"(b2));
+                            asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(s2) : "l"(pos2), "l"(sl2));
                             asm("mov.b64 {%0, %1}, %2;" : "=r"(r[i]), "=r"(r[i + 1]) : "l"(s2));
                             asm("add.rn.f32x2 %0, %0, %1;" : "+l"(pos2) : "l"(two2));
                         }
@@ -856,6 +856,8 @@ bool forward_sm100_supported(const FwdParams &p) {
         if (p.varlen || p.page_table) return false;
         const int64_t delta = p.alibi_kv_off - p.alibi_q_off;
         if ((delta < 0 ? -delta : delta) + std::max(p.q_len, p.kv_len) >= (1 << 24)) return false;
+        // the bias enters as slope / scale: keep that quotient far from overflow
+        if (!(p.alibi_max_abs_slope / p.scale < 1.0e30f)) return false;
     }
     return true;
 }
@@ -970,6 +972,7 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     };
     kp.alibi_slopes = p.alibi_slopes;
     kp.alibi_delta = (int)(p.alibi_kv_off - p.alibi_q_off);
+    kp.alibi_inv_scale = 1.0f / p.scale;
     if (p.alibi_slopes) {
         if (D == 128) st = convk ? run(fwd_sm100_kernel<128, true, true>, Cfg<128, true>::kSmemBytes)
                                  : run(fwd_sm100_kernel<128, false, true>, Cfg<128, false>::kSmemBytes);
