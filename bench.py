@@ -213,6 +213,48 @@ def timed_region(torch, dist, world, fn, steps):
     return ms
 
 
+def write_manifest(torch, fa, ctx, args, c, step):
+    """Benchmark manifest (BenchmarkManifest, src/benchmark_manifest.rs:46-199) of the headline workload: per-step device
+    latencies of up to 101 further steps, median and p95 in integer nanoseconds, canonical JSON from the library."""
+    import importlib
+    import platform
+    import subprocess
+    tel = importlib.import_module("flat_attention_b200.telemetry")
+    n = max(1, min(args.steps, 101))
+    events = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+    torch.cuda.synchronize()
+    for i in range(n):
+        events[i].record()
+        step()
+    events[n].record()
+    torch.cuda.synchronize()
+    lat = sorted(int(round(events[i].elapsed_time(events[i + 1]) * 1e6)) for i in range(n))
+    median = lat[n // 2]
+    p95 = max(median, lat[min(n - 1, (95 * n + 99) // 100 - 1)])
+    sha = args.commit_sha
+    if not sha:
+        try:
+            sha = subprocess.run(["git", "-C", ROOT, "rev-parse", "HEAD"], capture_output=True, text=True, timeout=10).stdout.strip()
+        except Exception:
+            sha = ""
+    if len(sha) != 40:
+        sha = "0" * 40
+    fp = tel.device_fingerprint(ctx)
+    tokens = c["B"] * c["N"]
+    m = tel.BenchmarkManifest(
+        commit_sha=sha, benchmark_id="c2-gqa-rope-causal-prefill", command="python bench.py " + " ".join(sys.argv[1:]),
+        device=fp.name.decode(), backend=fp.backend.decode(), driver=fp.driver.decode() + "; " + fp.driver_info.decode(),
+        os=platform.system(), arch=platform.machine(), precision="bf16", batch=c["B"], q_heads=c["Hq"], kv_heads=c["Hkv"],
+        query_len=c["N"], kv_len=c["N"], head_dim=c["D"], causal=True, warmup_iterations=args.warmup, measured_iterations=n,
+        median_latency_ns=median, p95_latency_ns=p95, tokens_per_second_milli=tokens * 1_000_000_000_000 // max(median, 1))
+    text = m.canonical_json()
+    os.makedirs(os.path.dirname(os.path.abspath(args.manifest)), exist_ok=True)
+    with open(args.manifest, "w") as f:
+        f.write(text + "\n")
+    return {"path": args.manifest, "result_checksum": m.result_checksum(), "median_latency_ns": median, "p95_latency_ns": p95,
+            "device_fingerprint": "%016x" % tel.fingerprint_stable(fp)}
+
+
 def bench_decode(torch, np, fa, ctx, peaks, steps, warmup):
     """Config 3: batched paged decode, HBM GB/s of the algorithmic bytes."""
     c = C3
@@ -417,6 +459,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-extras", action="store_true", help="only the headline prefill workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle legs (parity gate, cpu_baseline): for profiler runs")
+    ap.add_argument("--manifest", default=None, help="write a schema-1 canonical-JSON benchmark manifest of the headline "
+                                                     "workload to this path (rank 0)")
+    ap.add_argument("--commit-sha", default=None, help="40-hex source revision recorded in the manifest "
+                                                       "(default: git rev-parse HEAD, else zeros)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -531,6 +577,8 @@ def main():
         "parity": parity,
         "device_status": status,
     }
+    if rank == 0 and args.manifest:
+        line["manifest"] = write_manifest(torch, fa, ctx, args, c, step)
     if rank == 0 and world == 1 and not args.no_cpu:
         from oracle import binding as ob
         rows = sample_rows(np, 40000, 11)

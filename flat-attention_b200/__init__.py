@@ -33,6 +33,8 @@ STATUS = {
     30: "EmptyCache", 31: "InvalidCacheLength", 32: "InvalidQueryLen", 33: "CausalVisibilityMismatch",
     34: "EmptyTable", 35: "PageOutOfRange", 36: "PageShared", 37: "InvalidTheta", 40: "CapacityOverflow",
     41: "CapacityExceeded", 42: "GenerationOverflow", 50: "ZeroQueryChunkSize", 60: "DeviceWaitTimeout",
+    70: "ManifestInvalidCommitSha", 71: "ManifestEmptyField", 72: "ManifestZeroMeasuredIterations",
+    73: "ManifestInvalidPercentileOrdering",
 }
 
 

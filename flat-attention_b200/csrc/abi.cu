@@ -524,6 +524,31 @@ int32_t flat_ctx_create(int32_t device, void *stream, flat_ctx **out) {
     ctx->sm_count = prop.multiProcessorCount;
     ctx->cc_major = prop.major;
     ctx->cc_minor = prop.minor;
+    {
+        // RuntimeDeviceFingerprint / RuntimeDeviceCapabilities, captured once (src/wgpu_backend.rs:239-316)
+        int driver = 0, runtime = 0;
+        cudaDriverGetVersion(&driver);
+        cudaRuntimeGetVersion(&runtime);
+        flat_device_fingerprint &fp = ctx->fingerprint;
+        std::snprintf(fp.name, sizeof fp.name, "%s", prop.name);
+        std::snprintf(fp.backend, sizeof fp.backend, "Cuda");
+        std::snprintf(fp.driver, sizeof fp.driver, "cuda-driver-api %d.%d", driver / 1000, (driver % 1000) / 10);
+        std::snprintf(fp.driver_info, sizeof fp.driver_info, "cuda-runtime %d.%d sm_%d%d %d SMs", runtime / 1000,
+                      (runtime % 1000) / 10, prop.major, prop.minor, prop.multiProcessorCount);
+        fp.vendor = 0x10de;
+        fp.device = (uint32_t)(prop.major * 10 + prop.minor);
+        flat_device_capabilities &c = ctx->capabilities;
+        c.max_workgroups_per_dimension = (uint32_t)prop.maxGridSize[0];
+        c.max_workgroup_size_x = (uint32_t)prop.maxThreadsDim[0];
+        c.max_workgroup_size_y = (uint32_t)prop.maxThreadsDim[1];
+        c.max_workgroup_size_z = (uint32_t)prop.maxThreadsDim[2];
+        c.max_workgroup_storage_bytes = (uint32_t)prop.sharedMemPerBlockOptin;
+        c.max_binding_entries = 0;
+        c.max_storage_buffer_binding_size = (uint32_t)std::min<uint64_t>(prop.totalGlobalMem, 0xffffffffull);
+        c.subgroup_supported = 1;
+        c.subgroup_min_size = c.subgroup_max_size = (uint32_t)prop.warpSize;
+        c.f16_supported = 1;
+    }
     if (cudaMalloc(&ctx->dev_status, sizeof(DeviceStatus)) != cudaSuccess ||
         cudaMemset(ctx->dev_status, 0, sizeof(DeviceStatus)) != cudaSuccess) {
         delete ctx;
@@ -599,6 +624,10 @@ const char *flat_status_str(int32_t status) {
         case FLAT_ERR_GENERATION_OVERFLOW: return "paged KV generation counter overflowed";
         case FLAT_ERR_ZERO_QUERY_CHUNK_SIZE: return "chunked prefill requires a non-zero query chunk size";
         case FLAT_ERR_DEVICE_WAIT_TIMEOUT: return "a bounded device-side wait expired";
+        case FLAT_ERR_MANIFEST_INVALID_COMMIT_SHA: return "commit_sha must contain exactly 40 hex digits";
+        case FLAT_ERR_MANIFEST_EMPTY_FIELD: return "benchmark manifest field must not be empty";
+        case FLAT_ERR_MANIFEST_ZERO_MEASURED_ITERATIONS: return "measured_iterations must be non-zero";
+        case FLAT_ERR_MANIFEST_INVALID_PERCENTILE_ORDERING: return "p95 latency must be greater than or equal to median latency";
     }
     return "unknown status";
 }
@@ -736,6 +765,47 @@ int32_t flat_forward_projection_rope_asymmetric(flat_ctx *ctx, int32_t dtype, co
                                                 flat_buffer v, flat_buffer out_and_lse) {
     ForwardCall c{dtype, FLAT_LAYOUT_PROJECTION, true, rotary, nullptr, 0, false};
     return forward_common(ctx, c, shape, config, q, k, v, out_and_lse);
+}
+
+int32_t flat_forward_runtime_telemetry(flat_ctx *ctx, int32_t dtype, int32_t layout, const flat_attention_shape *shape,
+                                       const flat_rotary_config *rotary, flat_dispatch_telemetry *out) {
+    if (!ctx) return FLAT_ERR_NULL_POINTER;
+    if (!out) return fail(ctx, FLAT_ERR_NULL_POINTER, "telemetry output is null");
+    if (layout != FLAT_LAYOUT_HEAD_MAJOR && layout != FLAT_LAYOUT_PROJECTION)
+        return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE, "unknown layout %d", layout);
+    // the parameter block of the call, built with stand-in buffers (any 256-byte aligned address of sufficient size)
+    ForwardCall c{dtype, layout, rotary != nullptr, rotary, nullptr, 0, false};
+    const flat_buffer stand_in{reinterpret_cast<void *>(uintptr_t(1) << 20), ~uint64_t(0)};
+    const flat_attention_config cfg{1, 0, 0.f};
+    FwdParams p{};
+    int st = forward_common(ctx, c, shape, &cfg, stand_in, stand_in, stand_in, stand_in, &p);
+    if (st) return st;
+    std::memset(out, 0, sizeof *out);
+    out->device = ctx->fingerprint;
+    out->autotuner_cache = FLAT_AUTOTUNER_NOT_APPLICABLE;
+    if (dtype == FLAT_BF16 && forward_sm100_supported(p)) {
+        out->kernel_id = FLAT_KERNEL_FORWARD_TCGEN05;
+        forward_sm100_geometry(ctx, p, &out->query_rows, &out->kv_rows, out->workgroups, &out->dispatch_count);
+        out->temporary_allocation_bytes = forward_sm100_workspace_bytes(p);
+        out->temporary_allocation_count = out->temporary_allocation_bytes ? 1 : 0;
+        return FLAT_OK;
+    }
+    out->kernel_id = FLAT_KERNEL_FORWARD_GENERIC;
+    forward_simt_geometry(p, &out->query_rows, &out->kv_rows, out->workgroups);
+    out->dispatch_count = 1;
+    out->has_fallback_reason = 1;
+    if (dtype != FLAT_BF16)
+        std::snprintf(out->fallback_reason, sizeof out->fallback_reason, "tensor-core specialization requires bf16 storage");
+    else if (p.head_dim != 64 && p.head_dim != 128)
+        std::snprintf(out->fallback_reason, sizeof out->fallback_reason,
+                      "tensor-core specialization unavailable for head_dim=%d", p.head_dim);
+    else if (p.q_len < 32 || p.kv_len < 32)
+        std::snprintf(out->fallback_reason, sizeof out->fallback_reason,
+                      "tensor-core specialization unavailable for query_len=%d kv_len=%d", p.q_len, p.kv_len);
+    else
+        std::snprintf(out->fallback_reason, sizeof out->fallback_reason,
+                      "tensor-core specialization unavailable for this layout or position range");
+    return FLAT_OK;
 }
 
 int32_t flat_forward_projection_rope_asymmetric_alibi(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,

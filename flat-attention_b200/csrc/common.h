@@ -31,6 +31,8 @@ struct flat_ctx {
     cudaStream_t stream = nullptr;
     int sm_count = 0;
     int cc_major = 0, cc_minor = 0;
+    flat_device_fingerprint fingerprint{};    // captured once at creation, like the reference's owned context
+    flat_device_capabilities capabilities{};
     void *workspace = nullptr;
     uint64_t workspace_bytes = 0;
     flat::DeviceStatus *dev_status = nullptr;  // device memory
@@ -135,6 +137,10 @@ struct FwdParams {
 
 // Generic SIMT forward (f32 arithmetic; T = float or __nv_bfloat16 storage).
 int launch_forward_simt(flat_ctx *ctx, int dtype, const FwdParams &p);
+// tile geometry and grid of the two forward kernels for a parameter block (telemetry; nothing is launched)
+void forward_simt_geometry(const FwdParams &p, uint32_t *query_rows, uint32_t *kv_rows, uint32_t grid[3]);
+void forward_sm100_geometry(const flat_ctx *ctx, const FwdParams &p, uint32_t *query_rows, uint32_t *kv_rows, uint32_t grid[3],
+                            uint32_t *dispatches);
 // tcgen05 forward for bf16, head_dim 64/128; returns FLAT_ERR_UNSUPPORTED_SHAPE when the shape
 // does not fit it (the caller then uses the SIMT kernel).
 bool forward_sm100_supported(const FwdParams &p);

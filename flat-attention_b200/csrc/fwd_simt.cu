@@ -227,6 +227,14 @@ int dispatch(flat_ctx *ctx, const FwdParams &p) {
 
 }  // namespace
 
+void forward_simt_geometry(const FwdParams &p, uint32_t *query_rows, uint32_t *kv_rows, uint32_t grid[3]) {
+    *query_rows = kRows;
+    *kv_rows = kKeys;
+    grid[0] = (uint32_t)((p.q_len + kRows - 1) / kRows);
+    grid[1] = (uint32_t)p.q_heads;
+    grid[2] = (uint32_t)p.batch;
+}
+
 int launch_forward_simt(flat_ctx *ctx, int dtype, const FwdParams &p) {
     if (p.q_heads > 65535 || p.batch > 65535)
         return fail(ctx, FLAT_ERR_DISPATCH_LIMIT, "grid dimension %d exceeds 65535", p.q_heads > 65535 ? p.q_heads : p.batch);

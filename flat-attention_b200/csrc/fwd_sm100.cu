@@ -869,6 +869,17 @@ uint64_t forward_sm100_workspace_bytes(const FwdParams &p) {
     return bytes;
 }
 
+void forward_sm100_geometry(const flat_ctx *ctx, const FwdParams &p, uint32_t *query_rows, uint32_t *kv_rows, uint32_t grid[3],
+                            uint32_t *dispatches) {
+    *query_rows = 2 * kTileRows;  // one work item: two 128-row Q tiles of one (batch, q_head)
+    *kv_rows = kTileRows;
+    const long long items = (long long)((p.q_len + 2 * kTileRows - 1) / (2 * kTileRows)) * p.batch * p.q_heads;
+    grid[0] = (uint32_t)std::min<long long>(items, ctx->sm_count);  // persistent: one CTA per SM
+    grid[1] = grid[2] = 1;
+    // the attention kernel, the K rotation pass when K arrives raw, and the two fills of a padded variable-length batch
+    *dispatches = 1 + (p.rope_k ? 1 : 0) + (p.varlen ? 1 : 0);
+}
+
 int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     int st = ensure_workspace(ctx, kWorkspaceMeta + forward_sm100_workspace_bytes(p));
     if (st) return st;

@@ -84,10 +84,44 @@ class Context {
     void upload(DeviceBuffer dst, const void *host, uint64_t bytes) const { check(flat_upload(ctx_, dst, host, bytes)); }
     void download(void *host, DeviceBuffer src, uint64_t bytes) const { check(flat_download(ctx_, host, src, bytes)); }
     void reserve_workspace(uint64_t bytes) const { check(flat_ctx_reserve_workspace(ctx_, bytes)); }
+    // RuntimeDeviceFingerprint / RuntimeDeviceCapabilities captured at creation (src/wgpu_backend.rs:239-316, 341-345)
+    flat_device_fingerprint device_fingerprint() const {
+        flat_device_fingerprint out{};
+        check(flat_ctx_device_fingerprint(ctx_, &out));
+        return out;
+    }
+    flat_device_capabilities device_capabilities() const {
+        flat_device_capabilities out{};
+        check(flat_ctx_device_capabilities(ctx_, &out));
+        return out;
+    }
 
   private:
     flat_ctx *ctx_ = nullptr;
 };
+
+// canonical_record / stable_fingerprint (src/runtime_telemetry.rs:49-67, 116-135)
+inline std::string canonical_record(const flat_device_fingerprint &fp) {
+    std::string out((size_t)flat_device_fingerprint_canonical_record(&fp, nullptr, 0), '\0');
+    flat_device_fingerprint_canonical_record(&fp, out.data(), out.size() + 1);
+    return out;
+}
+inline std::string canonical_record(const flat_device_capabilities &caps) {
+    std::string out((size_t)flat_device_capabilities_canonical_record(&caps, nullptr, 0), '\0');
+    flat_device_capabilities_canonical_record(&caps, out.data(), out.size() + 1);
+    return out;
+}
+inline uint64_t stable_fingerprint(const flat_device_fingerprint &fp) { return flat_device_fingerprint_stable(&fp); }
+inline uint64_t stable_fingerprint(const flat_device_capabilities &caps) { return flat_device_capabilities_stable(&caps); }
+
+// BenchmarkManifest::canonical_json (src/benchmark_manifest.rs:140-199); throws the validation error.
+inline std::string canonical_json(const flat_benchmark_manifest &m) {
+    int64_t n = flat_benchmark_manifest_canonical_json(&m, nullptr, 0);
+    if (n < 0) throw Error((int32_t)-n, "");
+    std::string out((size_t)n, '\0');
+    flat_benchmark_manifest_canonical_json(&m, out.data(), out.size() + 1);
+    return out;
+}
 
 // GroupedForwardLayout / ExternalProjectionLayout (src/wgpu_forward_grouped.rs:23-42): pure, allocation-free.
 inline flat_forward_layout forward_layout(DType dtype, const AttentionShape &shape) {

@@ -69,7 +69,13 @@ typedef enum flat_status {
     FLAT_ERR_ZERO_QUERY_CHUNK_SIZE = 50,
     /* a bounded device-side wait expired; the kernel returned early and the context is
      * still usable (outputs of that launch are undefined) */
-    FLAT_ERR_DEVICE_WAIT_TIMEOUT = 60
+    FLAT_ERR_DEVICE_WAIT_TIMEOUT = 60,
+    /* BenchmarkManifestError (src/benchmark_manifest.rs:56-63); ZeroDimension and
+     * InvalidHeadGrouping reuse the codes above */
+    FLAT_ERR_MANIFEST_INVALID_COMMIT_SHA = 70,
+    FLAT_ERR_MANIFEST_EMPTY_FIELD = 71,
+    FLAT_ERR_MANIFEST_ZERO_MEASURED_ITERATIONS = 72,
+    FLAT_ERR_MANIFEST_INVALID_PERCENTILE_ORDERING = 73
 } flat_status;
 
 /* Storage/arithmetic mode.  F32: f32 I/O, f32 SIMT arithmetic (parity mode, <=1e-4).
@@ -502,6 +508,113 @@ int32_t flat_backward_grouped(flat_ctx *ctx, int32_t dtype, const flat_attention
 int32_t flat_backward_mha(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
                           const flat_attention_config *config, flat_buffer packed_inputs,
                           flat_buffer packed_grads);
+
+/* ---- runtime telemetry (src/runtime_telemetry.rs:10-177) ------------------------------ */
+/* Passive host-side metadata: none of these calls launches a kernel, touches the stream or
+ * synchronises.  Strings are NUL-terminated UTF-8. */
+
+/* RuntimeDeviceFingerprint (src/runtime_telemetry.rs:35-68).  backend is "Cuda"; driver is the
+ * CUDA driver API version, driver_info the runtime version, compute capability and SM count;
+ * vendor is the PCI vendor id 0x10de; device is compute capability major * 10 + minor. */
+typedef struct flat_device_fingerprint {
+    char name[256];
+    char backend[32];
+    char driver[64];
+    char driver_info[128];
+    uint32_t vendor;
+    uint32_t device;
+} flat_device_fingerprint;
+
+/* RuntimeDeviceCapabilities (src/runtime_telemetry.rs:99-135) with the CUDA counterparts of the
+ * limits: grid x extent, block extents, opt-in shared memory per block, kernel parameter
+ * pointers (bind groups have no CUDA counterpart: 0), largest single allocation (clamped to
+ * u32), warp size as the subgroup range, f16 arithmetic. */
+typedef struct flat_device_capabilities {
+    uint32_t max_workgroups_per_dimension;
+    uint32_t max_workgroup_size_x, max_workgroup_size_y, max_workgroup_size_z;
+    uint32_t max_workgroup_storage_bytes;
+    uint32_t max_binding_entries;
+    uint32_t max_storage_buffer_binding_size;
+    uint32_t subgroup_supported;
+    uint32_t subgroup_min_size, subgroup_max_size;
+    uint32_t f16_supported;
+} flat_device_capabilities;
+
+int32_t flat_ctx_device_fingerprint(const flat_ctx *ctx, flat_device_fingerprint *out);
+int32_t flat_ctx_device_capabilities(const flat_ctx *ctx, flat_device_capabilities *out);
+/* canonical_record (src/runtime_telemetry.rs:49-59, 116-131): writes at most cap bytes
+ * including the NUL and returns the full length without the NUL (snprintf convention), or
+ * a negative flat_status. */
+int64_t flat_device_fingerprint_canonical_record(const flat_device_fingerprint *fp, char *buf,
+                                                 uint64_t cap);
+int64_t flat_device_capabilities_canonical_record(const flat_device_capabilities *caps,
+                                                  char *buf, uint64_t cap);
+/* stable_fingerprint: FNV-1a-64 of the canonical record (src/runtime_telemetry.rs:65-67,
+ * 84-91, 133-135). */
+uint64_t flat_device_fingerprint_stable(const flat_device_fingerprint *fp);
+uint64_t flat_device_capabilities_stable(const flat_device_capabilities *caps);
+
+/* RuntimeKernelId (src/runtime_telemetry.rs:10-20) for this library's kernel families. */
+typedef enum flat_kernel_id {
+    FLAT_KERNEL_FORWARD_TCGEN05 = 0,  /* fwd_sm100_kernel: bf16, head_dim 64/128 */
+    FLAT_KERNEL_FORWARD_GENERIC = 1   /* fwd_simt_kernel: f32 arithmetic, any shape */
+} flat_kernel_id;
+
+/* AutotunerCacheStatus (src/runtime_telemetry.rs:138-145). */
+typedef enum flat_autotuner_cache {
+    FLAT_AUTOTUNER_NOT_APPLICABLE = 0,
+    FLAT_AUTOTUNER_HIT = 1,
+    FLAT_AUTOTUNER_MISS = 2
+} flat_autotuner_cache;
+
+/* RuntimeDispatchTelemetry + RuntimeTileGeometry (src/runtime_telemetry.rs:147-176). */
+typedef struct flat_dispatch_telemetry {
+    int32_t kernel_id;                   /* flat_kernel_id */
+    flat_device_fingerprint device;
+    uint32_t query_rows, kv_rows;        /* tile geometry of one work item */
+    uint32_t workgroups[3];              /* grid of the attention kernel */
+    uint32_t dispatch_count;             /* kernels of one call with warm (cos, sin) tables */
+    uint32_t temporary_allocation_count; /* scratch regions of the context workspace used */
+    uint64_t temporary_allocation_bytes;
+    int32_t has_fallback_reason;
+    char fallback_reason[160];           /* why the generic kernel was selected */
+    int32_t autotuner_cache;             /* flat_autotuner_cache */
+} flat_dispatch_telemetry;
+
+/* WgpuFlatAttention::runtime_telemetry (src/wgpu_backend.rs:370-416): metadata of the dispatch
+ * that a forward call of this dtype / layout / shape would select (rotary may be null: no
+ * RoPE).  The shape is validated like the forward entry points. */
+int32_t flat_forward_runtime_telemetry(flat_ctx *ctx, int32_t dtype, int32_t layout,
+                                       const flat_attention_shape *shape,
+                                       const flat_rotary_config *rotary,
+                                       flat_dispatch_telemetry *out);
+
+/* ---- benchmark manifests (src/benchmark_manifest.rs:10-199) --------------------------- */
+
+/* BenchmarkManifest with its environment, problem and result flattened
+ * (src/benchmark_manifest.rs:13-54); strings are NUL-terminated UTF-8. */
+typedef struct flat_benchmark_manifest {
+    const char *commit_sha, *benchmark_id, *command;
+    const char *device, *backend, *driver, *os, *arch; /* BenchmarkEnvironment */
+    const char *precision;                             /* BenchmarkProblem */
+    uint64_t batch, q_heads, kv_heads, query_len, kv_len, head_dim;
+    int32_t causal;
+    uint32_t warmup_iterations, measured_iterations;
+    uint64_t median_latency_ns, p95_latency_ns, tokens_per_second_milli; /* BenchmarkResult */
+} flat_benchmark_manifest;
+
+#define FLAT_BENCHMARK_MANIFEST_SCHEMA_VERSION 1
+
+/* BenchmarkManifest::validate (src/benchmark_manifest.rs:90-137); `*field` (optional) receives
+ * the name of the offending field for EMPTY_FIELD / ZERO_DIMENSION (static storage). */
+int32_t flat_benchmark_manifest_validate(const flat_benchmark_manifest *m, const char **field);
+/* canonical_json (src/benchmark_manifest.rs:140-199): validates, then writes the schema-1
+ * payload (snprintf convention: returns the full length without the NUL, or a negative
+ * flat_status). */
+int64_t flat_benchmark_manifest_canonical_json(const flat_benchmark_manifest *m, char *buf,
+                                               uint64_t cap);
+/* result_checksum (src/benchmark_manifest.rs:205-209): 16 lower-case hex digits + NUL. */
+int32_t flat_benchmark_manifest_result_checksum(const flat_benchmark_manifest *m, char out[17]);
 
 #ifdef __cplusplus
 }

@@ -48,6 +48,23 @@ int main() {
     CHECK(cfg.raw().has_softmax_scale == 0);
     cfg.softmax_scale = 0.25f;
     CHECK(cfg.raw().has_softmax_scale == 1 && cfg.raw().softmax_scale == 0.25f);
+    // telemetry records and manifests are host-only (src/runtime_telemetry.rs:207-214, src/benchmark_manifest.rs:285-316)
+    flat_device_fingerprint fp{};
+    std::snprintf(fp.name, sizeof fp.name, "GPU a;b=c%%");
+    std::snprintf(fp.backend, sizeof fp.backend, "Cuda");
+    fp.vendor = 0x10de;
+    fp.device = 100;
+    CHECK(canonical_record(fp) == "name=GPU a%3bb%3dc%25;backend=Cuda;driver=;driver_info=;vendor=000010de;device=00000064");
+    CHECK(stable_fingerprint(fp) == stable_fingerprint(fp));
+    flat_benchmark_manifest m{};
+    m.commit_sha = "main";
+    threw = false;
+    try {
+        canonical_json(m);
+    } catch (const Error &e) {
+        threw = e.status() == FLAT_ERR_MANIFEST_INVALID_COMMIT_SHA;
+    }
+    CHECK(threw);
     // without an sm_100 device a context cannot be created, and nothing falls back to the CPU
     if (std::getenv("FLAT_EXPECT_NO_DEVICE")) {
         threw = false;
