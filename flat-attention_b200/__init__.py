@@ -22,6 +22,7 @@ HEADER_PATH = os.path.join(HERE, "..", "include", "flat_attention_b200.h")
 
 F32 = 0
 BF16 = 1
+F16 = 2  # IEEE binary16 storage: forward entry points only
 HEAD_MAJOR = 0
 PROJECTION = 1
 
@@ -160,12 +161,14 @@ def _dtype_of(t) -> int:
         return F32
     if t.dtype == torch.bfloat16:
         return BF16
+    if t.dtype == torch.float16:
+        return F16
     raise FlatAttentionError(26, f"unsupported tensor dtype {t.dtype}")
 
 
 def torch_dtype(dtype: int):
     torch = _torch()
-    return torch.bfloat16 if dtype == BF16 else torch.float32
+    return {BF16: torch.bfloat16, F16: torch.float16}.get(dtype, torch.float32)
 
 
 def forward_layout(dtype: int, shp: Shape) -> ForwardLayout:

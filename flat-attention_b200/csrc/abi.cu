@@ -111,9 +111,15 @@ int check_buffer(flat_ctx *ctx, const char *name, flat_buffer b, uint64_t requir
 }
 
 int check_dtype(flat_ctx *ctx, int dtype) {
+    if (dtype == FLAT_F16)
+        return fail(ctx, FLAT_ERR_UNSUPPORTED_DTYPE, "binary16 storage is supported by the forward entry points only");
     if (dtype != FLAT_F32 && dtype != FLAT_BF16) return fail(ctx, FLAT_ERR_UNSUPPORTED_DTYPE, "unknown dtype %d", dtype);
     return FLAT_OK;
 }
+
+// forward entry points also take IEEE binary16 storage
+int check_forward_dtype(flat_ctx *ctx, int dtype) { return dtype == FLAT_F16 ? FLAT_OK : check_dtype(ctx, dtype); }
+inline bool storage16(int dtype) { return dtype == FLAT_BF16 || dtype == FLAT_F16; }
 
 uint64_t lse_offset_bytes(int dtype, uint64_t q_elements) {
     uint64_t o = q_elements * dtype_size(dtype);
@@ -133,7 +139,7 @@ struct ForwardCall {
 };
 
 int launch_forward(flat_ctx *ctx, int dtype, const FwdParams &p) {
-    if (dtype == FLAT_BF16 && forward_sm100_supported(p)) return launch_forward_sm100(ctx, p);
+    if (storage16(dtype) && forward_sm100_supported(p)) return launch_forward_sm100(ctx, p);
     return launch_forward_simt(ctx, dtype, p);
 }
 
@@ -143,7 +149,7 @@ int forward_common(flat_ctx *ctx, const ForwardCall &call, const flat_attention_
                    flat_buffer out_and_lse, FwdParams *params_out = nullptr) {
     if (!ctx) return FLAT_ERR_NULL_POINTER;
     int st;
-    if ((st = check_dtype(ctx, call.dtype))) return st;
+    if ((st = check_forward_dtype(ctx, call.dtype))) return st;
     Dims d;
     if ((st = validate_shape(ctx, shape, &d))) return st;
     float theta = 0.f;
@@ -208,6 +214,7 @@ int forward_common(flat_ctx *ctx, const ForwardCall &call, const flat_attention_
     if ((st = check_buffer(ctx, "O|LSE", out_and_lse, lse_off + d.lse_elements * 4))) return st;
 
     FwdParams p{};
+    p.f16_io = call.dtype == FLAT_F16 ? 1 : 0;
     p.q = q.ptr;
     p.k = k.ptr;
     p.v = v.ptr;
@@ -252,7 +259,7 @@ int forward_common(flat_ctx *ctx, const ForwardCall &call, const flat_attention_
         }
         // the metadata sits at the start of the workspace: size it for the kernel first, a later growth would move it
         p.varlen = reinterpret_cast<const flat_varlen_sequence *>(call.varlen_host);  // non-null for the capability test
-        const bool tensor_path = call.dtype == FLAT_BF16 && forward_sm100_supported(p);
+        const bool tensor_path = storage16(call.dtype) && forward_sm100_supported(p);
         if ((st = ensure_workspace(ctx, kWorkspaceMeta + (tensor_path ? forward_sm100_workspace_bytes(p) : 0)))) return st;
         FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ctx->workspace, call.varlen_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
         p.varlen = static_cast<const flat_varlen_sequence *>(ctx->workspace);
@@ -265,7 +272,7 @@ int forward_common(flat_ctx *ctx, const ForwardCall &call, const flat_attention_
         p.alibi_kv_off = (int64_t)call.alibi_kv_off;
         for (uint64_t i = 0; i < call.alibi_count; ++i)
             p.alibi_max_abs_slope = std::max(p.alibi_max_abs_slope, std::fabs(call.alibi_slopes[i]));
-        const bool tensor_path = call.dtype == FLAT_BF16 && forward_sm100_supported(p);
+        const bool tensor_path = storage16(call.dtype) && forward_sm100_supported(p);
         if ((st = ensure_workspace(ctx, kWorkspaceMeta + (tensor_path ? forward_sm100_workspace_bytes(p) : 0)))) return st;
         FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ctx->workspace, call.alibi_slopes, call.alibi_count * sizeof(float),
                                           cudaMemcpyHostToDevice, ctx->stream));
@@ -701,7 +708,7 @@ int32_t flat_synchronize(flat_ctx *ctx) {
 // ---- forward ---------------------------------------------------------------------------------
 int32_t flat_forward_layout_for(int32_t dtype, const flat_attention_shape *shape, flat_forward_layout *out) {
     if (!out) return FLAT_ERR_NULL_POINTER;
-    if (dtype != FLAT_F32 && dtype != FLAT_BF16) return FLAT_ERR_UNSUPPORTED_DTYPE;
+    if (dtype != FLAT_F32 && dtype != FLAT_BF16 && dtype != FLAT_F16) return FLAT_ERR_UNSUPPORTED_DTYPE;
     Dims d;
     int st = validate_shape(nullptr, shape, &d);
     if (st) return st;
@@ -783,7 +790,7 @@ int32_t flat_forward_runtime_telemetry(flat_ctx *ctx, int32_t dtype, int32_t lay
     std::memset(out, 0, sizeof *out);
     out->device = ctx->fingerprint;
     out->autotuner_cache = FLAT_AUTOTUNER_NOT_APPLICABLE;
-    if (dtype == FLAT_BF16 && forward_sm100_supported(p)) {
+    if (storage16(dtype) && forward_sm100_supported(p)) {
         out->kernel_id = FLAT_KERNEL_FORWARD_TCGEN05;
         forward_sm100_geometry(ctx, p, &out->query_rows, &out->kv_rows, out->workgroups, &out->dispatch_count);
         out->temporary_allocation_bytes = forward_sm100_workspace_bytes(p);
@@ -794,8 +801,8 @@ int32_t flat_forward_runtime_telemetry(flat_ctx *ctx, int32_t dtype, int32_t lay
     forward_simt_geometry(p, &out->query_rows, &out->kv_rows, out->workgroups);
     out->dispatch_count = 1;
     out->has_fallback_reason = 1;
-    if (dtype != FLAT_BF16)
-        std::snprintf(out->fallback_reason, sizeof out->fallback_reason, "tensor-core specialization requires bf16 storage");
+    if (!storage16(dtype))
+        std::snprintf(out->fallback_reason, sizeof out->fallback_reason, "tensor-core specialization requires 16-bit storage");
     else if (p.head_dim != 64 && p.head_dim != 128)
         std::snprintf(out->fallback_reason, sizeof out->fallback_reason,
                       "tensor-core specialization unavailable for head_dim=%d", p.head_dim);
@@ -847,9 +854,11 @@ static int validate_host_tensor(flat_ctx *ctx, const char *name, int dtype, cons
                 return fail(ctx, FLAT_ERR_NON_FINITE_INPUT, "tensor %s contains a non-finite value at index %llu", name,
                             (unsigned long long)i);
     } else {
+        // bf16: 8 exponent bits below the sign; binary16: 5 (F16::is_finite, src/f16.rs:112-115)
+        const uint16_t mask = dtype == FLAT_F16 ? 0x7c00u : 0x7f80u;
         const uint16_t *p = static_cast<const uint16_t *>(data);
         for (uint64_t i = 0; i < actual; ++i)
-            if ((p[i] & 0x7f80u) == 0x7f80u)
+            if ((p[i] & mask) == mask)
                 return fail(ctx, FLAT_ERR_NON_FINITE_INPUT, "tensor %s contains a non-finite value at index %llu", name,
                             (unsigned long long)i);
     }
@@ -862,7 +871,7 @@ int32_t flat_forward_host(flat_ctx *ctx, int32_t dtype, int32_t layout, const fl
                           int32_t check_finite, void *out_and_lse, uint64_t out_bytes) {
     if (!ctx) return FLAT_ERR_NULL_POINTER;
     int st;
-    if ((st = check_dtype(ctx, dtype))) return st;
+    if ((st = check_forward_dtype(ctx, dtype))) return st;
     if (layout != FLAT_LAYOUT_HEAD_MAJOR && layout != FLAT_LAYOUT_PROJECTION)
         return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE, "unknown layout %d", layout);
     Dims d;

@@ -86,7 +86,7 @@ struct KernelTimer {
     }
 };
 
-inline size_t dtype_size(int dtype) { return dtype == FLAT_BF16 ? 2 : 4; }
+inline size_t dtype_size(int dtype) { return dtype == FLAT_F32 ? 4 : 2; }
 
 // Grows (never shrinks) the context scratch; synchronises the stream when it reallocates, so it
 // must be called before anything of the current call is copied into the scratch.
@@ -133,6 +133,7 @@ struct FwdParams {
     const float *alibi_slopes;           // device, [q_heads] or null
     int64_t alibi_q_off, alibi_kv_off;
     float alibi_max_abs_slope;           // host-side copy of max |slope|
+    int f16_io;                          // 16-bit storage is IEEE binary16 instead of bf16 (forward only)
 };
 
 // Generic SIMT forward (f32 arithmetic; T = float or __nv_bfloat16 storage).

@@ -18,9 +18,11 @@ constexpr int kThreads = 128;
 template <typename T> __device__ __forceinline__ float to_f32(T x);
 template <> __device__ __forceinline__ float to_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half x) { return __half2float(x); }
 template <typename T> __device__ __forceinline__ T from_f32(float x);
 template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float x) { return __float2half_rn(x); }
 
 // Rotation of one interleaved pair at an absolute position (src/rotary_grouped.rs:36-50): the
 // frequency comes from the host table, the angle is one f32 multiply as in the oracle.
@@ -238,6 +240,7 @@ void forward_simt_geometry(const FwdParams &p, uint32_t *query_rows, uint32_t *k
 int launch_forward_simt(flat_ctx *ctx, int dtype, const FwdParams &p) {
     if (p.q_heads > 65535 || p.batch > 65535)
         return fail(ctx, FLAT_ERR_DISPATCH_LIMIT, "grid dimension %d exceeds 65535", p.q_heads > 65535 ? p.q_heads : p.batch);
+    if (dtype == FLAT_F16) return dispatch<__half>(ctx, p);
     return dtype == FLAT_BF16 ? dispatch<__nv_bfloat16>(ctx, p) : dispatch<float>(ctx, p);
 }
 

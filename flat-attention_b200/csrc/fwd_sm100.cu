@@ -178,7 +178,9 @@ __device__ __forceinline__ int item_index(const KernelParams &p, int k) {
 
 // ALIBI: the softmax warps add slope[q_head] * (key position - query position) to every scaled score
 // (src/attention_bias.rs:82-95) before the running maximum is taken.
-template <int D, bool CONVK, bool ALIBI>
+// F16IO: Q, K, V and O are IEEE binary16 instead of bf16 (P is then written as binary16 too, since one MMA takes A and B
+// of one format); accumulation, softmax and LSE stay f32.
+template <int D, bool CONVK, bool ALIBI, bool F16IO>
 __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_constant__ KernelParams p) {
     using C = Cfg<D, CONVK>;
     extern __shared__ uint8_t smem_raw[];
@@ -582,8 +584,13 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                             asm("mov.b64 %0, {%1, %2};" : "=l"(p2) : "f"(p0), "f"(p1));
                             if (i & 2) asm("add.rn.f32x2 %0, %0, %1;" : "+l"(sum3) : "l"(p2));
                             else asm("add.rn.f32x2 %0, %0, %1;" : "+l"(sum2) : "l"(p2));
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
-                            pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                            if constexpr (F16IO) {
+                                __half2 h2 = __floats2half2_rn(p0, p1);
+                                pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                            } else {
+                                __nv_bfloat162 h2 = __floats2bfloat162_rn(p0, p1);
+                                pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                            }
                         }
                         tmem_st16(t_s + c * 16, pk);
                     }
@@ -659,7 +666,15 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                             uint32_t hi[4];
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
-                                const float x = __uint_as_float(in[e] << 16), y = __uint_as_float(in[e] & 0xffff0000u);
+                                float x, y;
+                                if constexpr (F16IO) {
+                                    const float2 xy = __half22float2(*reinterpret_cast<const __half2 *>(&in[e]));
+                                    x = xy.x;
+                                    y = xy.y;
+                                } else {
+                                    x = __uint_as_float(in[e] << 16);
+                                    y = __uint_as_float(in[e] & 0xffff0000u);
+                                }
                                 const float rx = x * cc[e] - y * ss[e], ry = x * ss[e] + y * cc[e];
                                 const __half2 h2 = __floats2half2_rn(rx, ry);
                                 hi[e] = *reinterpret_cast<const uint32_t *>(&h2);
@@ -699,9 +714,14 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                         uint32_t pk[16];
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
-                            __nv_bfloat162 h2 =
-                                __floats2bfloat162_rn(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
-                            pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                            if constexpr (F16IO) {
+                                __half2 h2 = __floats2half2_rn(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                                pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                            } else {
+                                __nv_bfloat162 h2 =
+                                    __floats2bfloat162_rn(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                                pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                            }
                         }
                         if (p.o_align32) {
                             // 32-byte stores: a lane fills whole 32-byte sectors of its row
@@ -765,7 +785,8 @@ __global__ void __launch_bounds__(256) fill_u32_kernel(uint32_t *__restrict__ ds
 
 // K rotation prologue: x (bf16, strided) -> y (fp16, compact [B, H, N, D]) with interleaved pairs
 // (src/rotary_grouped.rs:36-50).  One thread moves 8 elements (16 bytes).
-__global__ void __launch_bounds__(256) rotate_to_f16_kernel(const __nv_bfloat16 *__restrict__ x, __half *__restrict__ y,
+template <bool F16IN>
+__global__ void __launch_bounds__(256) rotate_to_f16_kernel(const uint16_t *__restrict__ x, __half *__restrict__ y,
                                                             const float2 *__restrict__ table, int heads, int rows,
                                                             int head_dim, int64_t bs, int64_t hs, int64_t rs,
                                                             int64_t total_vec) {
@@ -785,7 +806,15 @@ __global__ void __launch_bounds__(256) rotate_to_f16_kernel(const __nv_bfloat16 
         uint32_t out[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-            const float fx = __uint_as_float(in[e] << 16), fy = __uint_as_float(in[e] & 0xffff0000u);
+            float fx, fy;
+            if constexpr (F16IN) {
+                const float2 xy = __half22float2(*reinterpret_cast<const __half2 *>(&in[e]));
+                fx = xy.x;
+                fy = xy.y;
+            } else {
+                fx = __uint_as_float(in[e] << 16);
+                fy = __uint_as_float(in[e] & 0xffff0000u);
+            }
             const __half2 h2 = __floats2half2_rn(fx * cc[e] - fy * ss[e], fx * ss[e] + fy * cc[e]);
             out[e] = *reinterpret_cast<const uint32_t *>(&h2);
         }
@@ -851,6 +880,7 @@ bool forward_sm100_supported(const FwdParams &p) {
         if (!(ps == 8 || ps == 16 || ps == 32 || ps == 64 || ps == 128)) return false;
     }
     if (p.rope_k && !p.rope_q) return false;
+    if (p.f16_io && p.alibi_slopes) return false;  // no binary16 instantiation of the ALiBi kernel
     if (p.alibi_slopes) {
         // the kernel forms bias positions in f32: they must stay exact
         if (p.varlen || p.page_table) return false;
@@ -887,8 +917,9 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     const void *k_ptr = p.k;
     int64_t k_rs = p.kv_rs, k_hs = p.kv_hs, k_bs = p.kv_bs;
     bool k_f16 = false;
-    const bool convk = p.rope_q && !p.rope_k;  // Q rotated against already rotated bf16 K: K tiles become fp16 in smem
-    const bool q_f16 = p.rope_q;
+    const bool io16 = p.f16_io != 0;                    // binary16 storage: every operand is fp16 from the start
+    const bool convk = p.rope_q && !p.rope_k && !io16;  // Q rotated against already rotated bf16 K: K tiles become fp16 in smem
+    const bool q_f16 = p.rope_q || io16;
     char *scratch = scratch_ptr(ctx);
     const float2 *q_table = nullptr;
     if (p.rope_q) {
@@ -906,8 +937,12 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
             if ((st = rope_table(ctx, f, D / 2, p.kv_len, p.k_rope_off, &kt))) return st;
             const int64_t kvecs = (int64_t)p.batch * p.kv_heads * p.kv_len * (D / 8);
             const int blocks = (int)std::min<int64_t>((kvecs + 255) / 256, (int64_t)ctx->sm_count * 16);
-            rotate_to_f16_kernel<<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const __nv_bfloat16 *>(p.k), rk, kt,
-                                                                  p.kv_heads, p.kv_len, D, p.kv_bs, p.kv_hs, p.kv_rs, kvecs);
+            if (p.f16_io)
+                rotate_to_f16_kernel<true><<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const uint16_t *>(p.k), rk, kt, p.kv_heads,
+                                                                            p.kv_len, D, p.kv_bs, p.kv_hs, p.kv_rs, kvecs);
+            else
+                rotate_to_f16_kernel<false><<<blocks, 256, 0, ctx->stream>>>(reinterpret_cast<const uint16_t *>(p.k), rk, kt, p.kv_heads,
+                                                                             p.kv_len, D, p.kv_bs, p.kv_hs, p.kv_rs, kvecs);
             ctx->launches += 1;
             k_ptr = rk;
             k_rs = D; k_hs = (int64_t)p.kv_len * D; k_bs = k_hs * p.kv_heads;
@@ -917,17 +952,17 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
 
     KernelParams kp{};
     // Q always arrives as the caller's bf16 tensor; rotation (if any) happens in shared memory
-    if ((st = make_map(ctx, &kp.map_q, false, p.q, D, p.q_len, p.q_heads, p.batch, p.q_rs, p.q_hs, p.q_bs, kTileRows))) return st;
+    if ((st = make_map(ctx, &kp.map_q, io16, p.q, D, p.q_len, p.q_heads, p.batch, p.q_rs, p.q_hs, p.q_bs, kTileRows))) return st;
     if (p.page_table) {
         // physical layout [pages, page_size, kv_heads*D]: dims (d, token in page, head, page)
         const int64_t row = p.page_row_stride;
-        if ((st = make_map(ctx, &kp.map_k, false, p.k, D, p.page_size, p.kv_heads, p.max_pages, row, p.kv_hs,
+        if ((st = make_map(ctx, &kp.map_k, io16, p.k, D, p.page_size, p.kv_heads, p.max_pages, row, p.kv_hs,
                            row * p.page_size, p.page_size))) return st;
-        if ((st = make_map(ctx, &kp.map_v, false, p.v, D, p.page_size, p.kv_heads, p.max_pages, row, p.kv_hs,
+        if ((st = make_map(ctx, &kp.map_v, io16, p.v, D, p.page_size, p.kv_heads, p.max_pages, row, p.kv_hs,
                            row * p.page_size, p.page_size))) return st;
     } else {
-        if ((st = make_map(ctx, &kp.map_k, k_f16, k_ptr, D, p.kv_len, p.kv_heads, p.batch, k_rs, k_hs, k_bs, kTileRows))) return st;
-        if ((st = make_map(ctx, &kp.map_v, false, p.v, D, p.kv_len, p.kv_heads, p.batch, p.kv_rs, p.kv_hs, p.kv_bs, kTileRows))) return st;
+        if ((st = make_map(ctx, &kp.map_k, k_f16 || io16, k_ptr, D, p.kv_len, p.kv_heads, p.batch, k_rs, k_hs, k_bs, kTileRows))) return st;
+        if ((st = make_map(ctx, &kp.map_v, io16, p.v, D, p.kv_len, p.kv_heads, p.batch, p.kv_rs, p.kv_hs, p.kv_bs, kTileRows))) return st;
     }
     kp.o = p.o;
     kp.lse = p.lse;
@@ -938,8 +973,8 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     kp.causal = p.causal;
     kp.causal_off = p.causal_off;
     kp.scale_log2 = p.scale * kLog2e;
-    kp.idesc_qk = make_idesc(q_f16 ? kFmtF16 : kFmtBF16, (k_f16 || convk) ? kFmtF16 : kFmtBF16, 0, 0, 128, 128);
-    kp.idesc_pv = make_idesc(kFmtBF16, kFmtBF16, 0, 1, 128, (uint32_t)D);
+    kp.idesc_qk = make_idesc(q_f16 ? kFmtF16 : kFmtBF16, (k_f16 || convk || io16) ? kFmtF16 : kFmtBF16, 0, 0, 128, 128);
+    kp.idesc_pv = io16 ? make_idesc(kFmtF16, kFmtF16, 0, 1, 128, (uint32_t)D) : make_idesc(kFmtBF16, kFmtBF16, 0, 1, 128, (uint32_t)D);
     kp.page_table = p.page_table;
     kp.page_size = p.page_size;
     kp.max_pages = p.max_pages;
@@ -984,15 +1019,18 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     kp.alibi_slopes = p.alibi_slopes;
     kp.alibi_delta = (int)(p.alibi_kv_off - p.alibi_q_off);
     kp.alibi_inv_scale = 1.0f / p.scale;
-    if (p.alibi_slopes) {
-        if (D == 128) st = convk ? run(fwd_sm100_kernel<128, true, true>, Cfg<128, true>::kSmemBytes)
-                                 : run(fwd_sm100_kernel<128, false, true>, Cfg<128, false>::kSmemBytes);
-        else st = convk ? run(fwd_sm100_kernel<64, true, true>, Cfg<64, true>::kSmemBytes)
-                        : run(fwd_sm100_kernel<64, false, true>, Cfg<64, false>::kSmemBytes);
-    } else if (D == 128) st = convk ? run(fwd_sm100_kernel<128, true, false>, Cfg<128, true>::kSmemBytes)
-                                    : run(fwd_sm100_kernel<128, false, false>, Cfg<128, false>::kSmemBytes);
-    else st = convk ? run(fwd_sm100_kernel<64, true, false>, Cfg<64, true>::kSmemBytes)
-                    : run(fwd_sm100_kernel<64, false, false>, Cfg<64, false>::kSmemBytes);
+    if (io16) {
+        st = D == 128 ? run(fwd_sm100_kernel<128, false, false, true>, Cfg<128, false>::kSmemBytes)
+                      : run(fwd_sm100_kernel<64, false, false, true>, Cfg<64, false>::kSmemBytes);
+    } else if (p.alibi_slopes) {
+        if (D == 128) st = convk ? run(fwd_sm100_kernel<128, true, true, false>, Cfg<128, true>::kSmemBytes)
+                                 : run(fwd_sm100_kernel<128, false, true, false>, Cfg<128, false>::kSmemBytes);
+        else st = convk ? run(fwd_sm100_kernel<64, true, true, false>, Cfg<64, true>::kSmemBytes)
+                        : run(fwd_sm100_kernel<64, false, true, false>, Cfg<64, false>::kSmemBytes);
+    } else if (D == 128) st = convk ? run(fwd_sm100_kernel<128, true, false, false>, Cfg<128, true>::kSmemBytes)
+                                    : run(fwd_sm100_kernel<128, false, false, false>, Cfg<128, false>::kSmemBytes);
+    else st = convk ? run(fwd_sm100_kernel<64, true, false, false>, Cfg<64, true>::kSmemBytes)
+                    : run(fwd_sm100_kernel<64, false, false, false>, Cfg<64, false>::kSmemBytes);
     if (st) return st;
     ctx->launches += 1;
     FLAT_CUDA_OK(ctx, cudaGetLastError());

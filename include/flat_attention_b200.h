@@ -80,7 +80,10 @@ typedef enum flat_status {
 
 /* Storage/arithmetic mode.  F32: f32 I/O, f32 SIMT arithmetic (parity mode, <=1e-4).
  * BF16: bf16 Q/K/V/dO/O, f32 LSE, tcgen05 tensor-core arithmetic with f32 accumulation. */
-typedef enum flat_dtype { FLAT_F32 = 0, FLAT_BF16 = 1 } flat_dtype;
+/* FLAT_F16 is IEEE binary16 storage (F16, src/f16.rs:9-115; the packed-f16 executor
+ * src/wgpu_f16_backend.rs:168-430): accepted by the forward entry points and
+ * flat_forward_layout_for only; arithmetic, softmax and LSE stay f32 as in the reference. */
+typedef enum flat_dtype { FLAT_F32 = 0, FLAT_BF16 = 1, FLAT_F16 = 2 } flat_dtype;
 
 /* HEAD_MAJOR: Q/O [B,Hq,Nq,D], K/V [B,Hkv,Nkv,D] (src/grouped.rs:11-16).
  * PROJECTION: Q/O [B*Nq, Hq*D], K/V [B*Nkv, Hkv*D] (src/projection_grouped.rs:3-8).

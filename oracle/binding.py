@@ -301,6 +301,27 @@ def fixture(length, step, phase, a, c=0.0, b=0.0):
     return out
 
 
+def f16_from_f32(values) -> np.ndarray:
+    """F16::from_f32 (src/f16.rs:26-82) element-wise; returns the binary16 bit patterns."""
+    a = _f32(values)
+    out = np.empty(a.size, np.uint16)
+    lib().flat_oracle_f16_from_f32(_p(a), C.c_uint64(a.size), out.ctypes.data_as(C.POINTER(C.c_uint16)))
+    return out
+
+
+def f16_to_f32(bits) -> np.ndarray:
+    """F16::to_f32 (src/f16.rs:85-110) element-wise."""
+    a = np.ascontiguousarray(bits, dtype=np.uint16).reshape(-1)
+    out = np.empty(a.size, np.float32)
+    lib().flat_oracle_f16_to_f32(a.ctypes.data_as(C.POINTER(C.c_uint16)), C.c_uint64(a.size), _p(out))
+    return out
+
+
+def f16_round(values) -> np.ndarray:
+    """Quantise to binary16 and expand again: the values a binary16 kernel consumes."""
+    return f16_to_f32(f16_from_f32(values))
+
+
 class PagedKvTable:
     """PagedKvTable restatement (src/paged_kv.rs:75-188)."""
 

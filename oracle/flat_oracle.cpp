@@ -734,6 +734,80 @@ void flat_oracle_rope_frequencies(float theta, uint64_t head_dim, float *out) {
 
 // Closed-form test fixtures of the reference tests: sin(x)*a + cos(x*c)*b with x = i*step + phase
 // in f32 libm arithmetic (tests/grouped.rs:6-13, tests/rotary_grouped.rs:6-13, ...).
+// F16::from_f32 (src/f16.rs:26-82): IEEE binary16, round to nearest, ties to even, written out on the bit fields.
+static uint16_t f16_from_f32_bits(float value) {
+    uint32_t bits;
+    std::memcpy(&bits, &value, 4);
+    const uint16_t sign = (uint16_t)((bits >> 16) & 0x8000);
+    const int32_t exponent = (int32_t)((bits >> 23) & 0xff);
+    uint32_t mantissa = bits & 0x007fffffu;
+    if (exponent == 0xff) {
+        if (mantissa == 0) return sign | 0x7c00;
+        uint16_t payload = (uint16_t)(mantissa >> 13);
+        if (payload == 0) payload = 1;
+        return sign | 0x7c00 | payload;
+    }
+    int32_t half_exponent = exponent - 127 + 15;
+    if (half_exponent >= 31) return sign | 0x7c00;
+    if (half_exponent <= 0) {
+        if (half_exponent < -10) return sign;
+        mantissa |= 0x00800000u;
+        const uint32_t shift = (uint32_t)(14 - half_exponent);
+        uint32_t half_mantissa = mantissa >> shift;
+        const uint32_t remainder = mantissa & ((1u << shift) - 1);
+        const uint32_t halfway = 1u << (shift - 1);
+        if (remainder > halfway || (remainder == halfway && (half_mantissa & 1))) half_mantissa += 1;
+        return sign | (uint16_t)half_mantissa;
+    }
+    uint32_t half_mantissa = mantissa >> 13;
+    const uint32_t remainder = mantissa & 0x1fff;
+    if (remainder > 0x1000 || (remainder == 0x1000 && (half_mantissa & 1))) {
+        half_mantissa += 1;
+        if (half_mantissa == 0x400) {
+            half_mantissa = 0;
+            half_exponent += 1;
+            if (half_exponent >= 31) return sign | 0x7c00;
+        }
+    }
+    return sign | (uint16_t)(half_exponent << 10) | (uint16_t)half_mantissa;
+}
+
+// F16::to_f32 (src/f16.rs:85-110): exact.
+static float f16_to_f32_bits(uint16_t bits) {
+    const uint32_t sign = (uint32_t)(bits & 0x8000) << 16;
+    const uint32_t exponent = (bits >> 10) & 0x1f;
+    const uint32_t mantissa = bits & 0x03ff;
+    uint32_t out;
+    if (exponent == 0) {
+        if (mantissa == 0) {
+            out = sign;
+        } else {
+            uint32_t normalized = mantissa;
+            uint32_t exponent32 = 127 - 14;
+            while ((normalized & 0x400) == 0) {
+                normalized <<= 1;
+                exponent32 -= 1;
+            }
+            normalized &= 0x03ff;
+            out = sign | (exponent32 << 23) | (normalized << 13);
+        }
+    } else if (exponent == 0x1f) {
+        out = sign | 0x7f800000u | (mantissa << 13);
+    } else {
+        out = sign | ((exponent + (127 - 15)) << 23) | (mantissa << 13);
+    }
+    float f;
+    std::memcpy(&f, &out, 4);
+    return f;
+}
+
+void flat_oracle_f16_from_f32(const float *src, uint64_t n, uint16_t *dst) {
+    for (uint64_t i = 0; i < n; ++i) dst[i] = f16_from_f32_bits(src[i]);
+}
+void flat_oracle_f16_to_f32(const uint16_t *src, uint64_t n, float *dst) {
+    for (uint64_t i = 0; i < n; ++i) dst[i] = f16_to_f32_bits(src[i]);
+}
+
 void flat_oracle_fixture(float *out, uint64_t len, float step, float phase, float a, float c,
                          float b) {
     for (usize i = 0; i < len; ++i) {

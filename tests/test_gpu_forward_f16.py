@@ -1,0 +1,126 @@
+"""IEEE binary16 storage on the forward entry points against the CPU oracle evaluated on the
+de-quantised inputs, as tests/wgpu_f16.rs does: O is compared with the oracle's output rounded to
+binary16 (ATOL 2e-3, RTOL 5e-3), LSE with the oracle's f32 LSE (ATOL 8e-4, RTOL 2e-3)."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import binding as ob
+from tests.gpu_util import assert_close, ctx, fa
+
+pytestmark = pytest.mark.gpu
+
+O_ATOL, O_RTOL, LSE_ATOL, LSE_RTOL = 2.0e-3, 5.0e-3, 8.0e-4, 2.0e-3  # tests/wgpu_f16.rs:8-11
+
+
+def fixture(n):
+    # tests/wgpu_f16.rs:13-25
+    i = np.arange(n, dtype=np.float32)
+    q = np.sin(i * np.float32(0.031) - np.float32(0.7), dtype=np.float32) * np.float32(0.85)
+    k = np.cos(i * np.float32(0.047) + np.float32(0.2), dtype=np.float32) * np.float32(0.75)
+    v = np.sin(i * np.float32(0.019) - np.float32(0.4), dtype=np.float32) * np.float32(1.2)
+    return q, k, v
+
+
+def half(bits):
+    return torch.from_numpy(np.ascontiguousarray(bits).view(np.float16)).cuda()
+
+
+def run(kind, shp, cfg, q16, k16, v16, rot=None, layout=None):
+    c = ctx()
+    out = c.create_output_buffer(fa.F16, shp)
+    out.fill_(0x7f)
+    before = c.launch_count()
+    args = (fa.F16, shp, cfg) + ((rot,) if rot is not None else ()) + (half(q16), half(k16), half(v16), out)
+    getattr(c, kind)(*args)
+    o, lse = c.split_output(out, fa.F16, shp, layout if layout is not None else fa.HEAD_MAJOR)
+    assert o.dtype == torch.float16
+    return o.float().cpu().numpy().reshape(-1), lse.cpu().numpy().reshape(-1), c.launch_count() - before
+
+
+# tests/wgpu_f16.rs:68-137: the two reference shapes (generic kernel: seq_len < 32)
+@pytest.mark.parametrize("B,H,N,D", [(1, 2, 17, 64), (1, 1, 9, 128)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_packed_f16_reference_shapes(B, H, N, D, causal):
+    q, k, v = fixture(B * H * N * D)
+    q16, k16, v16 = ob.f16_from_f32(q), ob.f16_from_f32(k), ob.f16_from_f32(v)
+    eo, el = ob.forward_reference(ob.f16_to_f32(q16), ob.f16_to_f32(k16), ob.f16_to_f32(v16), B, H, N, D, causal)
+    o, l, _ = run("forward_mha", fa.shape(B, H, H, N, N, D), fa.config(causal), q16, k16, v16)
+    assert_close("packed-f16 O", o, ob.f16_round(eo), O_ATOL, O_RTOL)
+    assert_close("packed-f16 LSE", l, el, LSE_ATOL, LSE_RTOL)
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,N,D", [(1, 4, 2, 256, 128), (2, 2, 2, 128, 128), (1, 4, 1, 200, 128), (1, 2, 2, 333, 64),
+                                          (1, 8, 2, 700, 64), (1, 2, 1, 640, 128), (1, 3, 3, 50, 80)])
+@pytest.mark.parametrize("causal", [False, True])
+def test_grouped_f16(B, Hq, Hkv, N, D, causal):
+    """Tensor-core route (generic for head_dim 80): N(0,1) inputs quantised to binary16."""
+    g = lambda n, s: torch.randn(n, generator=torch.Generator().manual_seed(s)).numpy()
+    q16, k16, v16 = (ob.f16_from_f32(g(B * h * N * D, s)) for h, s in ((Hq, 1), (Hkv, 2), (Hkv, 3)))
+    eo, el = ob.forward_reference_grouped(ob.f16_to_f32(q16), ob.f16_to_f32(k16), ob.f16_to_f32(v16), B, Hq, Hkv, N, D, causal)
+    o, l, launches = run("forward_grouped", fa.shape(B, Hq, Hkv, N, N, D), fa.config(causal), q16, k16, v16)
+    assert_close("f16 O", o, ob.f16_round(eo), O_ATOL, O_RTOL)
+    assert_close("f16 LSE", l, el, LSE_ATOL, LSE_RTOL)
+    assert launches == 1 and ctx().device_status() == 0
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Nq,Nkv,D,causal,coff,qr,kr,rotate_k", [
+    (1, 4, 2, 256, 256, 128, True, 0, 7, 7, True),
+    (2, 4, 2, 100, 300, 128, True, 200, 200, 0, True),
+    (1, 8, 2, 130, 517, 64, True, 387, 400, 13, True),
+    (1, 4, 1, 64, 400, 128, False, 0, 50, 3, True),
+    (1, 4, 2, 128, 384, 128, True, 256, 256, 0, False),  # K already rotated and stored in binary16
+])
+def test_projection_rope_asymmetric_f16(B, Hq, Hkv, Nq, Nkv, D, causal, coff, qr, kr, rotate_k):
+    theta = 5e5
+    g = lambda n, s: ob.f16_round(torch.randn(n, generator=torch.Generator().manual_seed(s)).numpy())
+    q, k, v = g(B * Nq * Hq * D, 1), g(B * Nkv * Hkv * D, 2), g(B * Nkv * Hkv * D, 3)
+    kpos = np.repeat(np.tile(np.arange(Nkv, dtype=np.uint64) + kr, B), Hkv)
+    qpos = np.repeat(np.tile(np.arange(Nq, dtype=np.uint64) + qr, B), Hq)
+    k_in = k
+    if rotate_k:
+        rk = ob.rotate_rows(k, D, kpos, theta)
+    else:
+        k_in = rk = ob.f16_round(ob.rotate_rows(k, D, kpos, theta))
+    rq = ob.rotate_rows(q, D, qpos, theta)
+    rows = [(b, h, r) for b in range(B) for h in range(Hq) for r in range(Nq)]
+    eo, el = ob.forward_rows(rq, rk, v, ob._shape(B, Hq, Hkv, Nq, Nkv, D, coff), ob.PROJECTION, rows, causal, threads=8)
+    o, l, launches = run("forward_projection_rope_asymmetric", fa.shape(B, Hq, Hkv, Nq, Nkv, D, coff), fa.config(causal),
+                         ob.f16_from_f32(q), ob.f16_from_f32(k_in), ob.f16_from_f32(v), rot=fa.rotary(theta, qr, kr, rotate_k=rotate_k),
+                         layout=fa.PROJECTION)
+    o = o.reshape(B, Nq, Hq, D).transpose(0, 2, 1, 3).reshape(-1)
+    assert_close("f16 rope O", o, ob.f16_round(eo), O_ATOL, O_RTOL)
+    assert_close("f16 rope LSE", l, el, LSE_ATOL, LSE_RTOL)
+    assert launches >= 2 and ctx().device_status() == 0  # tables / K rotation + the tensor-core kernel
+
+
+def test_f16_only_on_forward_entry_points():
+    c = ctx()
+    shp = fa.shape(1, 2, 2, 64, 64, 64)
+    L = fa.backward_layout(fa.BF16, shp)
+    packed = c.empty_bytes(L.input_bytes)
+    grads = c.empty_bytes(L.output_bytes)
+    with pytest.raises(fa.FlatAttentionError) as e:
+        c.backward_grouped(fa.F16, shp, fa.config(True), packed, grads)
+    assert e.value.kind == "UnsupportedDtype"
+
+
+def test_f16_host_slice_forward_validates_finiteness():
+    # validate_f16_input (src/wgpu_f16_backend.rs:566-586): infinity and NaN patterns are rejected with their index
+    c = ctx()
+    B, H, N, D = 1, 2, 40, 64
+    shp = fa.shape(B, H, H, N, N, D)
+    q, k, v = fixture(B * H * N * D)
+    hq, hk, hv = (torch.from_numpy(ob.f16_from_f32(x).view(np.float16).copy()) for x in (q, k, v))
+    L = fa.forward_layout(fa.F16, shp)
+    out = torch.empty(L.combined_bytes, dtype=torch.uint8)
+    c.forward_host(fa.F16, fa.HEAD_MAJOR, shp, fa.config(True), None, hq, hk, hv, out, check_finite=True)
+    o = out[:L.q_bytes].view(torch.float16).float().numpy()
+    lse = out[L.lse_byte_offset:].view(torch.float32).numpy()
+    eo, el = ob.forward_reference(ob.f16_round(q), ob.f16_round(k), ob.f16_round(v), B, H, N, D, True)
+    assert_close("host f16 O", o, ob.f16_round(eo), O_ATOL, O_RTOL)
+    assert_close("host f16 LSE", lse, el, LSE_ATOL, LSE_RTOL)
+    hk.view(torch.int16)[5] = 0x7c00
+    with pytest.raises(fa.FlatAttentionError) as e:
+        c.forward_host(fa.F16, fa.HEAD_MAJOR, shp, fa.config(True), None, hq, hk, hv, out, check_finite=True)
+    assert e.value.kind == "NonFiniteInput" and "K" in str(e.value) and "index 5" in str(e.value)
