@@ -630,6 +630,70 @@ class CudaFlatAttention:
         return FlatAttentionOutput(o, lse.view(B, Hq, Nq))
 
 
+IO_F32, IO_PACKED_F16 = 0, 1
+EXACT_REFERENCE, FAST_PORTABLE, DETERMINISTIC_PORTABLE = 0, 1, 2
+
+
+class NumericalGuarantees(C.Structure):
+    """NumericalGuarantees (src/numerical.rs:56-66); policies are the integer codes of the C header."""
+    _fields_ = [(n, C.c_int32) for n in ("accumulation", "reduction", "softmax_update", "repeatable_same_backend_device",
+                                           "allows_subgroup")]
+
+
+def numerical_mode_guarantees(mode: int) -> NumericalGuarantees:
+    out = NumericalGuarantees()
+    st = lib().flat_numerical_mode_guarantees(C.c_int32(mode), C.byref(out))
+    if st:
+        raise FlatAttentionError(st, "unknown numerical mode")
+    return out
+
+
+def _host_f32_call(ctx, fn, shp, cfg, q, k, v, pre=(), post=()):
+    torch = _torch()
+    hq, hk, hv = (torch.as_tensor(x, dtype=torch.float32).contiguous().reshape(-1) for x in (q, k, v))
+    L = forward_layout(F32, shp)
+    out = torch.empty(L.combined_bytes // 4, dtype=torch.float32)
+    fp = lambda t: C.cast(C.c_void_p(t.data_ptr()), C.POINTER(C.c_float))
+    ctx.check(fn(ctx.h, *pre, C.byref(shp), C.byref(cfg), fp(hq), C.c_uint64(hq.numel()), fp(hk), C.c_uint64(hk.numel()),
+                 fp(hv), C.c_uint64(hv.numel()), fp(out), C.c_uint64(out.numel() * 4), *post))
+    B, H, N, D = shp.batch, shp.q_heads, shp.query_len, shp.head_dim
+    return FlatAttentionOutput(out[:L.q_elements].view(B, H, N, D), out[L.lse_byte_offset // 4:].view(B, H, N))
+
+
+class CudaPreferredAttention:
+    """WgpuPreferredAttention (src/wgpu_f16_backend.rs:474-544): routes by head_dim between binary16 and f32
+    storage; host f32 in, host f32 out; never a CPU path."""
+
+    def __init__(self, device: int = 0):
+        self.ctx = Context(device)
+        self.last_precision = None
+
+    @staticmethod
+    def io_precision_for_head_dim(head_dim: int) -> int:
+        return int(lib().flat_preferred_io_precision_for_head_dim(C.c_uint64(head_dim)))
+
+    def forward(self, q, k, v, shp: Shape, cfg: Config) -> "FlatAttentionOutput":
+        used = C.c_int32(-1)
+        out = _host_f32_call(self.ctx, lib().flat_preferred_forward_host, shp, cfg, q, k, v, post=(C.byref(used),))
+        self.last_precision = used.value
+        return out
+
+
+class NumericalExecutor:
+    """NumericalExecutor (src/numerical.rs:135-256).  ExactReference is CPU execution in the reference; this library
+    has no CPU path, so constructing it raises Unavailable."""
+
+    def __init__(self, mode: int = FAST_PORTABLE, device: int = 0):
+        self.guarantees = numerical_mode_guarantees(mode)
+        if mode == EXACT_REFERENCE:
+            raise FlatAttentionError(23, "exact-reference execution is CPU-only and is not part of this library")
+        self.mode = mode
+        self.ctx = Context(device)
+
+    def forward(self, q, k, v, shp: Shape, cfg: Config) -> "FlatAttentionOutput":
+        return _host_f32_call(self.ctx, lib().flat_numerical_forward_host, shp, cfg, q, k, v, pre=(C.c_int32(self.mode),))
+
+
 def exported_symbols_in_header() -> list[str]:
     """Names of every function the C header declares (used by the symbol-export test)."""
     import re

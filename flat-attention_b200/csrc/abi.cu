@@ -32,6 +32,17 @@ int ensure_workspace(flat_ctx *ctx, uint64_t bytes) {
     return FLAT_OK;
 }
 
+int ensure_host_stage(flat_ctx *ctx, uint64_t need) {
+    if (need <= ctx->host_stage_bytes) return FLAT_OK;
+    FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    if (ctx->host_stage) FLAT_CUDA_OK(ctx, cudaFree(ctx->host_stage));
+    ctx->host_stage = nullptr;
+    ctx->host_stage_bytes = 0;
+    FLAT_CUDA_OK(ctx, cudaMalloc(&ctx->host_stage, need));
+    ctx->host_stage_bytes = need;
+    return FLAT_OK;
+}
+
 namespace {
 
 struct Dims {
@@ -894,14 +905,7 @@ int32_t flat_forward_host(flat_ctx *ctx, int32_t dtype, int32_t layout, const fl
     auto up = [](uint64_t x) { return (x + 255) & ~uint64_t(255); };
     const uint64_t qb = up(d.q_elements * es), kb = up(d.kv_elements * es), ob = up(combined);
     const uint64_t need = qb + 2 * kb + ob;
-    if (need > ctx->host_stage_bytes) {
-        FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
-        if (ctx->host_stage) FLAT_CUDA_OK(ctx, cudaFree(ctx->host_stage));
-        ctx->host_stage = nullptr;
-        ctx->host_stage_bytes = 0;
-        FLAT_CUDA_OK(ctx, cudaMalloc(&ctx->host_stage, need));
-        ctx->host_stage_bytes = need;
-    }
+    if ((st = ensure_host_stage(ctx, need))) return st;
     char *base = static_cast<char *>(ctx->host_stage);
     flat_buffer dq{base, qb}, dk{base + qb, kb}, dv{base + qb + kb, kb}, dout{base + qb + 2 * kb, ob};
     ForwardCall c{dtype, layout, rotary != nullptr, rotary, nullptr, 0, false};

@@ -91,6 +91,8 @@ inline size_t dtype_size(int dtype) { return dtype == FLAT_F32 ? 4 : 2; }
 // Grows (never shrinks) the context scratch; synchronises the stream when it reallocates, so it
 // must be called before anything of the current call is copied into the scratch.
 int ensure_workspace(flat_ctx *ctx, uint64_t bytes);
+// Grows the device staging area of the host-slice entry points (synchronises the stream when it reallocates).
+int ensure_host_stage(flat_ctx *ctx, uint64_t bytes);
 // Scratch convention: the first kWorkspaceMeta bytes hold small host-provided tables of the
 // current call (variable-length metadata, a single-sequence page table); kernel scratch (split-KV
 // partials, rotated operands, backward accumulators) starts behind it.

@@ -512,6 +512,59 @@ int32_t flat_backward_mha(flat_ctx *ctx, int32_t dtype, const flat_attention_sha
                           const flat_attention_config *config, flat_buffer packed_inputs,
                           flat_buffer packed_grads);
 
+/* ---- precision routing and numerical modes -------------------------------------------- */
+
+/* WgpuIoPrecision (src/wgpu_f16_backend.rs:19-23). */
+typedef enum flat_io_precision { FLAT_IO_F32 = 0, FLAT_IO_PACKED_F16 = 1 } flat_io_precision;
+
+/* WgpuPreferredAttention::io_precision_for_head_dim (src/wgpu_f16_backend.rs:491-497):
+ * binary16 storage for head_dim 64 and 128, f32 otherwise. */
+int32_t flat_preferred_io_precision_for_head_dim(uint64_t head_dim);
+
+/* WgpuPreferredAttention::forward (src/wgpu_f16_backend.rs:505-544): host f32 slices of an MHA
+ * shape (q_heads == kv_heads, query_len == kv_len, head-major) in, host f32 [O | LSE] out.
+ * Qualified head dims are quantised to binary16 on the device (round to nearest even,
+ * F16::from_f32, src/f16.rs:26-82), run through the binary16 forward and expanded again; if any
+ * quantised value is not finite the call runs in f32 instead.  Never a CPU path.  Blocks.
+ * `*used_precision` (optional) receives the flat_io_precision that ran. */
+int32_t flat_preferred_forward_host(flat_ctx *ctx, const flat_attention_shape *shape,
+                                    const flat_attention_config *config, const float *q,
+                                    uint64_t q_elements, const float *k, uint64_t k_elements,
+                                    const float *v, uint64_t v_elements, float *out_and_lse,
+                                    uint64_t out_bytes, int32_t *used_precision);
+
+/* NumericalMode and NumericalGuarantees (src/numerical.rs:17-96). */
+typedef enum flat_numerical_mode {
+    FLAT_NUMERICAL_EXACT_REFERENCE = 0,
+    FLAT_NUMERICAL_FAST_PORTABLE = 1,
+    FLAT_NUMERICAL_DETERMINISTIC_PORTABLE = 2
+} flat_numerical_mode;
+typedef enum flat_accumulation_policy {
+    FLAT_ACC_SERIAL_FP32 = 0, FLAT_ACC_FIXED_TREE_FP32 = 1, FLAT_ACC_CAPABILITY_OPTIMIZED_FP32 = 2
+} flat_accumulation_policy;
+typedef enum flat_reduction_policy {
+    FLAT_RED_SERIAL_REFERENCE = 0, FLAT_RED_CAPABILITY_OPTIMIZED = 1, FLAT_RED_FIXED_WORKGROUP_TREE = 2
+} flat_reduction_policy;
+typedef struct flat_numerical_guarantees {
+    int32_t accumulation;   /* flat_accumulation_policy */
+    int32_t reduction;      /* flat_reduction_policy */
+    int32_t softmax_update; /* 0 = StableOnlineFp32, the only policy */
+    int32_t repeatable_same_backend_device;
+    int32_t allows_subgroup;
+} flat_numerical_guarantees;
+int32_t flat_numerical_mode_guarantees(int32_t mode, flat_numerical_guarantees *out);
+
+/* NumericalExecutor::forward (src/numerical.rs:154-256) for host f32 slices of an MHA shape.
+ * FAST_PORTABLE and DETERMINISTIC_PORTABLE run the f32-arithmetic generic kernel, whose
+ * reduction tree is fixed (bitwise repeatable on one device); EXACT_REFERENCE is CPU execution
+ * in the reference and is never presented as a GPU result: it returns FLAT_ERR_UNAVAILABLE
+ * here, the library has no CPU path. */
+int32_t flat_numerical_forward_host(flat_ctx *ctx, int32_t mode, const flat_attention_shape *shape,
+                                    const flat_attention_config *config, const float *q,
+                                    uint64_t q_elements, const float *k, uint64_t k_elements,
+                                    const float *v, uint64_t v_elements, float *out_and_lse,
+                                    uint64_t out_bytes);
+
 /* ---- runtime telemetry (src/runtime_telemetry.rs:10-177) ------------------------------ */
 /* Passive host-side metadata: none of these calls launches a kernel, touches the stream or
  * synchronises.  Strings are NUL-terminated UTF-8. */

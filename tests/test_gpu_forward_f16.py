@@ -124,3 +124,102 @@ def test_f16_host_slice_forward_validates_finiteness():
     with pytest.raises(fa.FlatAttentionError) as e:
         c.forward_host(fa.F16, fa.HEAD_MAJOR, shp, fa.config(True), None, hq, hk, hv, out, check_finite=True)
     assert e.value.kind == "NonFiniteInput" and "K" in str(e.value) and "index 5" in str(e.value)
+
+
+# ---- WgpuPreferredAttention (tests/wgpu_f16.rs:139-243) ----------------------------------------
+def test_preferred_router_uses_packed_f16_only_for_qualified_shapes_and_never_cpu():
+    router = fa.CudaPreferredAttention(0)
+    assert router.io_precision_for_head_dim(80) == fa.IO_F32
+    assert router.io_precision_for_head_dim(64) == fa.IO_PACKED_F16
+    assert router.io_precision_for_head_dim(128) == fa.IO_PACKED_F16
+    for D in (64, 80, 128):
+        B, H, N = 1, 1, 9
+        q, k, v = fixture(B * H * N * D)
+        got = router.forward(q, k, v, fa.shape(B, H, H, N, N, D), fa.config(True))
+        o, l = got.output.numpy().reshape(-1), got.lse.numpy().reshape(-1)
+        if router.io_precision_for_head_dim(D) == fa.IO_F32:
+            assert router.last_precision == fa.IO_F32
+            eo, el = ob.forward_reference(q, k, v, B, H, N, D, True)
+            assert_close("preferred f32 O", o, eo, 5e-5, 5e-4)
+            assert_close("preferred f32 LSE", l, el, 5e-5, 5e-4)
+        else:
+            assert router.last_precision == fa.IO_PACKED_F16
+            eo, el = ob.forward_reference(ob.f16_round(q), ob.f16_round(k), ob.f16_round(v), B, H, N, D, True)
+            assert_close("preferred packed-f16 O", o, ob.f16_round(eo), O_ATOL, O_RTOL)
+            assert_close("preferred packed-f16 LSE", l, el, LSE_ATOL, LSE_RTOL)
+
+
+def test_preferred_router_tensor_core_shape_and_overflow_route():
+    router = fa.CudaPreferredAttention(0)
+    B, H, N, D = 2, 3, 300, 128
+    g = lambda s: torch.randn(B * H * N * D, generator=torch.Generator().manual_seed(s)).numpy()
+    q, k, v = g(1), g(2), g(3)
+    got = router.forward(q, k, v, fa.shape(B, H, H, N, N, D), fa.config(True))
+    assert router.last_precision == fa.IO_PACKED_F16
+    eo, el = ob.forward_reference(ob.f16_round(q), ob.f16_round(k), ob.f16_round(v), B, H, N, D, True)
+    assert_close("router O", got.output.numpy().reshape(-1), ob.f16_round(eo), O_ATOL, O_RTOL)
+    assert_close("router LSE", got.lse.numpy().reshape(-1), el, LSE_ATOL, LSE_RTOL)
+    # a finite f32 value beyond the binary16 range: the call runs in f32 (src/wgpu_f16_backend.rs:521-528)
+    v2 = v.copy()
+    v2[7] = 1.0e5
+    got = router.forward(q, k, v2, fa.shape(B, H, H, N, N, D), fa.config(True))
+    assert router.last_precision == fa.IO_F32
+    rows = [(b, h, r) for b in range(B) for h in range(H) for r in (0, 1, 7, 150, 299)]
+    eo, el = ob.forward_rows(q, k, v2, ob._shape(B, H, H, N, N, D, 0), ob.HEAD_MAJOR, rows, True, threads=4)
+    go = np.stack([got.output.numpy()[b, h, r] for b, h, r in rows]).reshape(-1)
+    gl = np.array([got.lse.numpy()[b, h, r] for b, h, r in rows])
+    assert_close("overflow-route O", go, eo, 2e-3, 5e-4)  # rows that see the 1e5 value carry an f32 rounding of it
+    assert_close("overflow-route LSE", gl, el, 5e-5, 5e-4)
+    # non-finite f32 input is rejected before anything is quantised
+    v2[9] = np.inf
+    with pytest.raises(fa.FlatAttentionError) as e:
+        router.forward(q, k, v2, fa.shape(B, H, H, N, N, D), fa.config(True))
+    assert e.value.kind == "NonFiniteInput" and "index 9" in str(e.value)
+    with pytest.raises(fa.FlatAttentionError) as e:
+        router.forward(q, k[:-1], v, fa.shape(B, H, H, N, N, D), fa.config(True))
+    assert e.value.kind == "LengthMismatch"
+
+
+# ---- NumericalExecutor (tests/numerical_policy.rs, tests/wgpu_numerical_policy.rs) ------------------
+def numerical_fixture(n):
+    # tests/wgpu_numerical_policy.rs:26-43
+    i = np.arange(n)
+    f = i.astype(np.float32)
+    q = np.where(i % 3 == 0, -1.0, 1.0).astype(np.float32) * (np.sin(f * np.float32(0.027), dtype=np.float32) * np.float32(3.5) + np.float32(0.125))
+    k = np.where((i // 5) % 2 == 0, 1.0, -1.0).astype(np.float32) * (np.cos(f * np.float32(0.019), dtype=np.float32) * np.float32(2.75) - np.float32(0.0625))
+    v = np.sin(f * np.float32(0.013), dtype=np.float32) * np.float32(4.0)
+    return q, k, v
+
+
+def test_mode_guarantees_are_explicit():
+    # src/numerical.rs:283-311
+    exact, fast, det = (fa.numerical_mode_guarantees(m) for m in (fa.EXACT_REFERENCE, fa.FAST_PORTABLE, fa.DETERMINISTIC_PORTABLE))
+    assert (exact.accumulation, exact.reduction, exact.repeatable_same_backend_device, exact.allows_subgroup) == (0, 0, 1, 0)
+    assert (fast.accumulation, fast.reduction, fast.repeatable_same_backend_device, fast.allows_subgroup) == (2, 1, 0, 1)
+    assert (det.accumulation, det.reduction, det.repeatable_same_backend_device, det.allows_subgroup) == (1, 2, 1, 0)
+    with pytest.raises(fa.FlatAttentionError) as e:
+        fa.NumericalExecutor(fa.EXACT_REFERENCE)  # reference execution is never presented as a GPU result
+    assert e.value.kind == "Unavailable"
+
+
+def test_deterministic_mode_is_bit_repeatable_and_matches_reference():
+    # tests/wgpu_numerical_policy.rs:88-128
+    ex = fa.NumericalExecutor(fa.DETERMINISTIC_PORTABLE)
+    for N, D in [(17, 64), (33, 80), (9, 128)]:
+        q, k, v = numerical_fixture(2 * N * D)
+        for causal in (False, True):
+            shp, cfg = fa.shape(1, 2, 2, N, N, D), fa.config(causal, 0.125)
+            first = ex.forward(q, k, v, shp, cfg)
+            for _ in range(4):
+                again = ex.forward(q, k, v, shp, cfg)
+                assert torch.equal(again.output.view(torch.int32), first.output.view(torch.int32))
+                assert torch.equal(again.lse.view(torch.int32), first.lse.view(torch.int32))
+            eo, el = ob.forward_reference(q, k, v, 1, 2, N, D, causal, 0.125)
+            assert_close("deterministic O", first.output.numpy().reshape(-1), eo, 5e-5, 5e-4)
+            assert_close("deterministic LSE", first.lse.numpy().reshape(-1), el, 5e-5, 5e-4)
+    fast = fa.NumericalExecutor(fa.FAST_PORTABLE)
+    q, k, v = numerical_fixture(17 * 64)
+    got = fast.forward(q, k, v, fa.shape(1, 1, 1, 17, 17, 64), fa.config(True))
+    eo, el = ob.forward_reference(q, k, v, 1, 1, 17, 64, True)
+    assert_close("fast O", got.output.numpy().reshape(-1), eo, 5e-5, 5e-4)
+    assert_close("fast LSE", got.lse.numpy().reshape(-1), el, 5e-5, 5e-4)
