@@ -34,7 +34,7 @@ class Error : public std::runtime_error {
 };
 
 using DeviceBuffer = flat_buffer;
-enum class DType : int32_t { F32 = FLAT_F32, BF16 = FLAT_BF16 };
+enum class DType : int32_t { F32 = FLAT_F32, BF16 = FLAT_BF16, F16 = FLAT_F16 };
 
 // AttentionShape / GroupedAttentionShape / AsymmetricGroupedAttentionShape (src/lib.rs:211-245,
 // src/grouped.rs:17-75, src/asymmetric_grouped.rs:26-35) in their api::v1 form (src/api.rs:24-33).
@@ -237,6 +237,56 @@ class CudaExternalVariableProjectionRotaryGroupedPipeline {
   private:
     const Context &ctx_;
     DType dtype_;
+};
+
+// WgpuPreferredAttention (src/wgpu_f16_backend.rs:474-544): binary16 storage for head_dim 64 / 128, f32 otherwise.
+class CudaPreferredAttention {
+  public:
+    explicit CudaPreferredAttention(const Context &ctx) : ctx_(ctx) {}
+    static flat_io_precision io_precision_for_head_dim(uint64_t head_dim) {
+        return static_cast<flat_io_precision>(flat_preferred_io_precision_for_head_dim(head_dim));
+    }
+    // host f32 slices in, packed host f32 [O | LSE] out; returns the precision that ran
+    flat_io_precision forward(const std::vector<float> &q, const std::vector<float> &k, const std::vector<float> &v,
+                              const AttentionShape &shape, const FlatAttentionConfig &config, std::vector<float> &out_and_lse) const {
+        auto cfg = config.raw();
+        const auto layout = forward_layout(DType::F32, shape);
+        out_and_lse.resize(layout.combined_bytes / 4);
+        int32_t used = FLAT_IO_F32;
+        ctx_.check(flat_preferred_forward_host(ctx_.raw(), &shape, &cfg, q.data(), q.size(), k.data(), k.size(), v.data(), v.size(),
+                                               out_and_lse.data(), out_and_lse.size() * 4, &used));
+        return static_cast<flat_io_precision>(used);
+    }
+
+  private:
+    const Context &ctx_;
+};
+
+// NumericalExecutor (src/numerical.rs:135-256).  ExactReference is CPU execution in the reference: Error(Unavailable) here.
+class NumericalExecutor {
+  public:
+    NumericalExecutor(const Context &ctx, flat_numerical_mode mode) : ctx_(ctx), mode_(mode) {
+        if (mode == FLAT_NUMERICAL_EXACT_REFERENCE) throw Error(FLAT_ERR_UNAVAILABLE, "exact-reference execution is CPU-only");
+    }
+    static flat_numerical_guarantees guarantees(flat_numerical_mode mode) {
+        flat_numerical_guarantees g{};
+        int32_t st = flat_numerical_mode_guarantees(mode, &g);
+        if (st) throw Error(st, "");
+        return g;
+    }
+    flat_numerical_mode mode() const { return mode_; }
+    void forward(const std::vector<float> &q, const std::vector<float> &k, const std::vector<float> &v, const AttentionShape &shape,
+                 const FlatAttentionConfig &config, std::vector<float> &out_and_lse) const {
+        auto cfg = config.raw();
+        const auto layout = forward_layout(DType::F32, shape);
+        out_and_lse.resize(layout.combined_bytes / 4);
+        ctx_.check(flat_numerical_forward_host(ctx_.raw(), mode_, &shape, &cfg, q.data(), q.size(), k.data(), k.size(), v.data(),
+                                               v.size(), out_and_lse.data(), out_and_lse.size() * 4));
+    }
+
+  private:
+    const Context &ctx_;
+    flat_numerical_mode mode_;
 };
 
 // PagedKvTable (src/paged_kv.rs:75-188).

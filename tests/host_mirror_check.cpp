@@ -65,6 +65,12 @@ int main() {
         threw = e.status() == FLAT_ERR_MANIFEST_INVALID_COMMIT_SHA;
     }
     CHECK(threw);
+    // routing table and numerical guarantees are pure (src/wgpu_f16_backend.rs:491-497, src/numerical.rs:68-96)
+    CHECK(CudaPreferredAttention::io_precision_for_head_dim(64) == FLAT_IO_PACKED_F16);
+    CHECK(CudaPreferredAttention::io_precision_for_head_dim(80) == FLAT_IO_F32);
+    CHECK(NumericalExecutor::guarantees(FLAT_NUMERICAL_DETERMINISTIC_PORTABLE).repeatable_same_backend_device == 1);
+    CHECK(NumericalExecutor::guarantees(FLAT_NUMERICAL_FAST_PORTABLE).allows_subgroup == 1);
+    CHECK(forward_layout(DType::F16, shape).q_bytes == 2 * L.q_elements);
     // without an sm_100 device a context cannot be created, and nothing falls back to the CPU
     if (std::getenv("FLAT_EXPECT_NO_DEVICE")) {
         threw = false;
