@@ -167,7 +167,9 @@ def test_passive_snapshot_matches_selected_dispatch():
     assert t.kernel == "ForwardGeneric" and t.fallback_reason == "tensor-core specialization unavailable for head_dim=32"
     assert (t.query_rows, t.kv_rows, list(t.workgroups)) == (32, 32, [1, 1, 1]) and t.dispatch_count == 1
     t = tel.forward_runtime_telemetry(c, fa.F32, fa.PROJECTION, fa.shape(2, 3, 3, 17, 17, 64))
-    assert t.kernel == "ForwardGeneric" and list(t.workgroups) == [1, 3, 2] and "bf16" in t.fallback_reason
+    assert t.kernel == "ForwardGeneric" and list(t.workgroups) == [1, 3, 2] and "16-bit storage" in t.fallback_reason
     with pytest.raises(fa.FlatAttentionError) as e:
         tel.forward_runtime_telemetry(c, fa.BF16, fa.HEAD_MAJOR, fa.shape(1, 3, 2, 5, 5, 32))
     assert e.value.kind == "InvalidHeadGrouping"
+    t = tel.forward_runtime_telemetry(c, fa.F16, fa.HEAD_MAJOR, fa.shape(1, 4, 2, 512, 512, 64))
+    assert t.kernel == "ForwardTcgen05" and list(t.workgroups) == [8, 1, 1] and t.dispatch_count == 1
