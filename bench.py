@@ -364,6 +364,54 @@ def bench_backward(torch, fa, ctx, peaks, steps, warmup):
                          "note": "7 GEMM units are executed for 5 algorithmic ones (scores recomputed in both kernels)"}}
 
 
+def bench_prefill_variants(torch, fa, ctx, peaks, steps, warmup):
+    """The C2 prefill shape through the two widened modes of the forward: the ALiBi score bias on the rectangular
+    projection entry point (bf16) and IEEE binary16 storage (GQA + RoPE, head-major).  Same flops as the headline."""
+    c = C2
+    B, Hq, Hkv, N, D, theta = c["B"], c["Hq"], c["Hkv"], c["N"], c["D"], c["theta"]
+    shp, cfg, rot = fa.shape(B, Hq, Hkv, N, N, D), fa.config(True), fa.rotary(theta, 0)
+    flops = prefill_flops(c)
+    peak = peaks["bf16_tflops"]
+    results = {}
+
+    def timed(name, kernel, fn, note):
+        for _ in range(warmup):
+            fn()
+        ctx.set_kernel_timing(True)
+        ctx.take_kernel_time()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        kms, kn = ctx.take_kernel_time()
+        ctx.set_kernel_timing(False)
+        kms /= max(kn, 1)
+        results[name] = {"value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms, "workload": note,
+                         "roofline": {"bound": "tensor", "achieved": flops / (kms * 1e-3) / 1e12, "peak": peak, "unit": "TFLOP/s",
+                                      "frac": flops / (kms * 1e-3) / 1e12 / peak, "traffic": None, "kernel": kernel,
+                                      "kernel_ms": kms, "peak_source": peaks["source"] + " (burst cuBLAS bf16)"}}
+
+    g = torch.Generator(device="cuda").manual_seed(21)
+    q = torch.randn(B, N, Hq, D, generator=g, device="cuda").bfloat16()
+    k = torch.randn(B, N, Hkv, D, generator=g, device="cuda").bfloat16()
+    v = torch.randn(B, N, Hkv, D, generator=g, device="cuda").bfloat16()
+    out = ctx.create_output_buffer(fa.BF16, shp)
+    slopes = [2.0 ** -(8.0 * (h + 1) / Hq) for h in range(Hq)]
+    timed("alibi", "fwd_sm100_kernel<128,false,ALIBI>",
+          lambda: ctx.forward_projection_rope_asymmetric_alibi(fa.BF16, shp, cfg, rot, slopes, 0, 0, q, k, v, out),
+          "C2 shape, projection layout, bf16, RoPE + ALiBi (slopes 2^(-8(h+1)/Hq))")
+    q16, k16, v16 = (x.transpose(1, 2).contiguous().half() for x in (q, k, v))
+    out16 = ctx.create_output_buffer(fa.F16, shp)
+    timed("binary16", "fwd_sm100_kernel<128,false,false,F16IO>",
+          lambda: ctx.forward_grouped_rope(fa.F16, shp, cfg, rot, q16, k16, v16, out16),
+          "C2 shape, head-major, IEEE binary16 storage, RoPE")
+    return results
+
+
 def bench_chunked_prefill(torch, fa, ctx, peaks, warmup):
     """Config 4 (prefill part): one 32768-token sequence fed in 2048-token chunks into a growing paged cache."""
     Hq, Hkv, D, N, chunk, ps, theta = 64, 8, 128, 32768, 2048, 16, 500000.0
@@ -591,6 +639,7 @@ def main():
             line["decode"] = bench_decode(torch, np, fa, ctx, peaks, max(5, min(args.steps, 20)), args.warmup)
             line["backward"] = bench_backward(torch, fa, ctx, peaks, max(3, min(args.steps, 10)), args.warmup)
             line["chunked_prefill"] = bench_chunked_prefill(torch, fa, ctx, peaks, args.warmup)
+            line["prefill_variants"] = bench_prefill_variants(torch, fa, ctx, peaks, max(5, min(args.steps, 20)), args.warmup)
     if world > 1 and not args.skip_extras:
         extra = bench_splitkv_128k(torch, np, dist, fa, ctx, rank, world, max(5, min(args.steps, 20)), args.warmup)
         line["splitkv_decode_128k"] = extra
