@@ -507,6 +507,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-extras", action="store_true", help="only the headline prefill workload")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle legs (parity gate, cpu_baseline): for profiler runs")
+    ap.add_argument("--variants-only", action="store_true", help="run only the ALiBi / binary16 prefill variants (N=1): "
+                                                                "a short command for profiler captures")
     ap.add_argument("--manifest", default=None, help="write a schema-1 canonical-JSON benchmark manifest of the headline "
                                                      "workload to this path (rank 0)")
     ap.add_argument("--commit-sha", default=None, help="40-hex source revision recorded in the manifest "
@@ -537,6 +539,11 @@ def main():
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     peaks = load_peaks()
     ctx = fa.Context(local_rank)
+    if args.variants_only:
+        if rank == 0:
+            print(json.dumps({"prefill_variants": bench_prefill_variants(torch, fa, ctx, peaks, max(1, args.steps), args.warmup)}),
+                  flush=True)
+        return
     c = C2
     B, Hq, Hkv, N, D, theta = c["B"], c["Hq"], c["Hkv"], c["N"], c["D"], c["theta"]
     shp = fa.shape(B, Hq, Hkv, N, N, D)
