@@ -119,3 +119,64 @@ def test_null_context_is_an_error_not_a_crash():
     assert lib.flat_synchronize(None) == 27
     assert lib.flat_forward_host(None, C.c_int32(0), C.c_int32(0), C.byref(shp), C.byref(cfg), None, None, C.c_uint64(0), None,
                                  C.c_uint64(0), None, C.c_uint64(0), C.c_int32(1), None, C.c_uint64(0)) == 27
+    assert lib.flat_forward_projection_rope_asymmetric_alibi(None, C.c_int32(1), C.byref(shp), C.byref(cfg), None, None,
+                                                             C.c_uint64(0), C.c_uint64(0), C.c_uint64(0), z, z, z, z) == 27
+    assert lib.flat_forward_runtime_telemetry(None, C.c_int32(1), C.c_int32(0), C.byref(shp), None, None) == 27
+    assert lib.flat_preferred_forward_host(None, C.byref(shp), C.byref(cfg), None, C.c_uint64(0), None, C.c_uint64(0), None,
+                                           C.c_uint64(0), None, C.c_uint64(0), None) == 27
+    assert lib.flat_numerical_forward_host(None, C.c_int32(1), C.byref(shp), C.byref(cfg), None, C.c_uint64(0), None,
+                                           C.c_uint64(0), None, C.c_uint64(0), None, C.c_uint64(0)) == 27
+    assert lib.flat_ctx_device_fingerprint(None, None) == 27 and lib.flat_ctx_device_capabilities(None, None) == 27
+    assert lib.flat_benchmark_manifest_validate(None, None) == 27
+    lib.flat_benchmark_manifest_canonical_json.restype = C.c_int64
+    assert lib.flat_benchmark_manifest_canonical_json(None, None, C.c_uint64(0)) == -27
+    lib.flat_device_fingerprint_canonical_record.restype = C.c_int64
+    assert lib.flat_device_fingerprint_canonical_record(None, None, C.c_uint64(0)) == -27
+
+
+def test_manifest_and_record_fuzz_matches_the_restatement():
+    """Random byte soup (valid UTF-8, control characters, delimiters, quotes) through the canonical-record and
+    canonical-JSON writers: library and restatement agree byte for byte, small buffers truncate without overrun."""
+    import dataclasses
+    import importlib
+    from oracle import telemetry_oracle as to
+    tel = importlib.import_module("flat_attention_b200.telemetry")
+    rng = XorShift(0x9E3779B97F4A7C15)
+    alphabet = ['"', "\\", "\n", "\r", "\t", "\x01", "\x1f", ";", "=", "%", " ", "a", "Z", "é", "漢", "😀", " ", "\xa0", "7"]
+
+    def text(max_len):
+        return "".join(alphabet[rng.next() % len(alphabet)] for _ in range(rng.next() % max_len))
+
+    for _ in range(300):
+        name, backend, driver, info = text(40), text(12), text(20), text(30)
+        vendor, device = rng.next() & 0xffffffff, rng.next() & 0xffffffff
+        fp = tel.fingerprint(name, backend, driver, info, vendor, device)
+        # the struct fields are NUL-terminated fixed arrays: the restatement sees the same truncation
+        cut = lambda s, cap: s.encode()[:cap].decode(errors="ignore") if len(s.encode()) >= cap else s
+        if any(len(s.encode()) >= cap for s, cap in ((name, 256), (backend, 32), (driver, 64), (info, 128))):
+            continue
+        expect = to.fingerprint_record(name, backend, driver, info, vendor, device)
+        assert tel.fingerprint_canonical_record(fp) == expect
+        assert tel.fingerprint_stable(fp) == to.fnv1a64(expect.encode())
+        m = tel.BenchmarkManifest(
+            commit_sha="%040x" % (rng.next() << 64 | rng.next()), benchmark_id="b" + text(10), command="c" + text(60),
+            device="d" + text(20), backend="x" + text(5), driver="r" + text(9), os="o" + text(4), arch="a" + text(4),
+            precision="p" + text(4), batch=1 + rng.next() % 9, q_heads=8, kv_heads=1 + rng.next() % 2 * 3, query_len=1 + rng.next() % 99,
+            kv_len=1 + rng.next() % 99, head_dim=64, causal=bool(rng.next() & 1), warmup_iterations=rng.next() % 9,
+            measured_iterations=rng.next() % 5, median_latency_ns=rng.next() >> 20, p95_latency_ns=rng.next() >> 20,
+            tokens_per_second_milli=rng.next())
+        want = to.validate(dataclasses.asdict(m))
+        if want is None:
+            assert m.canonical_json() == to.canonical_json(dataclasses.asdict(m))
+        else:
+            try:
+                m.canonical_json()
+                raise AssertionError("expected " + want[0])
+            except fa.FlatAttentionError as e:
+                assert e.kind.replace("Manifest", "") == want[0]
+    # snprintf convention: a short buffer receives a NUL-terminated prefix and the call still reports the full length
+    fp = tel.fingerprint("abc", "Cuda", "d", "i", 1, 2)
+    lib = fa.lib()
+    buf = C.create_string_buffer(b"\xff" * 16, 16)
+    full = lib.flat_device_fingerprint_canonical_record(C.byref(fp), buf, C.c_uint64(8))
+    assert full == len(to.fingerprint_record("abc", "Cuda", "d", "i", 1, 2)) and buf.raw[:8] == b"name=ab\x00" and buf.raw[8:] == b"\xff" * 8
