@@ -485,7 +485,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                 }
                 // ALiBi is added to the raw score as (slope / scale) * position difference, so that the scaling of the
                 // softmax passes covers it.  Positions stay below 2^24 in magnitude (checked on the host): the float
-                // position arithmetic is exact and each bias is rounded once, inside the FMA.
+                // position arithmetic is exact.
                 float slope_rel = 0.f, bias_pos0 = 0.f;
                 if constexpr (ALIBI) {
                     slope_rel = __ldg(p.alibi_slopes + it.h) * p.alibi_inv_scale;
@@ -516,21 +516,13 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, r + c * 32);
                     tc_wait_ld();
                     if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(1);
+                    float bias_base = 0.f;  // tile-constant part of the bias, folded into the max and the exponent below
                     if constexpr (ALIBI) {
-                        // r[i] <- s_i + (slope / c) * (position difference of column i): the passes below scale by c
-                        uint64_t pos2, two2, sl2;
-                        const float x0 = bias_pos0 + (float)key0;
-                        asm("mov.b64 %0, {%1, %2};" : "=l"(pos2) : "f"(x0), "f"(x0 + 1.0f));
-                        asm("mov.b64 %0, {%1, %1};" : "=l"(two2) : "f"(2.0f));
-                        asm("mov.b64 %0, {%1, %1};" : "=l"(sl2) : "f"(slope_rel));
+                        // r[i] <- s_i + (slope / c) * i: one FFMA with an immediate per score.  The rest of the bias,
+                        // (slope / c) * (position difference of column 0), is the same for the whole tile row.
 #pragma unroll
-                        for (int i = 0; i < 128; i += 2) {
-                            uint64_t s2;
-                            asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(r[i]), "r"(r[i + 1]));
-                            asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(s2) : "l"(pos2), "l"(sl2));
-                            asm("mov.b64 {%0, %1}, %2;" : "=r"(r[i]), "=r"(r[i + 1]) : "l"(s2));
-                            asm("add.rn.f32x2 %0, %0, %1;" : "+l"(pos2) : "l"(two2));
-                        }
+                        for (int i = 0; i < 128; ++i) r[i] = __float_as_uint(fmaf(slope_rel, (float)i, __uint_as_float(r[i])));
+                        bias_base = slope_rel * (bias_pos0 + (float)key0);
                     }
                     if (tile_masked) {
 #pragma unroll
@@ -543,7 +535,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                         asm("max.f32 %0, %0, %1, %2;" : "+f"(mx) : "f"(__uint_as_float(r[i])), "f"(__uint_as_float(r[i + 1])));
                         asm("max.f32 %0, %0, %1, %2;" : "+f"(mx1) : "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3])));
                     }
-                    const float m_cand = fmaxf(m, fmaxf(mx, mx1) * c_log2);
+                    const float m_cand = fmaxf(m, (fmaxf(mx, mx1) + bias_base) * c_log2);
                     const bool grow = (m_cand - m) > kRescaleThreshold;
                     float alpha = 1.0f;
                     if (grow) {
@@ -566,7 +558,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     // P = exp2(S*c - m) as bf16, written over S; two scores per packed f32x2 FMA
                     uint64_t c2, nm2, sum2 = 0, sum3 = 0;
                     {
-                        const float neg_m = -m;
+                        const float neg_m = fmaf(bias_base, c_log2, -m);
                         asm("mov.b64 %0, {%1, %1};" : "=l"(nm2) : "f"(neg_m));
                         asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(c_log2));
                     }
