@@ -179,3 +179,43 @@ def test_alibi_validation_errors():
         call([0.0] * 257, s=big)
     assert e.value.kind == "IndexSpaceExceeded"
     assert c.device_status() == 0
+
+
+def test_random_shapes_alibi_tensor_core_against_f32_path():
+    """Differential sweep: the ALIBI instantiation of the tcgen05 kernel (bf16) against the generic f32 kernel (pinned to
+    the oracle above) on the same bf16-rounded inputs: ragged and rectangular lengths, causal offsets, bias origins on
+    either side of each other, negative slopes, both head dims, rotated and pre-rotated K."""
+    rng = np.random.default_rng(1312)
+    c = ctx()
+    for case in range(16):
+        D = int(rng.choice([64, 128]))
+        Hkv = int(rng.choice([1, 2, 4]))
+        Hq = Hkv * int(rng.choice([1, 2, 4]))
+        B = int(rng.integers(1, 3))
+        Nq = int(rng.integers(32, 600))
+        extra = int(rng.integers(0, 400))
+        Nkv = Nq + extra
+        causal = bool(rng.integers(0, 2))
+        coff = extra if causal else 0
+        qr, kr = int(rng.integers(0, 5000)), int(rng.integers(0, 5000))
+        bq, bk = int(rng.integers(0, 100000)), int(rng.integers(0, 100000))
+        if causal:
+            bq = bk + extra  # the usual convention: bias positions are the causal positions
+        rotate_k = bool(rng.integers(0, 2))
+        slopes = [float(s) for s in rng.choice([-1.0, 1.0], Hq) * 2.0 ** -rng.integers(3, 9, Hq)]
+        if not causal:
+            slopes = [s * 2.0 ** -4 for s in slopes]  # keep the LSE magnitude inside the absolute 2e-3 budget
+        g = lambda n, s: bf16_round(torch.randn(n, generator=torch.Generator().manual_seed(s)).numpy())
+        q, k, v = g(B * Nq * Hq * D, 100 + case), g(B * Nkv * Hkv * D, 200 + case), g(B * Nkv * Hkv * D, 300 + case)
+        if not rotate_k:
+            kpos = np.repeat(np.tile(np.arange(Nkv, dtype=np.uint64) + kr, B), Hkv)
+            k = bf16_round(ob.rotate_rows(k, D, kpos, 5e5))
+        shp, cfg, rot = fa.shape(B, Hq, Hkv, Nq, Nkv, D, coff), fa.config(causal), fa.rotary(5e5, qr, kr, rotate_k=rotate_k)
+        what = f"case {case}: B={B} Hq={Hq} Hkv={Hkv} Nq={Nq} Nkv={Nkv} D={D} causal={causal} rotate_k={rotate_k} bq={bq} bk={bk}"
+        o, l, launches = run_alibi(fa.BF16, shp, cfg, rot, slopes, bq, bk, q, k, v)
+        eo, el, one = run_alibi(fa.F32, shp, cfg, rot, slopes, bq, bk, q, k, v)
+        assert one == 1 and launches >= 2, what
+        assert np.isfinite(o).all() and np.isfinite(l).all(), what
+        assert np.abs(o - eo).max() <= 2e-2, (what, float(np.abs(o - eo).max()))
+        assert np.abs(l - el).max() <= 2e-3 + 2e-5 * np.abs(el).max(), (what, float(np.abs(l - el).max()))
+        assert c.device_status() == 0, what

@@ -223,3 +223,48 @@ def test_deterministic_mode_is_bit_repeatable_and_matches_reference():
     eo, el = ob.forward_reference(q, k, v, 1, 1, 17, 64, True)
     assert_close("fast O", got.output.numpy().reshape(-1), eo, 5e-5, 5e-4)
     assert_close("fast LSE", got.lse.numpy().reshape(-1), el, 5e-5, 5e-4)
+
+
+def test_random_shapes_f16_tensor_core_against_f32_path():
+    """Differential sweep: the binary16 instantiation of the tcgen05 kernel against the generic f32 kernel on the same
+    binary16-rounded inputs: ragged and rectangular lengths, causal offsets, RoPE offsets, both head dims, raw and
+    pre-rotated K, and padded variable-length batches."""
+    from tests.gpu_util import run_forward
+    rng = np.random.default_rng(1606)
+    for case in range(16):
+        D = int(rng.choice([64, 128]))
+        Hkv = int(rng.choice([1, 2, 4]))
+        Hq = Hkv * int(rng.choice([1, 2, 4]))
+        B = int(rng.integers(1, 4))
+        Nq = int(rng.integers(32, 600))
+        extra = int(rng.integers(0, 400))
+        Nkv = Nq + extra
+        causal = bool(rng.integers(0, 2))
+        coff = extra if causal else 0
+        qr, kr = int(rng.integers(0, 5000)), int(rng.integers(0, 5000))
+        rotate_k = bool(rng.integers(0, 2))
+        varlen = case % 4 == 3
+        g = lambda n, s: ob.f16_round(torch.randn(n, generator=torch.Generator().manual_seed(s)).numpy())
+        q, k, v = g(B * Nq * Hq * D, 100 + case), g(B * Nkv * Hkv * D, 200 + case), g(B * Nkv * Hkv * D, 300 + case)
+        if not rotate_k:
+            kpos = np.repeat(np.tile(np.arange(Nkv, dtype=np.uint64) + kr, B), Hkv)
+            k = ob.f16_round(ob.rotate_rows(k, D, kpos, 5e5))
+        shp, cfg, rot = fa.shape(B, Hq, Hkv, Nq, Nkv, D, coff), fa.config(causal), fa.rotary(5e5, qr, kr, rotate_k=rotate_k)
+        what = f"case {case}: B={B} Hq={Hq} Hkv={Hkv} Nq={Nq} Nkv={Nkv} D={D} causal={causal} rotate_k={rotate_k} varlen={varlen}"
+        kind, kw = "projection_rope_asymmetric", {}
+        if varlen:
+            seqs = []
+            for b in range(B):
+                aq = int(rng.integers(1, Nq + 1))
+                akv = int(rng.integers(aq, Nkv + 1))
+                seqs.append(fa.VarlenSequence(aq, akv, akv - aq, int(rng.integers(0, 3000))))
+            kind, kw = "projection_rope_varlen", {"sequences": seqs}
+            shp = fa.shape(B, Hq, Hkv, Nq, Nkv, D, 0)
+        # run_forward converts the (already binary16-exact) host values to the storage type of each route
+        o, l = run_forward(kind, fa.F16, shp, cfg, q, k, v, rot=rot, **kw)
+        eo, el = run_forward(kind, fa.F32, shp, cfg, q, k, v, rot=rot, **kw)
+        live = np.isfinite(el)
+        assert np.array_equal(np.isfinite(l), live), what  # padded rows: LSE = -inf on both routes
+        assert_close("sweep O " + what, o, ob.f16_round(eo), O_ATOL, O_RTOL)
+        assert_close("sweep LSE " + what, l[live], el[live], LSE_ATOL, LSE_RTOL)
+        assert ctx().device_status() == 0, what
