@@ -1,6 +1,6 @@
 """Resident / paged KV caches and q_len = 1 decode against the CPU oracle (f32 and bf16):
 tests/m14_resident_kv_cache.rs, m15_growing_cache.rs, m15_external_resident.rs, m16_paged_decode.rs,
-m16_paged_kv_cache.rs, plus the batched paged decode of BASELINE config 3 (reduced and full size)."""
+m16_paged_kv_cache.rs, plus the batched paged decode of benchmark configuration 3 (reduced and full size)."""
 import numpy as np
 import pytest
 import torch
@@ -214,7 +214,7 @@ def test_paged_decode_shapes_outside_the_streaming_kernel(Hq, Hkv, D):
     assert_close("LSE", l, el, *TOL)
 
 
-# ---- batched paged decode (BASELINE config 3) -------------------------------------------------
+# ---- batched paged decode (benchmark configuration 3) -------------------------------------------------
 def make_paged_batch(num_seqs, Hq, Hkv, D, ps, lo, hi, dtype, seed=5):
     rng = np.random.default_rng(seed)
     lens = (lo + rng.integers(0, hi - lo + 1, num_seqs)).astype(np.int32)

@@ -1,6 +1,6 @@
 """f32 parity of the CUDA forward path against the CPU oracle, on the reference's GPU-test shape
 inventory (tests/wgpu_device.rs, wgpu_matrix.rs, wgpu_grouped.rs, wgpu_rotary_grouped.rs,
-wgpu_external*.rs) and on BASELINE config 1.  north_star tolerance for the f32 mode: 1e-4."""
+wgpu_external*.rs) and on benchmark configuration 1.  The required tolerance for the f32 mode: 1e-4."""
 import numpy as np
 import pytest
 import torch
