@@ -91,6 +91,12 @@ class ForwardLayout(C.Structure):
                                             "lse_byte_offset", "combined_bytes")]
 
 
+class DecodeLayout(C.Structure):
+    """ResidentDecodeLayout / PagedDecodeLayout (src/wgpu_decode.rs:437-455, src/wgpu_paged_decode.rs:221-235)."""
+    _fields_ = [(n, C.c_uint64) for n in ("q_elements", "output_elements", "lse_elements", "combined_elements", "q_bytes",
+                                            "lse_byte_offset", "combined_bytes")]
+
+
 class VarlenSequence(C.Structure):
     """VariableLengthSequenceMetadata (src/wgpu_external_variable.rs:21-33)."""
     _fields_ = [(n, C.c_uint32) for n in ("active_query_len", "active_kv_len", "causal_query_offset",
@@ -179,6 +185,16 @@ def forward_layout(dtype: int, shp: Shape) -> ForwardLayout:
     return out
 
 
+def decode_layout(dtype: int, batch: int, q_heads: int, head_dim: int) -> DecodeLayout:
+    """*DecodePipeline::layout: offsets of the packed decode output [O | LSE] for `batch` decoded rows."""
+    out = DecodeLayout()
+    st = lib().flat_decode_layout_for(C.c_int32(dtype), C.c_uint64(batch), C.c_uint64(q_heads), C.c_uint64(head_dim),
+                                      C.byref(out))
+    if st:
+        raise FlatAttentionError(st, lib().flat_status_str(st).decode())
+    return out
+
+
 def backward_layout(dtype: int, shp: Shape) -> BackwardLayout:
     out = BackwardLayout()
     st = lib().flat_backward_layout_for(C.c_int32(dtype), C.byref(shp), C.byref(out))
@@ -258,6 +274,18 @@ class Context:
     def create_output_buffer(self, dtype: int, shp: Shape):
         return self.empty_bytes(forward_layout(dtype, shp).combined_bytes)
 
+    def create_decode_output_buffer(self, dtype: int, batch: int, q_heads: int, head_dim: int):
+        """*DecodePipeline::create_output_buffer (src/wgpu_paged_decode.rs:285-298)."""
+        return self.empty_bytes(decode_layout(dtype, batch, q_heads, head_dim).combined_bytes)
+
+    def split_decode_output(self, out_and_lse, dtype: int, batch: int, q_heads: int, head_dim: int):
+        """Views of a packed decode output: (O [batch, q_heads, head_dim], LSE [batch, q_heads] f32)."""
+        L = decode_layout(dtype, batch, q_heads, head_dim)
+        raw = out_and_lse.view(_torch().uint8).reshape(-1)
+        o = raw[:L.q_bytes].view(torch_dtype(dtype)).view(batch, q_heads, head_dim)
+        lse = raw[L.lse_byte_offset:L.lse_byte_offset + 4 * L.lse_elements].view(_torch().float32).view(batch, q_heads)
+        return o, lse
+
     def split_output(self, out_and_lse, dtype: int, shp: Shape, layout: int = HEAD_MAJOR):
         """Views of the packed [O | LSE] buffer: (O in its layout, LSE [B, Hq, Nq] f32)."""
         L = forward_layout(dtype, shp)
@@ -310,8 +338,10 @@ class Context:
                                                              C.byref(rot), arr, C.c_uint64(len(sequences)), buf(q),
                                                              buf(k), buf(v), buf(out)))
 
-    def forward_host(self, dtype, layout, shp, cfg, rot, q, k, v, out, check_finite=False):
-        """Host tensors in (torch CPU, ideally pinned), host packed [O | LSE] out; blocks."""
+    def forward_host(self, dtype, layout, shp, cfg, rot, q, k, v, out, check_finite=True):
+        """Host tensors in (torch CPU, ideally pinned), host packed [O | LSE] out; blocks.  Like the reference's
+        `forward`, the call rejects non-finite Q/K/V (validate_input, src/lib.rs:428-447); the scan runs on the
+        device as the chunks land.  check_finite=False skips it."""
         self.check(lib().flat_forward_host(self.h, C.c_int32(dtype), C.c_int32(layout), C.byref(shp), C.byref(cfg),
                                            C.byref(rot) if rot is not None else None, C.c_void_p(q.data_ptr()),
                                            C.c_uint64(q.numel()), C.c_void_p(k.data_ptr()), C.c_uint64(k.numel()),

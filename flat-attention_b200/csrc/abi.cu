@@ -26,6 +26,7 @@ int ensure_workspace(flat_ctx *ctx, uint64_t bytes) {
     if (ctx->workspace) FLAT_CUDA_OK(ctx, cudaFree(ctx->workspace));
     ctx->workspace = nullptr;
     ctx->workspace_bytes = 0;
+    ctx->plan_offsets_at = nullptr;  // whatever the old allocation held is gone
     uint64_t rounded = (bytes + 255) & ~uint64_t(255);
     FLAT_CUDA_OK(ctx, cudaMalloc(&ctx->workspace, rounded));
     ctx->workspace_bytes = rounded;
@@ -272,6 +273,7 @@ int forward_common(flat_ctx *ctx, const ForwardCall &call, const flat_attention_
         p.varlen = reinterpret_cast<const flat_varlen_sequence *>(call.varlen_host);  // non-null for the capability test
         const bool tensor_path = storage16(call.dtype) && forward_sm100_supported(p);
         if ((st = ensure_workspace(ctx, kWorkspaceMeta + (tensor_path ? forward_sm100_workspace_bytes(p) : 0)))) return st;
+        ctx->plan_offsets_at = nullptr;  // the metadata may reach into the part that holds a cached decode plan
         FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ctx->workspace, call.varlen_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
         p.varlen = static_cast<const flat_varlen_sequence *>(ctx->workspace);
         return tensor_path ? launch_forward_sm100(ctx, p) : launch_forward_simt(ctx, call.dtype, p);
@@ -413,7 +415,7 @@ int validate_decode_geometry(flat_ctx *ctx, uint64_t q_heads, uint64_t kv_heads,
 constexpr uint64_t kSeqOffsetsAt = 48 << 10;  // byte offset of the sequence offsets inside the metadata region
 
 uint64_t plan_decode(flat_ctx *ctx, int dtype, DecodeParams &p, const int32_t *host_lens, uint64_t total_tokens_hint,
-                     int max_len_hint, uint32_t kv_splits, std::vector<int32_t> *offsets) {
+                     int max_len_hint, uint32_t kv_splits, std::vector<int32_t> *offsets, uint64_t max_splits = 0) {
     p.kv_splits = 1;
     p.chunk_tokens = 0;
     p.balanced = 0;
@@ -458,6 +460,7 @@ uint64_t plan_decode(flat_ctx *ctx, int dtype, DecodeParams &p, const int32_t *h
         c = (c + 63) / 64 * 64;
         if (c < 64) c = 64;
         splits = (int)((max_len_hint + c - 1) / c);
+        if (max_splits && (uint64_t)splits > max_splits) splits = (int)max_splits;  // what a fixed scratch holds
     }
     if (splits > 1) {
         chunk = (max_len_hint + splits - 1) / splits;
@@ -475,8 +478,14 @@ uint64_t plan_decode(flat_ctx *ctx, int dtype, DecodeParams &p, const int32_t *h
 int upload_decode_plan(flat_ctx *ctx, DecodeParams &p, const std::vector<int32_t> &offsets) {
     if (!p.balanced) return FLAT_OK;
     char *dst = static_cast<char *>(ctx->workspace) + kSeqOffsetsAt;
-    FLAT_CUDA_OK(ctx, cudaMemcpyAsync(dst, offsets.data(), offsets.size() * sizeof(int32_t), cudaMemcpyHostToDevice,
-                                      ctx->stream));
+    // a serving loop decodes the same batch step after step: while the lengths stay inside their 16-token
+    // paddings the offsets do not change, and only decode plans write this part of the metadata region
+    if (ctx->plan_offsets_at != dst || ctx->plan_offsets != offsets) {
+        FLAT_CUDA_OK(ctx, cudaMemcpyAsync(dst, offsets.data(), offsets.size() * sizeof(int32_t), cudaMemcpyHostToDevice,
+                                          ctx->stream));
+        ctx->plan_offsets = offsets;
+        ctx->plan_offsets_at = dst;
+    }
     p.seq_offsets = reinterpret_cast<const int32_t *>(dst);
     return FLAT_OK;
 }
@@ -589,21 +598,27 @@ void flat_ctx_destroy(flat_ctx *ctx) {
     for (auto &t : ctx->rope_tables)
         if (t.dev) cudaFree(t.dev);
     for (cudaEvent_t e : ctx->pipe_events) cudaEventDestroy(e);
+    if (ctx->stream_switch) cudaEventDestroy(ctx->stream_switch);
     if (ctx->copy_in) cudaStreamDestroy(ctx->copy_in);
     if (ctx->copy_out) cudaStreamDestroy(ctx->copy_out);
     if (ctx->dev_status) cudaFree(ctx->dev_status);
+    if (ctx->finite_first) cudaFree(ctx->finite_first);
+    if (ctx->finite_first_host) cudaFreeHost(ctx->finite_first_host);
     delete ctx;
 }
 
 int32_t flat_ctx_set_stream(flat_ctx *ctx, void *stream) {
     if (!ctx) return FLAT_ERR_NULL_POINTER;
-    if (ctx->stream != static_cast<cudaStream_t>(stream)) {
-        // cached RoPE tables were written on the old stream; later calls read them on the new one
-        bool cached = false;
-        for (auto &t : ctx->rope_tables) cached = cached || t.rows > 0;
-        if (cached) FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    cudaStream_t next = static_cast<cudaStream_t>(stream);
+    if (ctx->stream != next) {
+        // The context's scratch (workspace, metadata region, cached RoPE tables, host staging, the static decode
+        // array) is shared by consecutive calls: work queued on the old stream may still read what the first call
+        // on the new stream overwrites.  The new stream waits for the old one; the host does not.
+        if (!ctx->stream_switch) FLAT_CUDA_OK(ctx, cudaEventCreateWithFlags(&ctx->stream_switch, cudaEventDisableTiming));
+        FLAT_CUDA_OK(ctx, cudaEventRecord(ctx->stream_switch, ctx->stream));
+        FLAT_CUDA_OK(ctx, cudaStreamWaitEvent(next, ctx->stream_switch, 0));
     }
-    ctx->stream = static_cast<cudaStream_t>(stream);
+    ctx->stream = next;
     return FLAT_OK;
 }
 
@@ -665,7 +680,12 @@ int32_t flat_ctx_device_status(flat_ctx *ctx) {
     FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
     FLAT_CUDA_OK(ctx, cudaMemcpy(&h, ctx->dev_status, sizeof h, cudaMemcpyDeviceToHost));
     if (h.code != 0) {
-        fail(ctx, h.code, "device wait expired at site %d", h.where);
+        if (h.code == FLAT_ERR_PAGE_OUT_OF_RANGE)
+            fail(ctx, h.code, "a page-table entry of sequence %d lies outside the physical pool; its tokens were masked", h.where);
+        else if (h.code == FLAT_ERR_NON_FINITE_INPUT)
+            fail(ctx, h.code, "a device-side input scan found a non-finite value (tensor %d)", h.where);
+        else
+            fail(ctx, h.code, "device wait expired at site %d", h.where);
         cudaMemset(ctx->dev_status, 0, sizeof(DeviceStatus));
     }
     return h.code;
@@ -850,29 +870,13 @@ int32_t flat_forward_projection_rope_varlen(flat_ctx *ctx, int32_t dtype, const 
     return forward_common(ctx, c, shape, config, q, k, v, out_and_lse);
 }
 
-// validate_input (src/lib.rs:428-447): exact length, then the first non-finite element
-static int validate_host_tensor(flat_ctx *ctx, const char *name, int dtype, const void *data, uint64_t actual,
-                                uint64_t expected, int check_finite) {
+// validate_input (src/lib.rs:428-447), host part: the exact length.  Finiteness is scanned on the device, chunk by
+// chunk as the upload lands (validate.cu), and reported with the same tensor name and first index.
+static int validate_host_tensor(flat_ctx *ctx, const char *name, const void *data, uint64_t actual, uint64_t expected) {
     if (!data) return fail(ctx, FLAT_ERR_NULL_POINTER, "%s is null", name);
     if (actual != expected)
         return fail(ctx, FLAT_ERR_LENGTH_MISMATCH, "tensor %s contains %llu elements, expected %llu", name,
                     (unsigned long long)actual, (unsigned long long)expected);
-    if (!check_finite) return FLAT_OK;
-    if (dtype == FLAT_F32) {
-        const uint32_t *p = static_cast<const uint32_t *>(data);
-        for (uint64_t i = 0; i < actual; ++i)
-            if ((p[i] & 0x7f800000u) == 0x7f800000u)
-                return fail(ctx, FLAT_ERR_NON_FINITE_INPUT, "tensor %s contains a non-finite value at index %llu", name,
-                            (unsigned long long)i);
-    } else {
-        // bf16: 8 exponent bits below the sign; binary16: 5 (F16::is_finite, src/f16.rs:112-115)
-        const uint16_t mask = dtype == FLAT_F16 ? 0x7c00u : 0x7f80u;
-        const uint16_t *p = static_cast<const uint16_t *>(data);
-        for (uint64_t i = 0; i < actual; ++i)
-            if ((p[i] & mask) == mask)
-                return fail(ctx, FLAT_ERR_NON_FINITE_INPUT, "tensor %s contains a non-finite value at index %llu", name,
-                            (unsigned long long)i);
-    }
     return FLAT_OK;
 }
 
@@ -891,9 +895,9 @@ int32_t flat_forward_host(flat_ctx *ctx, int32_t dtype, int32_t layout, const fl
         if ((st = validate_rotary(ctx, rotary->theta, rotary->query_position_offset, shape->head_dim, shape->query_len))) return st;
         if ((st = validate_rotary(ctx, rotary->theta, rotary->kv_position_offset, shape->head_dim, shape->kv_len))) return st;
     }
-    if ((st = validate_host_tensor(ctx, "Q", dtype, q, q_elements, d.q_elements, check_finite))) return st;
-    if ((st = validate_host_tensor(ctx, "K", dtype, k, k_elements, d.kv_elements, check_finite))) return st;
-    if ((st = validate_host_tensor(ctx, "V", dtype, v, v_elements, d.kv_elements, check_finite))) return st;
+    if ((st = validate_host_tensor(ctx, "Q", q, q_elements, d.q_elements))) return st;
+    if ((st = validate_host_tensor(ctx, "K", k, k_elements, d.kv_elements))) return st;
+    if ((st = validate_host_tensor(ctx, "V", v, v_elements, d.kv_elements))) return st;
     float scale;
     if ((st = resolve_scale(ctx, config, shape->head_dim, &scale))) return st;
     const uint64_t es = dtype_size(dtype);
@@ -933,6 +937,14 @@ int32_t flat_forward_host(flat_ctx *ctx, int32_t dtype, int32_t layout, const fl
         FLAT_CUDA_OK(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
         ctx->pipe_events.push_back(e);
     }
+    if (check_finite) {
+        if (!ctx->finite_first) {
+            FLAT_CUDA_OK(ctx, cudaMalloc(reinterpret_cast<void **>(&ctx->finite_first), 3 * sizeof(unsigned long long)));
+            FLAT_CUDA_OK(ctx, cudaHostAlloc(reinterpret_cast<void **>(&ctx->finite_first_host), 3 * sizeof(unsigned long long),
+                                            cudaHostAllocDefault));
+        }
+        FLAT_CUDA_OK(ctx, cudaMemsetAsync(ctx->finite_first, 0xff, 3 * sizeof(unsigned long long), ctx->stream));
+    }
     // the staging buffers may still be read by earlier work on the context stream
     FLAT_CUDA_OK(ctx, cudaEventRecord(ctx->pipe_events[2 * n_chunks], ctx->stream));
     FLAT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->copy_in, ctx->pipe_events[2 * n_chunks], 0));
@@ -954,6 +966,16 @@ int32_t flat_forward_host(flat_ctx *ctx, int32_t dtype, int32_t layout, const fl
         FLAT_CUDA_OK(ctx, cudaMemcpyAsync((char *)dv.ptr + kv_off, hv + kv_off, kv_sz, cudaMemcpyHostToDevice, ctx->copy_in));
         FLAT_CUDA_OK(ctx, cudaEventRecord(ctx->pipe_events[c], ctx->copy_in));
         FLAT_CUDA_OK(ctx, cudaStreamWaitEvent(ctx->stream, ctx->pipe_events[c], 0));
+        if (check_finite) {
+            FiniteScan scan{};
+            scan.seg[0] = {(const char *)dq.ptr + q_off, q_sz / es, q_off / es, 0};
+            scan.seg[1] = {(const char *)dk.ptr + kv_off, kv_sz / es, kv_off / es, 1};
+            scan.seg[2] = {(const char *)dv.ptr + kv_off, kv_sz / es, kv_off / es, 2};
+            scan.first = ctx->finite_first;
+            scan.elem_size = (int)es;
+            scan.mask16 = dtype == FLAT_F16 ? 0x7c00u : 0x7f80u;  // F16::is_finite (src/f16.rs:112-115); bf16: 8 exponent bits
+            if ((st = launch_finite_scan(ctx, scan, ctx->stream))) return st;
+        }
         FwdParams pb = p;
         pb.batch = 1;
         pb.q_heads = heads_per_chunk * p.group;
@@ -970,8 +992,20 @@ int32_t flat_forward_host(flat_ctx *ctx, int32_t dtype, int32_t layout, const fl
         FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ho + lse_off + lse_row0 * sizeof(float), (char *)(p.lse + lse_row0), lse_sz,
                                           cudaMemcpyDeviceToHost, ctx->copy_out));
     }
+    if (check_finite)
+        FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ctx->finite_first_host, ctx->finite_first, 3 * sizeof(unsigned long long),
+                                          cudaMemcpyDeviceToHost, ctx->stream));
     FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->copy_out));
     FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));
+    if (check_finite) {
+        // the reference validates Q, then K, then V, and names the first offender; an input that fails has no result
+        // (what the output buffer received meanwhile is unspecified)
+        static const char *const names[3] = {"Q", "K", "V"};
+        for (int t = 0; t < 3; ++t)
+            if (ctx->finite_first_host[t] != ~0ull)
+                return fail(ctx, FLAT_ERR_NON_FINITE_INPUT, "tensor %s contains a non-finite value at index %llu", names[t],
+                            ctx->finite_first_host[t]);
+    }
     return FLAT_OK;
 }
 
@@ -1229,6 +1263,27 @@ flat_buffer flat_resident_kv_cache_v_buffer(const flat_resident_kv_cache *cache)
 }
 
 // ---- decode ----------------------------------------------------------------------------------
+int32_t flat_decode_layout_for(int32_t dtype, uint64_t batch, uint64_t q_heads, uint64_t head_dim, flat_decode_layout *out) {
+    if (!out) return FLAT_ERR_NULL_POINTER;
+    if (dtype != FLAT_F32 && dtype != FLAT_BF16) return FLAT_ERR_UNSUPPORTED_DTYPE;
+    // validate_geometry (src/wgpu_paged_decode.rs:439-458) / validate_kv_view (src/wgpu_decode.rs:466-489)
+    if (batch == 0 || q_heads == 0 || head_dim == 0) return FLAT_ERR_ZERO_DIMENSION;
+    if (head_dim % 2 != 0) return FLAT_ERR_INVALID_ROTARY_HEAD_DIM;
+    if (head_dim > (uint64_t)kMaxHeadDim) return FLAT_ERR_UNSUPPORTED_HEAD_DIM;
+    uint64_t rows, q_elements, combined;
+    if (!mul_ok(batch, q_heads, &rows) || !mul_ok(rows, head_dim, &q_elements) || !add_ok(q_elements, rows, &combined) ||
+        q_elements > (uint64_t)1 << 46)
+        return FLAT_ERR_SHAPE_OVERFLOW;
+    out->q_elements = q_elements;
+    out->output_elements = q_elements;
+    out->lse_elements = rows;
+    out->combined_elements = combined;
+    out->q_bytes = q_elements * dtype_size(dtype);
+    out->lse_byte_offset = lse_offset_bytes(dtype, q_elements);
+    out->combined_bytes = out->lse_byte_offset + rows * 4;
+    return FLAT_OK;
+}
+
 int32_t flat_decode_resident(flat_ctx *ctx, int32_t dtype, uint64_t batch, uint64_t q_heads, uint64_t kv_heads,
                              uint64_t head_dim, uint64_t kv_len, uint64_t kv_capacity,
                              const flat_attention_config *config, float theta, uint64_t q_rope_position,
@@ -1267,6 +1322,7 @@ int32_t flat_decode_resident(flat_ctx *ctx, int32_t dtype, uint64_t batch, uint6
     p.num_seqs = (int)batch; p.q_heads = (int)q_heads; p.kv_heads = (int)kv_heads; p.head_dim = (int)head_dim;
     p.group = (int)(q_heads / kv_heads);
     p.page_size = 0;
+    p.status = ctx->dev_status;
     p.uniform_len = (int)kv_len;
     p.uniform_q_pos = (int64_t)q_rope_position;
     p.seq_stride_rows = (int64_t)kv_capacity;
@@ -1333,6 +1389,8 @@ int32_t flat_decode_paged(flat_ctx *ctx, int32_t dtype, const flat_paged_kv_tabl
     p.group = (int)(q_heads / kv_heads);
     p.page_size = (int)table->page_size;
     p.max_pages = (int)mapped;
+    p.physical_pages = (int)table->physical_pages;
+    p.status = ctx->dev_status;
     p.uniform_len = (int)table->live_tokens;
     p.uniform_q_pos = (int64_t)q_rope_position;
     p.scale = scale;
@@ -1348,6 +1406,8 @@ int32_t flat_decode_paged(flat_ctx *ctx, int32_t dtype, const flat_paged_kv_tabl
     return run_decode(ctx, dtype, p);
 }
 
+enum DecodeRoute { kDecodeRegular = 0, kDecodePartialF32 = 1, kDecodeStaticScratch = 2 };
+
 static int32_t decode_paged_batched_impl(flat_ctx *ctx, int32_t dtype, uint64_t num_seqs, uint64_t q_heads,
                                          uint64_t kv_heads, uint64_t head_dim, uint64_t page_size, uint64_t physical_pages,
                                          uint64_t max_pages_per_seq, const int32_t *page_tables_dev,
@@ -1355,8 +1415,9 @@ static int32_t decode_paged_batched_impl(flat_ctx *ctx, int32_t dtype, uint64_t 
                                          const int32_t *host_page_tables, const int32_t *host_context_lens,
                                          const int32_t *host_q_rope_positions, const flat_attention_config *config,
                                          float theta, uint32_t kv_splits, flat_buffer q, flat_buffer k, flat_buffer v,
-                                         flat_buffer out_and_lse, bool out_f32) {
+                                         flat_buffer out_and_lse, DecodeRoute route) {
     if (!ctx) return FLAT_ERR_NULL_POINTER;
+    const bool out_f32 = route == kDecodePartialF32;
     int st;
     if ((st = check_dtype(ctx, dtype))) return st;
     if (num_seqs == 0 || page_size == 0 || physical_pages == 0 || max_pages_per_seq == 0)
@@ -1368,7 +1429,7 @@ static int32_t decode_paged_batched_impl(flat_ctx *ctx, int32_t dtype, uint64_t 
     const uint64_t lim = (uint64_t)std::numeric_limits<int32_t>::max();
     uint64_t pool_rows;
     if (num_seqs > 65535 || physical_pages > lim || max_pages_per_seq > lim || page_size > lim ||
-        !mul_ok(physical_pages, page_size, &pool_rows))
+        !mul_ok(physical_pages, page_size, &pool_rows) || pool_rows > lim)
         return fail(ctx, FLAT_ERR_INDEX_SPACE_EXCEEDED, "paged decode geometry exceeds the index space");
     uint64_t total = 0;
     int max_len = 0;
@@ -1407,13 +1468,17 @@ static int32_t decode_paged_batched_impl(flat_ctx *ctx, int32_t dtype, uint64_t 
     float scale;
     if ((st = resolve_scale(ctx, config, head_dim, &scale))) return st;
     const uint64_t es = dtype_size(dtype);
-    const uint64_t q_elems = num_seqs * q_heads * head_dim;
-    const uint64_t kv_bytes = pool_rows * kv_heads * head_dim * es;
+    // q_heads <= 2^20 and head_dim <= 128 (validate_decode_geometry), num_seqs < 2^16, pool rows < 2^31: no product wraps
+    const uint64_t rows = num_seqs * q_heads;
+    const uint64_t q_elems = rows * head_dim;
+    uint64_t kv_bytes;
+    if (!mul_ok(pool_rows, kv_heads * head_dim * es, &kv_bytes))
+        return fail(ctx, FLAT_ERR_SHAPE_OVERFLOW, "paged cache size overflows");
     const uint64_t lse_off = out_f32 ? q_elems * 4 : lse_offset_bytes(dtype, q_elems);
     if ((st = check_buffer(ctx, "Q", q, q_elems * es))) return st;
     if ((st = check_buffer(ctx, "K", k, kv_bytes))) return st;
     if ((st = check_buffer(ctx, "V", v, kv_bytes))) return st;
-    if ((st = check_buffer(ctx, "O|LSE", out_and_lse, lse_off + num_seqs * q_heads * 4))) return st;
+    if ((st = check_buffer(ctx, "O|LSE", out_and_lse, lse_off + rows * 4))) return st;
 
     DecodeParams p{};
     p.q = q.ptr; p.k = k.ptr; p.v = v.ptr; p.o = out_and_lse.ptr;
@@ -1422,6 +1487,8 @@ static int32_t decode_paged_batched_impl(flat_ctx *ctx, int32_t dtype, uint64_t 
     p.group = (int)(q_heads / kv_heads);
     p.page_size = (int)page_size;
     p.max_pages = (int)max_pages_per_seq;
+    p.physical_pages = (int)physical_pages;
+    p.status = ctx->dev_status;
     p.page_table = page_tables_dev;
     p.context_lens = context_lens_dev;
     p.q_rope_positions = q_rope_positions_dev;
@@ -1429,6 +1496,37 @@ static int32_t decode_paged_batched_impl(flat_ctx *ctx, int32_t dtype, uint64_t 
     p.rope_q = 1;
     p.out_f32 = out_f32 ? 1 : 0;
     fill_inv_freq(theta, p.head_dim, p.inv_freq);
+    if (route == kDecodeStaticScratch) {
+        // The partials live in the library's fixed device array; nothing here may allocate, so the balanced plan
+        // (whose sequence offsets go through the context workspace) and the generic fallback kernel are not used.
+        if (!decode_fast_path_ok(dtype, p.head_dim, p.group))
+            return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE,
+                        "the static-scratch decode needs head_dim %% %d == 0 and a query-head group of 1, 2, 4 or 8",
+                        dtype == FLAT_BF16 ? 8 : 4);
+        const flat_buffer bufs[] = {q, k, v, out_and_lse};
+        const char *names[] = {"Q", "K", "V", "O|LSE"};
+        for (int i = 0; i < 4; ++i)
+            if ((reinterpret_cast<uintptr_t>(bufs[i].ptr) & 15) != 0)
+                return fail(ctx, FLAT_ERR_MISALIGNED_BUFFER, "%s buffer must be 16-byte aligned", names[i]);
+        const uint64_t bytes_per_split = rows * (head_dim + 1) * sizeof(float);  // >= 8, < 2^46
+        const uint64_t fit = kDecodeStaticScratchBytes / bytes_per_split;
+        if (kv_splits > 1 && (uint64_t)kv_splits > fit)
+            return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE,
+                        "split-KV partials for %u chunks need %llu bytes, the static scratch holds %llu "
+                        "(num_seqs*q_heads*(head_dim+1)*4 bytes per chunk)",
+                        kv_splits, (unsigned long long)(kv_splits * bytes_per_split),
+                        (unsigned long long)kDecodeStaticScratchBytes);
+        // automatic plan: as many chunks as fill the machine about four times, clamped to what the array holds
+        // (fit == 0: a single chunk, which needs no scratch at all)
+        plan_decode(ctx, dtype, p, host_context_lens, total, max_len, kv_splits, nullptr, fit ? fit : 1);
+        if (p.kv_splits > 1) {
+            float *scratch = nullptr;
+            if ((st = decode_static_scratch(ctx, &scratch))) return st;
+            p.partial_o = scratch;
+            p.partial_lse = scratch + (uint64_t)p.kv_splits * rows * head_dim;
+        }
+        return launch_decode(ctx, dtype, p);
+    }
     std::vector<int32_t> offsets;
     const uint64_t scratch = plan_decode(ctx, dtype, p, host_context_lens, total, max_len, kv_splits, &offsets);
     if ((st = ensure_workspace(ctx, kWorkspaceMeta + scratch))) return st;
@@ -1447,7 +1545,7 @@ int32_t flat_decode_paged_batched(flat_ctx *ctx, int32_t dtype, uint64_t num_seq
     return decode_paged_batched_impl(ctx, dtype, num_seqs, q_heads, kv_heads, head_dim, page_size, physical_pages,
                                      max_pages_per_seq, page_tables_dev, context_lens_dev, q_rope_positions_dev,
                                      host_page_tables, host_context_lens, host_q_rope_positions, config, theta, kv_splits, q,
-                                     k, v, out_and_lse, false);
+                                     k, v, out_and_lse, kDecodeRegular);
 }
 
 int32_t flat_decode_paged_batched_partial(flat_ctx *ctx, int32_t dtype, uint64_t num_seqs, uint64_t q_heads,
@@ -1463,7 +1561,21 @@ int32_t flat_decode_paged_batched_partial(flat_ctx *ctx, int32_t dtype, uint64_t
     return decode_paged_batched_impl(ctx, dtype, num_seqs, q_heads, kv_heads, head_dim, page_size, physical_pages,
                                      max_pages_per_seq, page_tables_dev, context_lens_dev, q_rope_positions_dev,
                                      host_page_tables, host_context_lens, nullptr, config, theta, 0, q, k, v,
-                                     partial_out_and_lse, true);
+                                     partial_out_and_lse, kDecodePartialF32);
+}
+
+// The batched split-KV decode for callers that must not allocate: same validation and kernels as
+// flat_decode_paged_batched, partials in the fixed device array of the library image (decode.cu).
+int32_t flat_decode_paged_batched_static_scratch(
+    flat_ctx *ctx, int32_t dtype, uint64_t num_seqs, uint64_t q_heads, uint64_t kv_heads, uint64_t head_dim,
+    uint64_t page_size, uint64_t physical_pages, uint64_t max_pages_per_seq, const int32_t *page_tables_dev,
+    const int32_t *context_lens_dev, const int32_t *q_rope_positions_dev, const int32_t *host_context_lens,
+    const int32_t *host_q_rope_positions, const flat_attention_config *config, float theta, uint32_t kv_splits,
+    flat_buffer q, flat_buffer k, flat_buffer v, flat_buffer out_and_lse) {
+    return decode_paged_batched_impl(ctx, dtype, num_seqs, q_heads, kv_heads, head_dim, page_size, physical_pages,
+                                     max_pages_per_seq, page_tables_dev, context_lens_dev, q_rope_positions_dev, nullptr,
+                                     host_context_lens, host_q_rope_positions, config, theta, kv_splits, q, k, v,
+                                     out_and_lse, kDecodeStaticScratch);
 }
 
 int32_t flat_splitkv_merge_packed(flat_ctx *ctx, int32_t dtype, uint64_t parts, uint64_t rows, uint64_t head_dim,

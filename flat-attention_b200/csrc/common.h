@@ -7,6 +7,7 @@
 
 #include <cstdarg>
 #include <cstdint>
+#include <algorithm>
 #include <cstdio>
 #include <string>
 #include <utility>
@@ -41,6 +42,8 @@ struct flat_ctx {
     void *host_stage = nullptr;       // device staging of the host-slice entry points (Q | K | V | O|LSE)
     uint64_t host_stage_bytes = 0;
     cudaStream_t copy_in = nullptr, copy_out = nullptr;  // upload / download streams of the host-slice entry points
+    unsigned long long *finite_first = nullptr;       // device [3]: first non-finite index of Q, K, V (device-side scan)
+    unsigned long long *finite_first_host = nullptr;  // pinned host mirror, read once per call
     std::vector<cudaEvent_t> pipe_events;
     // (cos, sin) tables of recent RoPE calls, kept on the device: a serving or training loop calls with the same
     // theta, head_dim and positions every step, and the table is then computed once instead of per call
@@ -54,6 +57,10 @@ struct flat_ctx {
     };
     RopeTable rope_tables[2];
     uint64_t rope_clock = 0;
+    cudaEvent_t stream_switch = nullptr;  // orders the old and the new stream in flat_ctx_set_stream
+    // sequence offsets of the last balanced decode plan and where they were uploaded (skips identical re-uploads)
+    std::vector<int32_t> plan_offsets;
+    const void *plan_offsets_at = nullptr;
     // optional timing of the dominant kernel of each call (CUDA events on the launch stream)
     bool timing = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> timed;
@@ -158,6 +165,8 @@ struct DecodeParams {
     float *lse;          // [num_seqs, q_heads]
     int num_seqs, q_heads, kv_heads, head_dim, group;
     int page_size, max_pages;            // page_size == 0 -> resident (contiguous) addressing
+    int physical_pages;                  // paged: entries outside [0, physical_pages) are masked and flagged, never read
+    DeviceStatus *status;                // device status word of the context (page-table range violations)
     const int32_t *page_table;           // device [num_seqs, max_pages]
     const int32_t *context_lens;         // device [num_seqs] or null (-> uniform_len)
     const int32_t *q_rope_positions;     // device [num_seqs] or null (-> uniform_q_pos)
@@ -183,6 +192,10 @@ struct DecodeParams {
     const int32_t *seq_offsets;
 };
 uint64_t decode_workspace_bytes(const DecodeParams &p);
+// Fixed scratch of the allocation-free decode entry point: a file-scope device array of the library image.
+constexpr uint64_t kDecodeStaticScratchBytes = 8ull << 20;  // 8 MiB per device that loads the library
+// Device address of that array on the context's device (looked up once per device with cudaGetSymbolAddress).
+int decode_static_scratch(flat_ctx *ctx, float **out);
 bool decode_fast_path_ok(int dtype, int head_dim, int group);
 int launch_decode(flat_ctx *ctx, int dtype, const DecodeParams &p);
 // bf16 tensor-core decode (mma.sync), head_dim 64/128, group <= 8, pages of a multiple of 16 tokens
@@ -192,6 +205,22 @@ int launch_decode_mma(flat_ctx *ctx, const DecodeParams &p);
 int launch_splitkv_merge(flat_ctx *ctx, int dtype, int parts, int64_t rows, int head_dim,
                          const float *partial_o, const float *partial_lse, int64_t part_stride_o,
                          int64_t part_stride_lse, void *o, float *lse);
+
+// ---- input validation on the device ----------------------------------------------------------
+// Up to three segments (Q, K, V chunks) scanned for non-finite values in one launch; first[slot] receives the
+// smallest absolute element index of an offending value (atomicMin; ~0 = none found).
+struct FiniteScan {
+    struct Segment {
+        const void *data;     // device, 16-byte aligned
+        uint64_t elements;
+        uint64_t base_index;  // index of data[0] inside the caller's tensor
+        int slot;             // which entry of `first` the segment reports to
+    } seg[3];
+    unsigned long long *first;  // device, [3]
+    int elem_size;              // 4 (f32) or 2 (bf16 / binary16)
+    uint32_t mask16;            // exponent mask of the 16-bit type (0x7f80 bf16, 0x7c00 binary16)
+};
+int launch_finite_scan(flat_ctx *ctx, const FiniteScan &scan, cudaStream_t stream);
 
 // ---- KV cache --------------------------------------------------------------------------------
 // Copies `rows` source rows of `row_elems` elements to destination rows dst_rows[i] (device

@@ -129,14 +129,24 @@ __global__ void __launch_bounds__(256) decode_kernel(const __grid_constant__ Dec
             ok[u] = t < end;
             kraw[u] = make_uint4(0, 0, 0, 0);
             vraw[u] = make_uint4(0, 0, 0, 0);
-            if (ok[u] && lane_active) {
-                int64_t row;
+            int64_t row = 0;
+            if (ok[u]) {
                 if (table) {
-                    int page = table[t / p.page_size];
+                    const int page = table[t / p.page_size];
+                    // an entry outside the pool is never dereferenced: the token is masked and the call is flagged
+                    if ((unsigned)page >= (unsigned)p.physical_pages) {
+                        ok[u] = false;
+                        if (p.status) {
+                            p.status->code = FLAT_ERR_PAGE_OUT_OF_RANGE;
+                            p.status->where = seq;
+                        }
+                    }
                     row = (int64_t)page * p.page_size + t % p.page_size;
                 } else {
                     row = (int64_t)seq * p.seq_stride_rows + t;
                 }
+            }
+            if (ok[u] && lane_active) {
                 int64_t off = (row * row_elems + head_off) * (int64_t)sizeof(T);
                 kraw[u] = ldg_stream(kbase + off);
                 vraw[u] = ldg_stream(vbase + off);
@@ -209,8 +219,9 @@ __global__ void __launch_bounds__(256) decode_kernel(const __grid_constant__ Dec
 #pragma unroll
     for (int g = 0; g < G; ++g) {
         const int q_head = kv_head * G + g;
-        const float inv = 1.0f / l[g];
-        const float lse = (m[g] + log2f(l[g])) * kLn2;
+        // l == 0 only when every token of the range was masked (flagged page-table entries): O = 0, LSE = -inf
+        const float inv = l[g] > 0.f ? 1.0f / l[g] : 0.f;
+        const float lse = l[g] > 0.f ? (m[g] + log2f(l[g])) * kLn2 : -INFINITY;
         const int64_t out_row = (int64_t)seq * p.q_heads + q_head;
         if (p.kv_splits > 1) {
             float *po = p.partial_o + ((int64_t)split * p.num_seqs * p.q_heads + out_row) * D + d0;
@@ -407,25 +418,26 @@ int launch_splitkv_merge(flat_ctx *ctx, int dtype, int parts, int64_t rows, int 
 
 }  // namespace flat
 
-// ---- split-KV paged decode for callers that must not allocate --------------------------------
+// ---- fixed scratch for callers that must not allocate ------------------------------------------
 // Some hosts of this library cannot call cudaMalloc at the moment they need a decode step:
-// latency-critical serving loops where an allocation would synchronise the device, plug-ins living under a framework allocator that forbids side
-// allocations, or processes whose memory budget was fixed at start-up.  The split-KV decode needs
-// scratch for its per-chunk (O, LSE) partials; the regular entry point takes it from the context
-// workspace, which may grow.  This variant keeps the partials in a fixed array that is part of the
-// library image, so the call itself allocates nothing.
+// latency-critical serving loops where an allocation would synchronise the device, plug-ins living under a
+// framework allocator that forbids side allocations, or processes whose memory budget was fixed at start-up.
+// The split-KV decode needs scratch for its per-chunk (O, LSE) partials; the regular entry point takes it
+// from the context workspace, which may grow.  flat_decode_paged_batched_static_scratch keeps the partials
+// in this fixed array, which is part of the library image, so the call itself allocates nothing.
 namespace flat {
 namespace {
 
-constexpr uint64_t kStaticScratchBytes = 8ull << 20;  // 8 MiB per device that loads the library
-static __device__ __align__(256) float g_decode_static_scratch[kStaticScratchBytes / sizeof(float)];
+static __device__ __align__(256) float g_decode_static_scratch[kDecodeStaticScratchBytes / sizeof(float)];
 
 constexpr int kMaxDevices = 64;
 float *g_static_scratch_ptr[kMaxDevices] = {};
 
+}  // namespace
+
 // The array's name is only a host-side stand-in; the device address has to be asked for, once per
 // device, with that device current.
-int static_scratch_for_device(flat_ctx *ctx, float **out) {
+int decode_static_scratch(flat_ctx *ctx, float **out) {
     if (ctx->device < 0 || ctx->device >= kMaxDevices)
         return fail(ctx, FLAT_ERR_UNAVAILABLE, "device index %d is outside the supported range", ctx->device);
     if (!g_static_scratch_ptr[ctx->device]) {
@@ -443,121 +455,4 @@ int static_scratch_for_device(flat_ctx *ctx, float **out) {
     return FLAT_OK;
 }
 
-}  // namespace
 }  // namespace flat
-
-extern "C" int32_t flat_decode_paged_batched_static_scratch(
-    flat_ctx *ctx, int32_t dtype, uint64_t num_seqs, uint64_t q_heads, uint64_t kv_heads, uint64_t head_dim,
-    uint64_t page_size, uint64_t physical_pages, uint64_t max_pages_per_seq, const int32_t *page_tables_dev,
-    const int32_t *context_lens_dev, const int32_t *q_rope_positions_dev, const int32_t *host_context_lens,
-    const int32_t *host_q_rope_positions, const flat_attention_config *config, float theta, uint32_t kv_splits,
-    flat_buffer q, flat_buffer k, flat_buffer v, flat_buffer out_and_lse) {
-    using namespace flat;
-    if (!ctx) return FLAT_ERR_NULL_POINTER;
-    if (dtype != FLAT_F32 && dtype != FLAT_BF16) return fail(ctx, FLAT_ERR_UNSUPPORTED_DTYPE, "unknown dtype %d", dtype);
-    if (num_seqs == 0 || q_heads == 0 || kv_heads == 0 || head_dim == 0 || page_size == 0 || physical_pages == 0 ||
-        max_pages_per_seq == 0)
-        return fail(ctx, FLAT_ERR_ZERO_DIMENSION, "paged decode dimensions must all be non-zero");
-    if (q_heads % kv_heads != 0)
-        return fail(ctx, FLAT_ERR_INVALID_HEAD_GROUPING, "q_heads (%llu) must be exactly divisible by kv_heads (%llu)",
-                    (unsigned long long)q_heads, (unsigned long long)kv_heads);
-    if (head_dim > (uint64_t)kMaxHeadDim)
-        return fail(ctx, FLAT_ERR_UNSUPPORTED_HEAD_DIM, "head_dim %llu exceeds maximum %d", (unsigned long long)head_dim, kMaxHeadDim);
-    if (!(theta > 0.0f) || !std::isfinite(theta))
-        return fail(ctx, FLAT_ERR_INVALID_THETA, "decode RoPE theta must be finite and positive, got %g", (double)theta);
-    if (!page_tables_dev || !context_lens_dev || !q_rope_positions_dev || !host_context_lens || !config)
-        return fail(ctx, FLAT_ERR_NULL_POINTER, "page tables, context lengths, query positions and config are required");
-    const uint64_t lim = 0x7fffffffull;
-    if (num_seqs > 65535 || physical_pages > lim || max_pages_per_seq > lim || page_size > lim ||
-        physical_pages * page_size > lim)
-        return fail(ctx, FLAT_ERR_INDEX_SPACE_EXCEEDED, "paged decode geometry exceeds the index space");
-    const int group = (int)(q_heads / kv_heads);
-    if (!decode_fast_path_ok(dtype, (int)head_dim, group))
-        return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE,
-                    "the static-scratch decode needs head_dim %% %d == 0 and a query-head group of 1, 2, 4 or 8",
-                    dtype == FLAT_BF16 ? 8 : 4);
-    uint64_t total = 0;
-    int max_len = 0;
-    for (uint64_t s = 0; s < num_seqs; ++s) {
-        const int32_t len = host_context_lens[s];
-        if (len <= 0) return fail(ctx, FLAT_ERR_EMPTY_TABLE, "sequence %llu has no live KV token", (unsigned long long)s);
-        if (((uint64_t)len + page_size - 1) / page_size > max_pages_per_seq)
-            return fail(ctx, FLAT_ERR_INDEX_SPACE_EXCEEDED, "sequence %llu does not fit its page-table row", (unsigned long long)s);
-        if (host_q_rope_positions && config->causal && (int64_t)host_q_rope_positions[s] + 1 < (int64_t)len)
-            return fail(ctx, FLAT_ERR_CAUSAL_VISIBILITY_MISMATCH,
-                        "paged causal decode query position %d cannot see all %d live KV tokens (sequence %llu)",
-                        host_q_rope_positions[s], len, (unsigned long long)s);
-        total += (uint64_t)len;
-        if (len > max_len) max_len = len;
-    }
-    float scale = config->has_softmax_scale ? config->softmax_scale : 1.0f / std::sqrt((float)head_dim);
-    if (!std::isfinite(scale) || scale <= 0.0f)
-        return fail(ctx, FLAT_ERR_INVALID_SCALE, "softmax scale must be finite and positive, got %g", (double)scale);
-    const uint64_t es = dtype_size(dtype);
-    const uint64_t q_elems = num_seqs * q_heads * head_dim;
-    const uint64_t kv_bytes = physical_pages * page_size * kv_heads * head_dim * es;
-    const uint64_t lse_off = (q_elems * es + 3) & ~uint64_t(3);
-    const struct { const char *name; flat_buffer b; uint64_t need; } bufs[] = {
-        {"Q", q, q_elems * es}, {"K", k, kv_bytes}, {"V", v, kv_bytes}, {"O|LSE", out_and_lse, lse_off + num_seqs * q_heads * 4}};
-    for (const auto &bb : bufs) {
-        if (!bb.b.ptr) return fail(ctx, FLAT_ERR_NULL_POINTER, "%s buffer is null", bb.name);
-        if (bb.b.bytes < bb.need)
-            return fail(ctx, FLAT_ERR_BUFFER_TOO_SMALL, "%s buffer has %llu bytes, requires %llu", bb.name,
-                        (unsigned long long)bb.b.bytes, (unsigned long long)bb.need);
-        if ((reinterpret_cast<uintptr_t>(bb.b.ptr) & 15) != 0)
-            return fail(ctx, FLAT_ERR_MISALIGNED_BUFFER, "%s buffer must be 16-byte aligned", bb.name);
-    }
-
-    // split plan: as many chunks as fill the machine about four times, clamped to what the fixed
-    // scratch holds; an explicit kv_splits is taken as given and refused if it does not fit
-    const uint64_t rows = num_seqs * q_heads;
-    const uint64_t bytes_per_split = rows * (head_dim + 1) * sizeof(float);
-    const uint64_t fit = kStaticScratchBytes / bytes_per_split;
-    int splits;
-    if (kv_splits >= 1) {
-        splits = (int)kv_splits;
-    } else {
-        const uint64_t slots = (uint64_t)ctx->sm_count * 2, units = (kv_heads + 7) / 8;
-        uint64_t want = 4 * slots / units;
-        if (want < 1) want = 1;
-        uint64_t c = (total + want - 1) / want;
-        c = (c + 63) / 64 * 64;
-        splits = (int)(((uint64_t)max_len + c - 1) / c);
-        if ((uint64_t)splits > fit) splits = (int)fit;
-    }
-    if (splits < 2 || (uint64_t)splits > fit)
-        return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE,
-                    "split-KV partials for %d chunks need %llu bytes, the static scratch holds %llu "
-                    "(num_seqs*q_heads*(head_dim+1)*4 bytes per chunk, at least 2 chunks)",
-                    splits < 2 ? 2 : splits, (unsigned long long)((splits < 2 ? 2 : splits) * bytes_per_split),
-                    (unsigned long long)kStaticScratchBytes);
-    int chunk = (max_len + splits - 1) / splits;
-    chunk = (chunk + 63) / 64 * 64;
-    splits = (max_len + chunk - 1) / chunk;
-    if (splits < 1) splits = 1;
-
-    float *scratch = nullptr;
-    int st = static_scratch_for_device(ctx, &scratch);
-    if (st) return st;
-
-    DecodeParams p{};
-    p.q = q.ptr; p.k = k.ptr; p.v = v.ptr; p.o = out_and_lse.ptr;
-    p.lse = reinterpret_cast<float *>(static_cast<char *>(out_and_lse.ptr) + lse_off);
-    p.num_seqs = (int)num_seqs; p.q_heads = (int)q_heads; p.kv_heads = (int)kv_heads; p.head_dim = (int)head_dim;
-    p.group = group;
-    p.page_size = (int)page_size;
-    p.max_pages = (int)max_pages_per_seq;
-    p.page_table = page_tables_dev;
-    p.context_lens = context_lens_dev;
-    p.q_rope_positions = q_rope_positions_dev;
-    p.scale = scale;
-    p.rope_q = 1;
-    for (int pair = 0; pair < (int)head_dim / 2; ++pair)
-        p.inv_freq[pair] = powf(theta, -2.0f * (float)pair / (float)head_dim);
-    p.kv_splits = splits;
-    p.chunk_tokens = chunk;
-    // with one chunk the kernel writes the final result directly and the scratch stays untouched
-    p.partial_o = scratch;
-    p.partial_lse = scratch + (uint64_t)splits * rows * head_dim;
-    return launch_decode(ctx, dtype, p);
-}

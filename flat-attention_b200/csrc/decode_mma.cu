@@ -72,38 +72,42 @@ __device__ __forceinline__ void decode_range(const DecodeParams &p, int seq, int
     const int split = slot;
     const int G = p.group;
 
-    // Q^T fragments: head g of the group, dims 32j + 8c .. +7, rotated, scaled, split hi/lo
+    // Q^T fragments: head g of the group, dims 32j + 8c .. +7, rotated, scaled, split hi/lo.
+    // The rotation angle depends on (position, pair) only, so the warp evaluates each of the D/2 pairs once
+    // (lane l takes pairs l and l + 32; at long-context positions sincosf runs its slow argument reduction)
+    // and the fragments fetch their (cos, sin) with shuffles: pair 16j + 4c + e sits in lane
+    // 16 (j mod 2) + 4c + e, slot j / 2.
     uint32_t qhi[kChunks][4], qlo[kChunks][4];
     {
         const int64_t q_pos = p.q_rope_positions ? (int64_t)p.q_rope_positions[seq] : p.uniform_q_pos;
         const float fold = p.scale * kLog2e;
+        constexpr int kSlots = D / 64;
+        float cs_c[kSlots], cs_s[kSlots];
+#pragma unroll
+        for (int sl = 0; sl < kSlots; ++sl) {
+            cs_c[sl] = 1.f;
+            cs_s[sl] = 0.f;
+            if (p.rope_q) sincosf(__fmul_rn((float)q_pos, p.inv_freq[lane + 32 * sl]), &cs_s[sl], &cs_c[sl]);
+        }
 #pragma unroll
         for (int j = 0; j < kChunks; ++j) {
+            uint4 raw = make_uint4(0, 0, 0, 0);
+            if (g < G)
+                raw = *reinterpret_cast<const uint4 *>((const __nv_bfloat16 *)p.q +
+                                                       ((int64_t)seq * p.q_heads + kv_head * G + g) * D + 32 * j + 8 * c);
+            const uint32_t rr[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
-            for (int e = 0; e < 4; ++e) qhi[j][e] = qlo[j][e] = 0u;
-            if (g < G) {
-                const __nv_bfloat16 *qp = (const __nv_bfloat16 *)p.q + ((int64_t)seq * p.q_heads + kv_head * G + g) * D +
-                                          32 * j + 8 * c;
-                const uint4 raw = *reinterpret_cast<const uint4 *>(qp);
-                const uint32_t rr[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    float x = __uint_as_float(rr[e] << 16), y = __uint_as_float(rr[e] & 0xffff0000u);
-                    if (p.rope_q) {
-                        const float angle = __fmul_rn((float)q_pos, p.inv_freq[(32 * j + 8 * c) / 2 + e]);
-                        float s, co;
-                        sincosf(angle, &s, &co);
-                        const float rx = x * co - y * s, ry = x * s + y * co;
-                        x = rx;
-                        y = ry;
-                    }
-                    x *= fold;
-                    y *= fold;
-                    const __nv_bfloat162 hi = __floats2bfloat162_rn(x, y);
-                    const float2 hf = __bfloat1622float2(hi);
-                    qhi[j][e] = *reinterpret_cast<const uint32_t *>(&hi);
-                    qlo[j][e] = pack_bf16(x - hf.x, y - hf.y);
-                }
+            for (int e = 0; e < 4; ++e) {
+                const int src = 16 * (j & 1) + 4 * c + e;
+                const float co = __shfl_sync(0xffffffffu, cs_c[j >> 1], src), s = __shfl_sync(0xffffffffu, cs_s[j >> 1], src);
+                float x = __uint_as_float(rr[e] << 16), y = __uint_as_float(rr[e] & 0xffff0000u);
+                const float rx = x * co - y * s, ry = x * s + y * co;  // (cos, sin) = (1, 0) without RoPE: exact
+                x = rx * fold;
+                y = ry * fold;
+                const __nv_bfloat162 hi = __floats2bfloat162_rn(x, y);
+                const float2 hf = __bfloat1622float2(hi);
+                qhi[j][e] = *reinterpret_cast<const uint32_t *>(&hi);
+                qlo[j][e] = pack_bf16(x - hf.x, y - hf.y);
             }
         }
     }
@@ -121,8 +125,20 @@ __device__ __forceinline__ void decode_range(const DecodeParams &p, int seq, int
 
     for (int t0 = begin; t0 < end; t0 += 16) {
         int64_t row0;
-        if (table) row0 = (int64_t)table[t0 / p.page_size] * p.page_size + t0 % p.page_size;
-        else row0 = (int64_t)seq * p.seq_stride_rows + t0;
+        if (table) {
+            const int page = table[t0 / p.page_size];
+            // an entry outside the pool is never dereferenced: the tile is skipped and the call is flagged
+            if ((unsigned)page >= (unsigned)p.physical_pages) {
+                if (lane == 0 && p.status) {
+                    p.status->code = FLAT_ERR_PAGE_OUT_OF_RANGE;
+                    p.status->where = seq;
+                }
+                continue;
+            }
+            row0 = (int64_t)page * p.page_size + t0 % p.page_size;
+        } else {
+            row0 = (int64_t)seq * p.seq_stride_rows + t0;
+        }
         const char *ktile = kbase + row0 * row_bytes + head_bytes;
         const char *vtile = vbase + row0 * row_bytes + head_bytes;
 
@@ -212,8 +228,9 @@ __device__ __forceinline__ void decode_range(const DecodeParams &p, int seq, int
         const int head_in_group = 2 * c + hh;
         if (head_in_group >= G) continue;
         const float m = hh ? m1 : m0, l = hh ? l1 : l0;
-        const float inv = 1.0f / l;
-        const float lse = (m + log2f(l)) * kLn2;
+        // l == 0 only when every tile of the range was skipped (flagged page-table entries): O = 0, LSE = -inf
+        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        const float lse = l > 0.f ? (m + log2f(l)) * kLn2 : -INFINITY;
         const int64_t out_row = (int64_t)seq * p.q_heads + kv_head * G + head_in_group;
         float vals[kDims];
 #pragma unroll

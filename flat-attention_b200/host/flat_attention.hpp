@@ -130,6 +130,13 @@ inline flat_forward_layout forward_layout(DType dtype, const AttentionShape &sha
     if (st) throw Error(st, "");
     return out;
 }
+// ResidentDecodeLayout / PagedDecodeLayout (src/wgpu_decode.rs:437-455, src/wgpu_paged_decode.rs:268-283)
+inline flat_decode_layout decode_layout(DType dtype, uint64_t batch, uint64_t q_heads, uint64_t head_dim) {
+    flat_decode_layout out{};
+    int32_t st = flat_decode_layout_for(static_cast<int32_t>(dtype), batch, q_heads, head_dim, &out);
+    if (st) throw Error(st, flat_status_str(st));
+    return out;
+}
 inline flat_backward_layout backward_layout(DType dtype, const AttentionShape &shape) {
     flat_backward_layout out{};
     int32_t st = flat_backward_layout_for(static_cast<int32_t>(dtype), &shape, &out);
@@ -400,6 +407,9 @@ struct ResidentDecodePass {
 class CudaResidentDecodePipeline {
   public:
     CudaResidentDecodePipeline(const Context &ctx, DType dtype) : ctx_(ctx), dtype_(dtype) {}
+    static flat_decode_layout layout(DType dtype, uint64_t batch, uint64_t q_heads, uint64_t head_dim) {
+        return decode_layout(dtype, batch, q_heads, head_dim);
+    }
     void encode_external_pre_rotated_k(const ResidentDecodePass &p, uint64_t kv_capacity) const {
         auto cfg = p.config.raw();
         ctx_.check(flat_decode_resident(ctx_.raw(), static_cast<int32_t>(dtype_), p.batch, p.q_heads, p.kv_heads, p.head_dim,
@@ -423,6 +433,9 @@ struct PagedDecodePass {
 class CudaPagedDecodePipeline {
   public:
     CudaPagedDecodePipeline(const Context &ctx, DType dtype) : ctx_(ctx), dtype_(dtype) {}
+    static flat_decode_layout layout(DType dtype, uint64_t q_heads, uint64_t head_dim) {
+        return decode_layout(dtype, 1, q_heads, head_dim);
+    }
     void encode(const PagedDecodePass &p) const {
         auto cfg = p.config.raw();
         ctx_.check(flat_decode_paged(ctx_.raw(), static_cast<int32_t>(dtype_), p.page_table, p.q_heads, p.kv_heads, p.head_dim,

@@ -184,7 +184,9 @@ typedef struct flat_resident_kv_cache flat_resident_kv_cache;
  * cudaStream_t (NULL = legacy default stream); the caller owns it, like the wgpu queue. */
 int32_t flat_ctx_create(int32_t device, void *stream, flat_ctx **out);
 void flat_ctx_destroy(flat_ctx *ctx);
-/* Replace the stream later launches are enqueued on. */
+/* Replace the stream later launches are enqueued on.  The new stream is made to wait (on the
+ * device, by an event) for everything the context queued on the old one, because consecutive
+ * calls share the context's scratch; the host is not blocked. */
 int32_t flat_ctx_set_stream(flat_ctx *ctx, void *stream);
 const char *flat_status_str(int32_t status);
 /* Human-readable detail of the last error on this context (tensor name, actual/expected
@@ -196,8 +198,9 @@ int32_t flat_ctx_reserve_workspace(flat_ctx *ctx, uint64_t bytes);
 uint64_t flat_ctx_workspace_bytes(const flat_ctx *ctx);
 /* Number of kernel launches this context has enqueued since creation. */
 uint64_t flat_ctx_launch_count(const flat_ctx *ctx);
-/* Reads the device status word written by bounded waits (FLAT_OK or
- * FLAT_ERR_DEVICE_WAIT_TIMEOUT); synchronises the stream. */
+/* Reads the device status word written by kernels: FLAT_OK, FLAT_ERR_DEVICE_WAIT_TIMEOUT (a
+ * bounded wait gave up) or FLAT_ERR_PAGE_OUT_OF_RANGE (a decode kernel met a page-table entry
+ * outside the pool and masked its tokens); synchronises the stream and clears the word. */
 int32_t flat_ctx_device_status(flat_ctx *ctx);
 
 /* Kernel timing for benchmarks (the reference benches time encode+submit+poll on the host,
@@ -303,9 +306,12 @@ int32_t flat_forward_projection_rope_varlen(flat_ctx *ctx, int32_t dtype,
  * (src/wgpu_backend.rs:445-463, src/wgpu_grouped_backend.rs:126-146,
  * src/wgpu_rotary_grouped_backend.rs:117-139): host slices in, host [O | LSE] out.  Validates
  * like validate_input (src/lib.rs:428-447: exact element counts, and with check_finite != 0 the
- * first non-finite element by tensor name and index), uploads into staging owned by the context,
- * launches the forward of `layout` (with RoPE when rotary != NULL, rectangular shapes allowed),
- * downloads and blocks.  Pinned host memory makes the copies asynchronous to the host. */
+ * first non-finite element of Q, then K, then V, by tensor name and index), uploads into staging
+ * owned by the context, launches the forward of `layout` (with RoPE when rotary != NULL,
+ * rectangular shapes allowed), downloads and blocks.  The finiteness scan runs on the device,
+ * chunk by chunk as the upload lands, and its verdict is read back once before the call returns:
+ * a call that returns FLAT_ERR_NON_FINITE_INPUT has no result (the contents of out_and_lse are
+ * then unspecified).  Pinned host memory makes the copies asynchronous to the host. */
 int32_t flat_forward_host(flat_ctx *ctx, int32_t dtype, int32_t layout, const flat_attention_shape *shape,
                           const flat_attention_config *config, const flat_rotary_config *rotary,
                           const void *q, uint64_t q_elements, const void *k, uint64_t k_elements,
@@ -376,6 +382,28 @@ flat_buffer flat_resident_kv_cache_v_buffer(const flat_resident_kv_cache *cache)
 
 /* ---- decode -------------------------------------------------------------------------- */
 
+/* ResidentDecodeLayout / PagedDecodeLayout (src/wgpu_decode.rs:437-455,
+ * src/wgpu_paged_decode.rs:221-235) of the packed decode output
+ * [O(batch*q_heads*head_dim) | LSE(batch*q_heads)]: O in `dtype`, LSE f32 at lse_byte_offset
+ * (= q_bytes rounded up to 4).  combined_elements counts values (O and LSE together), the
+ * reference's f32 element count. */
+typedef struct flat_decode_layout {
+    uint64_t q_elements;
+    uint64_t output_elements;
+    uint64_t lse_elements;
+    uint64_t combined_elements;
+    uint64_t q_bytes;
+    uint64_t lse_byte_offset;
+    uint64_t combined_bytes;
+} flat_decode_layout;
+/* WgpuResidentDecodePipeline::layout / WgpuPagedDecodePipeline::layout
+ * (src/wgpu_decode.rs:245-261, src/wgpu_paged_decode.rs:268-283): pure, allocation-free.  `batch`
+ * is the number of decoded rows (1 for the single-sequence paged pipeline, num_seqs for the
+ * batched entry points).  Errors: ZERO_DIMENSION, INVALID_ROTARY_HEAD_DIM (odd head_dim),
+ * UNSUPPORTED_HEAD_DIM (> 128), SHAPE_OVERFLOW. */
+int32_t flat_decode_layout_for(int32_t dtype, uint64_t batch, uint64_t q_heads, uint64_t head_dim,
+                               flat_decode_layout *out);
+
 /* WgpuResidentDecodePipeline::encode_external_pre_rotated_k (src/wgpu_decode.rs:263-322,
  * 419-435): q_len = 1 per batch row over [batch, kv_capacity, kv_heads*head_dim] with live
  * prefix kv_len; Q [batch, q_heads*head_dim] is raw and rotated at q_rope_position, K is
@@ -444,16 +472,24 @@ int32_t flat_splitkv_merge_packed(flat_ctx *ctx, int32_t dtype, uint64_t parts, 
  * counterpart in the reference.  The per-chunk (O, LSE) partials live in an 8 MiB array that
  * is part of the library image (every GPU that loads the library holds it until exit) instead
  * of the growable context workspace; the call issues no cudaMalloc / cudaFree.
- *  - limit: kv_splits * num_seqs * q_heads * (head_dim + 1) * 4 bytes <= 8 MiB with at least two
- *    chunks, head_dim a multiple of 16 bytes and a query-head group of 1, 2, 4 or 8; anything
- *    else is refused with FLAT_ERR_UNSUPPORTED_SHAPE and a message giving both sizes.
- *    kv_splits = 0 picks a split that fits.
- *  - the first call on a device looks the array's device address up once
+ *  - limit: kv_splits * num_seqs * q_heads * (head_dim + 1) * 4 bytes <= 8 MiB, head_dim a
+ *    multiple of 16 bytes, a query-head group of 1, 2, 4 or 8 and 16-byte aligned buffers; an
+ *    explicit kv_splits beyond the limit is refused with FLAT_ERR_UNSUPPORTED_SHAPE and a message
+ *    giving both sizes.  kv_splits = 0 picks a split that fits.  Whenever the plan comes down to a
+ *    single chunk (short contexts, kv_splits = 1, or an explicit split that the 64-token chunk
+ *    rounding collapses) the kernel writes O and LSE directly and the array is not touched, so
+ *    the first tokens of a sequence decode through this entry point as well.
+ *  - the first call on a device that needs the array looks its device address up once
  *    (cudaGetSymbolAddress); make that first call before any stream capture.
  *  - all calls on a device share the array and it keeps the previous call's partials; nothing
  *    in it needs clearing (every live chunk is written before it is read), but two calls that
  *    overlap on the GPU (different streams) race on it.
- *  - page-sharing between sequences is not checked here (that check needs host memory). */
+ *  - arguments are validated like flat_decode_paged_batched (same helper).  There is no host
+ *    copy of the page tables here, so sharing of a page between sequences is not checked, and
+ *    entries are range-checked on the device instead: an entry outside [0, physical_pages) is
+ *    never dereferenced, its tokens are left out of the softmax, and flat_ctx_device_status
+ *    then returns FLAT_ERR_PAGE_OUT_OF_RANGE (the regular entry points do the same when they
+ *    are called without host_page_tables). */
 int32_t flat_decode_paged_batched_static_scratch(
     flat_ctx *ctx, int32_t dtype, uint64_t num_seqs, uint64_t q_heads, uint64_t kv_heads,
     uint64_t head_dim, uint64_t page_size, uint64_t physical_pages, uint64_t max_pages_per_seq,

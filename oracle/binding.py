@@ -240,6 +240,22 @@ def forward_rows(q, k, v, shape: Shape, layout, rows, causal=False, softmax_scal
     return out, lse
 
 
+def forward_rows_alibi(q, k, v, shape: Shape, layout, rows, slopes, bias_q_offset=0, bias_kv_offset=0, causal=False,
+                       softmax_scale=None, threads=1):
+    """forward_rows with an ALiBi score bias (one slope per query head); no RoPE (materialise it first)."""
+    q, k, v, slopes = _f32(q), _f32(k), _f32(v), _f32(slopes)
+    assert slopes.size == shape.q_heads
+    rows = np.ascontiguousarray(np.array(rows, dtype=np.uint64).reshape(-1, 3))
+    n = rows.shape[0]
+    out = np.empty((n, shape.head_dim), np.float32)
+    lse = np.empty(n, np.float32)
+    cfg = make_config(causal, softmax_scale)
+    _check(lib().flat_oracle_forward_rows_alibi(_p(q), _p(k), _p(v), C.byref(shape), C.c_int32(layout), C.byref(cfg),
+                                                _p(slopes), C.c_uint64(bias_q_offset), C.c_uint64(bias_kv_offset),
+                                                _u64p(rows), C.c_uint64(n), C.c_int32(threads), _p(out), _p(lse)))
+    return out, lse
+
+
 def backward_units(q, k, v, d_out, fwd_out, fwd_lse, batch, q_heads, kv_heads, seq_len, head_dim,
                    units, causal=False, softmax_scale=None, threads=1):
     """Oracle backward for whole (batch, kv_head) units."""

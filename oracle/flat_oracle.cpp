@@ -579,6 +579,41 @@ int32_t flat_oracle_forward_rows(const float *q, const float *k, const float *v,
     return FLAT_OK;
 }
 
+// The same row sampling with an ALiBi score bias (AttentionBias::Alibi, src/attention_bias.rs:82-95): slopes holds
+// one f32 per query head, bias positions start at bias_q_offset / bias_kv_offset.  No RoPE here either: with the
+// rotation materialised first the rows are bit-identical to flat_oracle_forward_projection_rope_asymmetric_biased.
+int32_t flat_oracle_forward_rows_alibi(const float *q, const float *k, const float *v,
+                                       const flat_attention_shape *shape, int32_t layout,
+                                       const flat_attention_config *cfg, const float *slopes,
+                                       uint64_t bias_q_offset, uint64_t bias_kv_offset, const uint64_t *rows,
+                                       uint64_t row_count, int32_t threads, float *out_rows, float *lse_rows) {
+    Shape s = to_shape(shape);
+    int st = validate_shape(s);
+    if (st) return st;
+    float scale;
+    if ((st = resolved_scale(cfg->has_softmax_scale, cfg->softmax_scale, s.head_dim, &scale))) return st;
+    const usize group = s.q_heads / s.kv_heads;
+    const usize kv_stride = layout == FLAT_LAYOUT_HEAD_MAJOR ? s.head_dim : s.kv_heads * s.head_dim;
+    run_parallel(row_count, threads, [&](usize i) {
+        const usize batch = rows[3 * i], q_head = rows[3 * i + 1], query_pos = rows[3 * i + 2];
+        const usize kv_head = q_head / group;
+        usize key_count = s.kv_len, absolute = s.query_position_offset + query_pos;
+        if (cfg->causal && absolute + 1 < key_count) key_count = absolute + 1;
+        Rope rope;
+        rope.on = false;
+        RowBias rb;
+        rb.mode = 2;
+        rb.slope = slopes[q_head];
+        rb.query_position = bias_q_offset + query_pos;
+        rb.kv_offset = bias_kv_offset;
+        const float *q_row = q + row_base(layout, batch, q_head, query_pos, s.q_heads, s.query_len, s.head_dim);
+        const float *k0 = k + row_base(layout, batch, kv_head, 0, s.kv_heads, s.kv_len, s.head_dim);
+        const float *v0 = v + row_base(layout, batch, kv_head, 0, s.kv_heads, s.kv_len, s.head_dim);
+        attend_row(q_row, k0, v0, kv_stride, key_count, s.head_dim, scale, rope, out_rows + i * s.head_dim, lse_rows + i, &rb);
+    });
+    return FLAT_OK;
+}
+
 // Backward for whole (batch, kv_head) units: dK/dV need every query row of the unit.  units holds
 // `unit_count` (batch, kv_head) pairs; dq_units is [unit_count, group, seq_len, head_dim], dk/dv
 // are [unit_count, seq_len, head_dim].  Loop order inside a unit is the reference's

@@ -86,6 +86,56 @@ def test_chunked_prefill_into_growing_paged_cache(dtype, Hq, Hkv, D, N, chunk, p
             assert_close("LSE", l, el, 2e-3, 0.0)
 
 
+def test_config4_chunked_prefill_full_size_sampled_rows():
+    """One sequence of 32768 tokens fed in 2048-token chunks into the growing paged cache (page 16), Hq=64,
+    Hkv=8, D=128, causal, bf16, theta 5e5: 16 launches with up to 256 KV tiles and 2048 pages per work item.
+    Per chunk the oracle (no-RoPE rectangular rows on the cache contents as stored, Q rotation materialised)
+    checks the first and last row, the rows either side of a tile border (127/128) and of a page border (15/16)
+    and random rows, each on sampled query heads."""
+    c = ctx()
+    Hq, Hkv, D, N, chunk, ps, theta = 64, 8, 128, 32768, 2048, 16, 5e5
+    q = torch.randn(N, Hq * D, generator=torch.Generator().manual_seed(31)).bfloat16()
+    k = torch.randn(N, Hkv * D, generator=torch.Generator().manual_seed(32)).bfloat16()
+    v = torch.randn(N, Hkv * D, generator=torch.Generator().manual_seed(33)).bfloat16()
+    cache = fa.CudaPagedKvCache(c, fa.BF16, ps, N // ps + 8, Hkv, D)
+    out = c.empty_bytes(chunk * Hq * D * 2 + Hq * chunk * 4)
+    rng = np.random.default_rng(4)
+    picked = []  # (chunk start, [(head, row)], O rows, LSE values)
+    for start in range(0, N, chunk):
+        c.chunked_prefill_paged(cache, Hq, chunk, fa.config(True), theta, 0, q[start:start + chunk].cuda(),
+                                k[start:start + chunk].cuda(), v[start:start + chunk].cuda(), out)
+        rows = [0, 15, 16, 127, 128, chunk - 1] + [int(r) for r in rng.integers(0, chunk, 3)]
+        pairs = [(int(rng.integers(Hq)), r) for r in rows] + [(Hq - 1, chunk - 1), (0, 0)]
+        o = out[:chunk * Hq * D * 2].view(torch.bfloat16).view(chunk, Hq, D)
+        l = out[chunk * Hq * D * 2:].view(torch.float32).view(Hq, chunk)
+        picked.append((start, pairs, torch.stack([o[r, h] for (h, r) in pairs]).float().cpu().numpy(),
+                       np.array([float(l[h, r]) for (h, r) in pairs], np.float32)))
+    c.synchronize()
+    assert c.device_status() == 0
+    assert len(cache) == N
+    K, V = cache.download()
+    tab = cache.table()
+    entries = np.array(tab.export(), np.int64)
+    rows = (entries[:, None] * ps + np.arange(ps)[None, :]).reshape(-1)[:N]
+    k_cache, v_cache = K.float().numpy()[rows], V.float().numpy()[rows]
+    assert np.array_equal(v_cache, v.float().numpy())
+    some = np.array([0, 1, 15, 16, 2047, 2048, N - 1] + [int(r) for r in rng.integers(0, N, 32)])
+    k_rot = ob.rotate_rows(k.float().numpy()[some], D, np.repeat(some.astype(np.uint64), Hkv), theta).reshape(len(some), Hkv * D)
+    assert_close("cached K", k_cache[some], k_rot, 0.0, 2.0 ** -7)
+    qf = q.float().numpy()
+    worst_o = worst_l = 0.0
+    for start, pairs, ao, al in picked:
+        kv_len = start + chunk
+        rq = qf[start:start + chunk].reshape(chunk, Hq, D).copy()
+        for (h, r) in pairs:
+            rq[r, h] = ob.rotate_rows(rq[r, h], D, [start + r], theta)
+        eo, el = ob.forward_rows(rq, k_cache[:kv_len], v_cache[:kv_len], ob._shape(1, Hq, Hkv, chunk, kv_len, D, start),
+                                 ob.PROJECTION, [(0, h, r) for (h, r) in pairs], True, threads=8)
+        worst_o = max(worst_o, float(np.abs(ao - eo).max()))
+        worst_l = max(worst_l, float(np.abs(al - el).max()))
+    assert worst_o <= 2e-2 and worst_l <= 2e-3, (worst_o, worst_l)
+
+
 # ---- backward -----------------------------------------------------------------------------------
 def run_backward(dtype, B, Hq, Hkv, N, D, causal, scale, q, k, v, do, fo, fl, mha=False):
     c = ctx()

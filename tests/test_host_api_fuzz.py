@@ -86,6 +86,42 @@ def test_layout_functions_never_crash_and_match_the_model():
     assert lib.flat_forward_layout_for(C.c_int32(0), None, C.byref(fa.ForwardLayout())) == 27
 
 
+def test_decode_layout_fuzz_matches_the_model():
+    """flat_decode_layout_for (the *DecodePipeline::layout functions, src/wgpu_paged_decode.rs:268-283): hostile
+    geometry gives a typed status that agrees with a big-integer model; valid geometry gives the packed offsets."""
+    rng = XorShift(0x0DEC_0DE5_EED5_1234)
+    lib = fa.lib()
+    seen = set()
+    for _ in range(2048):
+        batch, hq, d = hostile(rng), hostile(rng), hostile(rng)
+        dtype = rng.next() % 2
+        out = fa.DecodeLayout()
+        st = lib.flat_decode_layout_for(C.c_int32(dtype), C.c_uint64(batch), C.c_uint64(hq), C.c_uint64(d), C.byref(out))
+        kind = fa.STATUS.get(st)
+        if 0 in (batch, hq, d):
+            want = "ZeroDimension"
+        elif d % 2:
+            want = "InvalidRotaryHeadDim"
+        elif d > 128:
+            want = "UnsupportedHeadDim"
+        elif batch * hq > U64 or batch * hq * d > U64 or batch * hq * (d + 1) > U64 or batch * hq * d > 1 << 46:
+            want = "ShapeOverflow"
+        else:
+            want = "OK"
+        assert kind == want, (batch, hq, d, kind, want)
+        seen.add(kind)
+        if st == 0:
+            es = 4 if dtype == 0 else 2
+            assert out.q_elements == out.output_elements == batch * hq * d and out.lse_elements == batch * hq
+            assert out.combined_elements == batch * hq * (d + 1) and out.q_bytes == batch * hq * d * es
+            assert out.lse_byte_offset == (out.q_bytes + 3) // 4 * 4 and out.combined_bytes == out.lse_byte_offset + 4 * batch * hq
+    assert {"OK", "ZeroDimension", "ShapeOverflow", "UnsupportedHeadDim", "InvalidRotaryHeadDim"} <= seen
+    assert lib.flat_decode_layout_for(C.c_int32(2), C.c_uint64(1), C.c_uint64(1), C.c_uint64(2), C.byref(fa.DecodeLayout())) == 26
+    assert lib.flat_decode_layout_for(C.c_int32(0), C.c_uint64(1), C.c_uint64(1), C.c_uint64(2), None) == 27
+    L = fa.decode_layout(fa.BF16, 64, 32, 128)  # the paged-decode benchmark shape
+    assert (L.q_bytes, L.lse_byte_offset, L.combined_bytes) == (64 * 32 * 128 * 2, 64 * 32 * 128 * 2, 64 * 32 * 128 * 2 + 64 * 32 * 4)
+
+
 def test_paged_table_fuzz_never_crashes():
     rng = XorShift(0x1357_9BDF_2468_ACE0)
     lib = fa.lib()
@@ -126,6 +162,9 @@ def test_null_context_is_an_error_not_a_crash():
                                            C.c_uint64(0), None, C.c_uint64(0), None) == 27
     assert lib.flat_numerical_forward_host(None, C.c_int32(1), C.byref(shp), C.byref(cfg), None, C.c_uint64(0), None,
                                            C.c_uint64(0), None, C.c_uint64(0), None, C.c_uint64(0)) == 27
+    assert lib.flat_decode_paged_batched_static_scratch(
+        None, C.c_int32(1), C.c_uint64(1 << 62), C.c_uint64(1 << 62), C.c_uint64(1 << 62), C.c_uint64(64), C.c_uint64(16),
+        C.c_uint64(1), C.c_uint64(1), None, None, None, None, None, C.byref(cfg), C.c_float(1e4), C.c_uint32(0), z, z, z, z) == 27
     assert lib.flat_ctx_device_fingerprint(None, None) == 27 and lib.flat_ctx_device_capabilities(None, None) == 27
     assert lib.flat_benchmark_manifest_validate(None, None) == 27
     lib.flat_benchmark_manifest_canonical_json.restype = C.c_int64

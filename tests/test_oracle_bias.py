@@ -114,3 +114,25 @@ def test_alibi_against_two_pass_softmax():
                 p = np.exp(sc - m)
                 assert np.abs(out[b, i, h] - (p / p.sum()) @ vv[b, h // 2, :keys]).max() <= 2e-5
                 assert abs(lse[b, h, i] - (m + np.log(p.sum()))) <= 2e-5
+
+
+def test_alibi_row_sampling_is_bitwise_identical_to_the_full_biased_oracle():
+    """forward_rows_alibi (the sampled-row route the large-shape parity gates use) against the full biased oracle:
+    with the rotation materialised first the sampled rows carry the same bits."""
+    s = ob.Shape(2, 4, 2, 6, 9, 8, 3)
+    q, k, v = fixture(2 * 6 * 4 * 8, 0.3), fixture(2 * 9 * 2 * 8, 0.9), fixture(2 * 9 * 2 * 8, 1.7)
+    slopes = np.array([0.5, -0.25, 0.125, 0.0625], np.float32)
+    theta, q_off, kv_off = 10000.0, 11, 4
+    for causal in (False, True):
+        fo, fl = ob.forward_reference_projection_grouped_rope_asymmetric_biased(q, k, v, s, theta, q_off, kv_off, causal=causal,
+                                                                               alibi=(slopes, 7, 2))
+        qpos = np.repeat(np.tile(np.arange(6, dtype=np.uint64) + q_off, 2), 4)
+        kpos = np.repeat(np.tile(np.arange(9, dtype=np.uint64) + kv_off, 2), 2)
+        rq, rk = ob.rotate_rows(q, 8, qpos, theta), ob.rotate_rows(k, 8, kpos, theta)
+        rows = [(b, h, r) for b in range(2) for h in range(4) for r in range(6)]
+        ro, rl = ob.forward_rows_alibi(rq, rk, v, s, ob.PROJECTION, rows, slopes, 7, 2, causal=causal, threads=2)
+        full_o = fo.reshape(2, 6, 4, 8)
+        full_l = fl.reshape(2, 4, 6)
+        for i, (b, h, r) in enumerate(rows):
+            assert np.array_equal(bits(ro[i]), bits(full_o[b, r, h])), (causal, b, h, r)
+            assert bits(rl[i:i + 1])[0] == bits(full_l[b, h, r:r + 1])[0]
