@@ -178,7 +178,7 @@ def oracle_rows_c2(ob, np, q, k, v, rows, threads):
     qf, kf, vf = q.float().numpy(), k.float().numpy(), v.float().numpy()
     rk = ob.rotate_rows(kf, D, np.tile(np.arange(N, dtype=np.uint64), B * Hkv), theta)
     rq = qf.reshape(B, Hq, N, D).copy()
-    for (b, h, r) in rows:
+    for (b, h, r) in dict.fromkeys(rows):  # a row listed twice is still rotated once
         rq[b, h, r] = ob.rotate_rows(rq[b, h, r], D, [r], theta)
     t0 = time.perf_counter()
     eo, el = ob.forward_rows(rq, rk, vf, ob._shape(B, Hq, Hkv, N, N, D), ob.HEAD_MAJOR, rows, True, threads=threads)
@@ -465,12 +465,12 @@ def c2_rows_oracle(ob, np, q, k, v, rows, layout, threads, slopes=None):
     if layout == ob.HEAD_MAJOR:
         rk = ob.rotate_rows(k, D, np.tile(np.arange(N, dtype=np.uint64), B * Hkv), theta).reshape(B, Hkv, N, D)
         rq = q.reshape(B, Hq, N, D).copy()
-        for (b, h, r) in rows:
+        for (b, h, r) in dict.fromkeys(rows):  # a row listed twice is still rotated once
             rq[b, h, r] = ob.rotate_rows(rq[b, h, r], D, [r], theta)
     else:
         rk = ob.rotate_rows(k, D, np.repeat(np.tile(np.arange(N, dtype=np.uint64), B), Hkv), theta).reshape(B, N, Hkv, D)
         rq = q.reshape(B, N, Hq, D).copy()
-        for (b, h, r) in rows:
+        for (b, h, r) in dict.fromkeys(rows):
             rq[b, r, h] = ob.rotate_rows(rq[b, r, h], D, [r], theta)
     if slopes is None:
         return ob.forward_rows(rq, rk, v, shp, layout, rows, True, threads=threads)
@@ -581,7 +581,7 @@ def bench_chunked_prefill(torch, np, fa, ctx, peaks, warmup, ob=None, device_ind
     if ob is not None:
         # oracle gate: first, middle and last chunk; first / last row, a tile border and a page border, random rows
         rng = np.random.default_rng(14)
-        capture = {st: [(int(rng.integers(Hq)), r) for r in (0, 15, 16, 127, 128, chunk - 1, int(rng.integers(chunk)))]
+        capture = {st: list(dict.fromkeys((int(rng.integers(Hq)), r) for r in (0, 15, 16, 127, 128, chunk - 1, int(rng.integers(chunk)))))
                    for st in (0, 7 * chunk, N - chunk)}
         run(capture)
         torch.cuda.synchronize()
@@ -662,11 +662,18 @@ def bench_splitkv_128k(torch, np, dist, fa, ctx, peaks, rank, world, steps, warm
                 q_rope_positions_dev=torch.from_numpy(qpos).cuda(), host_page_tables=None, host_context_lens=lens,
                 cfg=fa.config(True), theta=theta, q=Q, k=K, v=V)
     out = ctx.create_decode_output_buffer(fa.BF16, 1, Hq, D)
-    partial = torch.empty(Hq * (D + 1), dtype=torch.float32, device="cuda")
+    block = Hq * (D + 1)
+    gathered = torch.empty(world * block, dtype=torch.float32, device="cuda")
+    partial = gathered[rank * block:(rank + 1) * block]  # this rank's block of the gather buffer (in-place all-gather)
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    dist.barrier()  # the communicator exists once the group has run a collective
+    comm = fd.nccl_comm_ptr()
+    abi = {k: v for k, v in args.items() if k not in ("cfg", "theta", "q", "k", "v")}
 
     def step():
-        return fd.splitkv_decode(ctx, fa, fa.BF16, args, Hq, D, out)
+        # the whole step through the C ABI: partial, in-place ncclAllGather, local merge
+        ctx.splitkv_decode_nccl(comm, rank, world, fa.BF16, cfg=args["cfg"], theta=theta, q=Q, k=K, v=V, gathered=gathered,
+                                out=out, **abi)
     for _ in range(warmup):
         step()
 
@@ -746,8 +753,7 @@ def bench_splitkv_128k(torch, np, dist, fa, ctx, peaks, rank, world, steps, warm
         e0.record()
         ctx.decode_paged_batched_partial(fa.BF16, out=partial, **args)
         e1.record()
-        gathered = fd.all_gather_partials(partial)
-        ctx.splitkv_merge_packed(fa.BF16, world, Hq, D, gathered, out)
+        ctx.splitkv_merge_nccl(comm, rank, world, fa.BF16, Hq, D, gathered, out)
         e2.record()
         torch.cuda.synchronize()
         tot += e0.elapsed_time(e2)
@@ -767,7 +773,8 @@ def bench_splitkv_128k(torch, np, dist, fa, ctx, peaks, rank, world, steps, warm
                          "frac": per_gpu_gbs / peaks["hbm_gbs"], "kernel": "decode_mma_kernel<128> (one rank's slice)",
                          "kernel_ms": kernel_ms, "peak_source": peaks["source"]},
             "kv_bytes_total": kv_bytes, "gathered_bytes": world * Hq * (D + 1) * 4, "parity": parity,
-            "workload": "1 sequence x 131072 tokens, Hq=64 Hkv=8 D=128 bf16, page 16, KV split over %d GPUs, NCCL all-gather; "
+            "workload": "1 sequence x 131072 tokens, Hq=64 Hkv=8 D=128 bf16, page 16, KV split over %d GPUs, in-place ncclAllGather "
+                        "issued by the library (flat_splitkv_merge_nccl); "
                         "ms_per_step = partial + gather + merge between CUDA events, max over ranks; partial_kernel_ms = the "
                         "decode kernel alone" % world}
 

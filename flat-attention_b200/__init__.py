@@ -403,6 +403,25 @@ class Context:
             C.c_void_p(q_rope_positions_dev.data_ptr()), ip(host_page_tables), ip(host_context_lens), C.byref(cfg),
             C.c_float(theta), buf(q), _b(k), _b(v), buf(out)))
 
+    def splitkv_decode_nccl(self, comm_ptr: int, rank: int, world: int, dtype, num_seqs, q_heads, kv_heads, head_dim,
+                            page_size, physical_pages, max_pages_per_seq, page_tables_dev, context_lens_dev,
+                            q_rope_positions_dev, host_page_tables, host_context_lens, cfg, theta, q, k, v, gathered, out):
+        """One KV-split decode step over an NCCL communicator (`comm_ptr` = the ncclComm_t as an integer): partial of
+        this rank's slice into its block of `gathered`, in-place all-gather, local merge.  Enqueues only."""
+        def ip(a):
+            return None if a is None else a.ctypes.data_as(C.POINTER(C.c_int32))
+        self.check(lib().flat_splitkv_decode_nccl(
+            self.h, C.c_void_p(comm_ptr), C.c_int32(rank), C.c_int32(world), C.c_int32(dtype), C.c_uint64(num_seqs),
+            C.c_uint64(q_heads), C.c_uint64(kv_heads), C.c_uint64(head_dim), C.c_uint64(page_size), C.c_uint64(physical_pages),
+            C.c_uint64(max_pages_per_seq), C.c_void_p(page_tables_dev.data_ptr()), C.c_void_p(context_lens_dev.data_ptr()),
+            C.c_void_p(q_rope_positions_dev.data_ptr()), ip(host_page_tables), ip(host_context_lens), C.byref(cfg),
+            C.c_float(theta), buf(q), _b(k), _b(v), buf(gathered), buf(out)))
+
+    def splitkv_merge_nccl(self, comm_ptr: int, rank: int, world: int, dtype, rows, head_dim, gathered, out):
+        self.check(lib().flat_splitkv_merge_nccl(self.h, C.c_void_p(comm_ptr), C.c_int32(rank), C.c_int32(world),
+                                                 C.c_int32(dtype), C.c_uint64(rows), C.c_uint64(head_dim), buf(gathered),
+                                                 buf(out)))
+
     def splitkv_merge_packed(self, dtype, parts, rows, head_dim, gathered, out):
         self.check(lib().flat_splitkv_merge_packed(self.h, C.c_int32(dtype), C.c_uint64(parts), C.c_uint64(rows),
                                                    C.c_uint64(head_dim), buf(gathered), buf(out)))

@@ -272,7 +272,7 @@ int forward_common(flat_ctx *ctx, const ForwardCall &call, const flat_attention_
         // the metadata sits at the start of the workspace: size it for the kernel first, a later growth would move it
         p.varlen = reinterpret_cast<const flat_varlen_sequence *>(call.varlen_host);  // non-null for the capability test
         const bool tensor_path = storage16(call.dtype) && forward_sm100_supported(p);
-        if ((st = ensure_workspace(ctx, kWorkspaceMeta + (tensor_path ? forward_sm100_workspace_bytes(p) : 0)))) return st;
+        if ((st = ensure_workspace(ctx, kWorkspaceMeta + (tensor_path ? forward_sm100_workspace_bytes(ctx, p) : 0)))) return st;
         ctx->plan_offsets_at = nullptr;  // the metadata may reach into the part that holds a cached decode plan
         FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ctx->workspace, call.varlen_host, bytes, cudaMemcpyHostToDevice, ctx->stream));
         p.varlen = static_cast<const flat_varlen_sequence *>(ctx->workspace);
@@ -286,7 +286,7 @@ int forward_common(flat_ctx *ctx, const ForwardCall &call, const flat_attention_
         for (uint64_t i = 0; i < call.alibi_count; ++i)
             p.alibi_max_abs_slope = std::max(p.alibi_max_abs_slope, std::fabs(call.alibi_slopes[i]));
         const bool tensor_path = storage16(call.dtype) && forward_sm100_supported(p);
-        if ((st = ensure_workspace(ctx, kWorkspaceMeta + (tensor_path ? forward_sm100_workspace_bytes(p) : 0)))) return st;
+        if ((st = ensure_workspace(ctx, kWorkspaceMeta + (tensor_path ? forward_sm100_workspace_bytes(ctx, p) : 0)))) return st;
         FLAT_CUDA_OK(ctx, cudaMemcpyAsync(ctx->workspace, call.alibi_slopes, call.alibi_count * sizeof(float),
                                           cudaMemcpyHostToDevice, ctx->stream));
         p.alibi_slopes = static_cast<const float *>(ctx->workspace);
@@ -824,7 +824,7 @@ int32_t flat_forward_runtime_telemetry(flat_ctx *ctx, int32_t dtype, int32_t lay
     if (storage16(dtype) && forward_sm100_supported(p)) {
         out->kernel_id = FLAT_KERNEL_FORWARD_TCGEN05;
         forward_sm100_geometry(ctx, p, &out->query_rows, &out->kv_rows, out->workgroups, &out->dispatch_count);
-        out->temporary_allocation_bytes = forward_sm100_workspace_bytes(p);
+        out->temporary_allocation_bytes = forward_sm100_workspace_bytes(ctx, p);
         out->temporary_allocation_count = out->temporary_allocation_bytes ? 1 : 0;
         return FLAT_OK;
     }

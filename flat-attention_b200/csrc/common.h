@@ -154,7 +154,7 @@ void forward_sm100_geometry(const flat_ctx *ctx, const FwdParams &p, uint32_t *q
 // tcgen05 forward for bf16, head_dim 64/128; returns FLAT_ERR_UNSUPPORTED_SHAPE when the shape
 // does not fit it (the caller then uses the SIMT kernel).
 bool forward_sm100_supported(const FwdParams &p);
-uint64_t forward_sm100_workspace_bytes(const FwdParams &p);
+uint64_t forward_sm100_workspace_bytes(const flat_ctx *ctx, const FwdParams &p);
 int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p);
 
 // ---- decode ----------------------------------------------------------------------------------

@@ -97,6 +97,13 @@ struct KernelParams {
     int page_size, max_pages, physical_pages;
     int q_blocks;
     long long total_items;  // q_blocks * batch * q_heads
+    // Work distribution: `full_rounds` rounds in which every CTA takes one whole item, then one round for the
+    // `rem_items` items that are left.  When those are few, each is cut along KV into `split` parts that run on
+    // different CTAs (a part writes its unnormalised O, running max and sum to part_o / part_ml; a merge kernel
+    // finishes the rows), so the last round keeps every SM busy instead of a fraction of them.
+    int full_rounds, rem_items, split;
+    float *part_o;    // [rem_items * split][256 rows][D] f32, unnormalised
+    float2 *part_ml;  // [rem_items * split][256 rows] (running max in the log2 domain, running sum)
     DeviceStatus *status;
     const flat_varlen_sequence *varlen;  // per batch element: active lengths, causal and RoPE offsets; null = uniform
     long long rope_table_base;           // varlen: position of the table's first row (the smallest query_rope_offset)
@@ -125,18 +132,27 @@ __device__ __forceinline__ void record_timeout(const KernelParams &p, int where)
     }
 }
 
-// One unit of work: 256 consecutive query rows of one (batch, q_head).
+// One unit of work: 256 consecutive query rows of one (batch, q_head), over all visible KV tiles or, for a split
+// item of the last round, over one contiguous part of them.
 struct WorkItem {
     int b, h, kvh, r0;
-    int n_tiles[2];  // KV tiles each of the two Q tiles visits (0 = the tile starts past q_len)
+    int n_tiles[2];  // KV tiles each of the two Q tiles visits in this item (0 = nothing to do for that tile)
+    int j0;          // first KV tile of the item (0 unless it is a part of a split item)
+    int part_slot;   // split items: index of this part's partial record; -1 = the item writes the final result
     int q_len, kv_len;     // this batch element's live rows (the call's lengths unless it is a variable-length batch)
     long long causal_off;  // key k is visible to local row q iff k <= causal_off + q
     int table_row0;        // row of the (cos, sin) table that belongs to local query row 0
 };
 
-__device__ __forceinline__ WorkItem make_item(const KernelParams &p, int lin) {
+struct ItemRef {
+    int lin;   // linear item index, -1 = none
+    int part;  // part of a split item, -1 = whole item
+};
+
+__device__ __forceinline__ WorkItem make_item(const KernelParams &p, ItemRef ref) {
     // item index -> (query block, batch, head); late (long) query blocks first
     WorkItem it;
+    const int lin = ref.lin;
     const int total_bh = p.batch * p.q_heads;
     const int qb = p.q_blocks - 1 - lin / total_bh;
     const int bh = lin % total_bh;
@@ -148,6 +164,8 @@ __device__ __forceinline__ WorkItem make_item(const KernelParams &p, int lin) {
     it.kv_len = p.kv_len;
     it.causal_off = p.causal_off;
     it.table_row0 = 0;
+    it.j0 = 0;
+    it.part_slot = -1;
     if (p.varlen) {  // padded batch: src/wgpu_external_variable.rs:21-33
         const flat_varlen_sequence m = p.varlen[it.b];
         it.q_len = (int)m.active_query_len;
@@ -165,15 +183,29 @@ __device__ __forceinline__ WorkItem make_item(const KernelParams &p, int lin) {
         }
         it.n_tiles[w] = first < it.q_len ? (int)((visible + kTileRows - 1) / kTileRows) : 0;
     }
+    if (ref.part >= 0) {
+        // part i of `split` takes KV tiles [i * n / split, (i + 1) * n / split) of the item's n
+        const int n = max(it.n_tiles[0], it.n_tiles[1]);
+        const int lo = (int)((long long)ref.part * n / p.split), hi = (int)((long long)(ref.part + 1) * n / p.split);
+        it.j0 = lo;
+#pragma unroll
+        for (int w = 0; w < 2; ++w) it.n_tiles[w] = max(0, min(it.n_tiles[w], hi) - lo);
+        it.part_slot = (lin - p.full_rounds * (int)gridDim.x) * p.split + ref.part;
+    }
     return it;
 }
 
-// The k-th item of this CTA, or -1.  Items are sorted longest first; CTAs take them in rounds of gridDim.x,
-// odd rounds in reverse CTA order, so that every CTA gets nearly the same number of KV tiles.
-__device__ __forceinline__ int item_index(const KernelParams &p, int k) {
+// The k-th item of this CTA.  Items are sorted longest first; CTAs take them in rounds of gridDim.x, odd rounds in
+// reverse CTA order, so that every CTA gets nearly the same number of KV tiles.  In the last, incomplete round
+// CTA position s works on item s mod rem_items, part s / rem_items.
+__device__ __forceinline__ ItemRef item_index(const KernelParams &p, int k) {
     const int g = (int)gridDim.x;
-    const long long idx = (long long)k * g + ((k & 1) ? g - 1 - (int)blockIdx.x : (int)blockIdx.x);
-    return idx < p.total_items ? (int)idx : -1;
+    const int s = (k & 1) ? g - 1 - (int)blockIdx.x : (int)blockIdx.x;
+    if (k < p.full_rounds) return ItemRef{k * g + s, -1};
+    if (k > p.full_rounds || p.rem_items == 0) return ItemRef{-1, -1};
+    if (p.split <= 1) return ItemRef{s < p.rem_items ? k * g + s : -1, -1};
+    const int part = s / p.rem_items;
+    return ItemRef{part < p.split ? k * g + s % p.rem_items : -1, part < p.split ? part : -1};
 }
 
 // ALIBI: the softmax warps add slope[q_head] * (key position - query position) to every scaled score
@@ -253,9 +285,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             uint32_t ring = 0;             // K/V ring entries requested so far
             uint32_t q_loads[2] = {0, 0};  // Q tiles requested so far, per slot
             for (int k = 0; ok; ++k) {
-                const int lin = item_index(p, k);
-                if (lin < 0) break;
-                const WorkItem it = make_item(p, lin);
+                const ItemRef ref = item_index(p, k);
+                if (ref.lin < 0) break;
+                const WorkItem it = make_item(p, ref);
                 const int n_max = max(it.n_tiles[0], it.n_tiles[1]);
                 for (int w = 0; w < 2 && ok; ++w) {
                     if (it.n_tiles[w] == 0) continue;
@@ -291,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     if (p.page_table) {
                         const int pages_per_tile = kTileRows / p.page_size;
                         if ((i & 1) == 0 && lane < pages_per_tile) {
-                            const int tok = j * kTileRows + lane * p.page_size;
+                            const int tok = (it.j0 + j) * kTileRows + lane * p.page_size;
                             page = tok < p.kv_len ? p.page_table[(long long)it.b * p.max_pages + tok / p.page_size]
                                                   : p.physical_pages;  // out of range: zero fill
                         }
@@ -303,7 +335,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                         }
                     } else if (lane == 0) {
                         for (int kb = 0; kb < C::kBoxes; ++kb)
-                            tma_load_4d(dst + kb * C::kBoxBytes, map, kb * 64, j * kTileRows, it.kvh, it.b, kv_full(s));
+                            tma_load_4d(dst + kb * C::kBoxBytes, map, kb * 64, (it.j0 + j) * kTileRows, it.kvh, it.b, kv_full(s));
                     }
                 }
             }
@@ -345,9 +377,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             auto phase_of = [&](uint32_t i) { return (uint32_t)(((ring0 + i) / C::kStages) & 1); };
 
             for (int k = 0; ok; ++k) {
-                const int lin = item_index(p, k);
-                if (lin < 0) break;
-                const WorkItem it = make_item(p, lin);
+                const ItemRef ref = item_index(p, k);
+                if (ref.lin < 0) break;
+                const WorkItem it = make_item(p, ref);
                 const int n_max = max(it.n_tiles[0], it.n_tiles[1]);
                 const bool trace_item = k == 0;
                 (void)trace_item;
@@ -417,9 +449,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
         bool ok = true;
         uint32_t ring = 0;
         for (int k = 0; ok; ++k) {
-            const int lin = item_index(p, k);
-            if (lin < 0) break;
-            const WorkItem it = make_item(p, lin);
+            const ItemRef ref = item_index(p, k);
+            if (ref.lin < 0) break;
+            const WorkItem it = make_item(p, ref);
             const int n_max = max(it.n_tiles[0], it.n_tiles[1]);
             for (int j = 0; ok && j < n_max; ++j, ring += 2) {
                 const int s = ring % C::kStages;
@@ -507,7 +539,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                         TRACE_FLUSH(w, j - 1);
                         TRACE_STAMP(0);
                     }
-                    const int key0 = j * kTileRows;
+                    const int key0 = (it.j0 + j) * kTileRows;
                     const bool tile_masked = key0 + kTileRows - 1 > lim_first;  // uniform over the Q tile
                     const int vis = min(kTileRows, lim - key0 + 1);             // visible columns of this row
                     const float c_log2 = p.scale_log2;
@@ -603,9 +635,10 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             }
 
             if ((warp & 3) == 0 && lane == 0) TRACEB(k, w, 0);
-            const int next_lin = item_index(p, k + 1);
+            const ItemRef next_ref = item_index(p, k + 1);
+            const int next_lin = next_ref.lin;
             if (p.rope_q_table && next_lin >= 0 && ok) {
-                const WorkItem nx = make_item(p, next_lin);
+                const WorkItem nx = make_item(p, next_ref);
                 if (nx.n_tiles[w] > 0) {
                     // Rotate the Q tile in place (bf16 in, fp16 out).  A warp rotates its 32 rows; lane l
                     // takes the 16-byte chunk (l mod CH) of row (step * RPS + l / CH), so that the (cos, sin) table is
@@ -693,6 +726,23 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                 tc_fence_after();
                 const WorkItem it = make_item(p, item_index(p, k));
                 const int row = it.r0 + w * kTileRows + row_in_tile, b = it.b, h = it.h;
+                if (it.part_slot >= 0) {
+                    // a part of a split item: unnormalised O, running max and sum go to the partial record
+                    const long long prow = (long long)it.part_slot * (2 * kTileRows) + w * kTileRows + row_in_tile;
+                    float4 *po = reinterpret_cast<float4 *>(p.part_o + prow * D);
+                    uint32_t r[32];
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) {
+                        tmem_ld32(t_o + c * 32, r);
+                        tc_wait_ld();
+#pragma unroll
+                        for (int q4 = 0; q4 < 8; ++q4)
+                            po[c * 8 + q4] = make_float4(__uint_as_float(r[q4 * 4]), __uint_as_float(r[q4 * 4 + 1]),
+                                                         __uint_as_float(r[q4 * 4 + 2]), __uint_as_float(r[q4 * 4 + 3]));
+                    }
+                    p.part_ml[prow] = make_float2(m, l);
+                    tc_fence_before();
+                } else {
                 const float inv = 1.0f / l;
                 const bool store = row < it.q_len;
                 __nv_bfloat16 *op = reinterpret_cast<__nv_bfloat16 *>(p.o) + (long long)b * p.o_bs + (long long)h * p.o_hs +
@@ -735,6 +785,12 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                 // the O columns are overwritten by the next item's first PV MMA, which is issued only after this
                 // thread's next hand-over of P: program order keeps the reads above ahead of it
                 tc_fence_before();
+                }
+            } else if (k >= 0 && ok) {
+                // a part in which this Q tile has no KV tile at all still owns a partial record: an empty one
+                const WorkItem it = make_item(p, item_index(p, k));
+                if (it.part_slot >= 0)
+                    p.part_ml[(long long)it.part_slot * (2 * kTileRows) + w * kTileRows + row_in_tile] = make_float2(-INFINITY, 0.f);
             }
             if ((warp & 3) == 0 && lane == 0) TRACEB(k, w, 4);
             if (next_lin < 0) break;
@@ -773,6 +829,56 @@ __global__ void __launch_bounds__(256) rope_table_kernel(float2 *__restrict__ ta
 
 __global__ void __launch_bounds__(256) fill_u32_kernel(uint32_t *__restrict__ dst, uint32_t value, int64_t n) {
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) dst[i] = value;
+}
+
+// Finishes the rows of the split items of the last round: for each row the parts' unnormalised O_i, running maxima
+// m_i (log2 domain) and sums l_i combine to  M = max m_i,  L = sum 2^(m_i - M) l_i,  O = sum 2^(m_i - M) O_i / L,
+// LSE = (M + log2 L) ln 2.  One CTA per item, one warp per row at a time, a lane owns D / 32 consecutive columns.
+template <int D, bool F16IO>
+__global__ void __launch_bounds__(256) fwd_split_merge_kernel(const __grid_constant__ KernelParams p, int first_lin) {
+    constexpr int kCols = D / 32;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lin = first_lin + blockIdx.x;
+    const int total_bh = p.batch * p.q_heads;
+    const int qb = p.q_blocks - 1 - lin / total_bh, bh = lin % total_bh;
+    const int b = bh / p.q_heads, h = bh % p.q_heads;
+    const int r0 = qb * 2 * kTileRows;
+    for (int rr = warp; rr < 2 * kTileRows; rr += 8) {
+        const int row = r0 + rr;
+        if (row >= p.q_len) break;
+        float mx = -INFINITY;
+        for (int i = 0; i < p.split; ++i)
+            mx = fmaxf(mx, p.part_ml[((long long)blockIdx.x * p.split + i) * (2 * kTileRows) + rr].x);
+        float acc[kCols], sum = 0.f;
+#pragma unroll
+        for (int c = 0; c < kCols; ++c) acc[c] = 0.f;
+        for (int i = 0; i < p.split; ++i) {
+            const long long prow = ((long long)blockIdx.x * p.split + i) * (2 * kTileRows) + rr;
+            const float2 ml = p.part_ml[prow];
+            if (ml.y == 0.f) continue;  // an empty part
+            const float wgt = ex2(ml.x - mx);
+            sum = fmaf(wgt, ml.y, sum);
+            const float *src = p.part_o + prow * D + lane * kCols;
+#pragma unroll
+            for (int c = 0; c < kCols; ++c) acc[c] = fmaf(wgt, src[c], acc[c]);
+        }
+        const float inv = 1.0f / sum;
+        uint16_t *op = reinterpret_cast<uint16_t *>(p.o) + (long long)b * p.o_bs + (long long)h * p.o_hs + (long long)row * p.o_rs +
+                       lane * kCols;
+#pragma unroll
+        for (int c = 0; c < kCols; c += 2) {
+            uint32_t packed;
+            if constexpr (F16IO) {
+                const __half2 h2 = __floats2half2_rn(acc[c] * inv, acc[c + 1] * inv);
+                packed = *reinterpret_cast<const uint32_t *>(&h2);
+            } else {
+                const __nv_bfloat162 h2 = __floats2bfloat162_rn(acc[c] * inv, acc[c + 1] * inv);
+                packed = *reinterpret_cast<const uint32_t *>(&h2);
+            }
+            *reinterpret_cast<uint32_t *>(op + c) = packed;
+        }
+        if (lane == 0) p.lse[((long long)b * p.q_heads + h) * p.lse_hs + row] = (mx + log2f(sum)) * kLn2;
+    }
 }
 
 // K rotation prologue: x (bf16, strided) -> y (fp16, compact [B, H, N, D]) with interleaved pairs
@@ -884,10 +990,58 @@ bool forward_sm100_supported(const FwdParams &p) {
     return true;
 }
 
-// scratch: rotated fp16 K (rope_k); the (cos, sin) tables live in the context's table cache
-uint64_t forward_sm100_workspace_bytes(const FwdParams &p) {
+namespace {
+
+// Work distribution of one launch (see KernelParams): the grid, the whole rounds, what is left for the last round and
+// into how many KV parts each of those items is cut.
+struct SplitPlan {
+    unsigned grid;
+    int full_rounds, rem_items, split;
+    long long total_items;
+};
+
+SplitPlan plan_split(int sm_count, const FwdParams &p) {
+    SplitPlan pl{};
+    const int q_blocks = (p.q_len + 2 * kTileRows - 1) / (2 * kTileRows);
+    pl.total_items = (long long)q_blocks * p.batch * p.q_heads;
+    const long long g = std::min<long long>(pl.total_items, sm_count);
+    pl.grid = (unsigned)g;
+    pl.full_rounds = (int)(pl.total_items / g);
+    pl.rem_items = (int)(pl.total_items % g);
+    pl.split = 1;
+    if (p.varlen) return pl;  // per-sequence lengths: the parts' tile counts are not known here
+    // fewer items than SMs: the only round is the incomplete one
+    if (pl.total_items < sm_count) {
+        pl.full_rounds = 0;
+        pl.rem_items = (int)pl.total_items;
+    }
+    if (pl.rem_items == 0) return pl;
+    int split = std::min(sm_count / pl.rem_items, 8);
+    // every part should keep at least two KV tiles; the last round holds the shortest items, the shortest of all is
+    // the first query block
+    long long visible = p.kv_len;
+    if (p.causal) visible = std::min<long long>(p.kv_len, p.causal_off + std::min(p.q_len, 2 * kTileRows));
+    const int n_min = (int)((visible + kTileRows - 1) / kTileRows);
+    split = std::min(split, n_min / 2);
+    if (split < 2) return pl;
+    pl.split = split;
+    if (pl.full_rounds == 0) pl.grid = (unsigned)(pl.rem_items * split);
+    return pl;
+}
+
+uint64_t split_scratch_bytes(const SplitPlan &pl, int head_dim) {
+    if (pl.split <= 1) return 0;
+    return (uint64_t)pl.rem_items * pl.split * (2 * kTileRows) * (head_dim + 2) * sizeof(float);
+}
+
+}  // namespace
+
+// scratch: rotated fp16 K (rope_k) and the partial records of split items; the (cos, sin) tables live in the context's
+// table cache
+uint64_t forward_sm100_workspace_bytes(const flat_ctx *ctx, const FwdParams &p) {
     uint64_t bytes = 0;
     if (p.rope_k) bytes += ((uint64_t)p.batch * p.kv_heads * p.kv_len * p.head_dim * 2 + 255) & ~uint64_t(255);
+    bytes += (split_scratch_bytes(plan_split(ctx->sm_count, p), p.head_dim) + 255) & ~uint64_t(255);
     return bytes;
 }
 
@@ -895,17 +1049,19 @@ void forward_sm100_geometry(const flat_ctx *ctx, const FwdParams &p, uint32_t *q
                             uint32_t *dispatches) {
     *query_rows = 2 * kTileRows;  // one work item: two 128-row Q tiles of one (batch, q_head)
     *kv_rows = kTileRows;
-    const long long items = (long long)((p.q_len + 2 * kTileRows - 1) / (2 * kTileRows)) * p.batch * p.q_heads;
-    grid[0] = (uint32_t)std::min<long long>(items, ctx->sm_count);  // persistent: one CTA per SM
+    const SplitPlan pl = plan_split(ctx->sm_count, p);
+    grid[0] = pl.grid;  // persistent: one CTA per SM
     grid[1] = grid[2] = 1;
-    // the attention kernel, the K rotation pass when K arrives raw, and the two fills of a padded variable-length batch
-    *dispatches = 1 + (p.rope_k ? 1 : 0) + (p.varlen ? 1 : 0);
+    // the attention kernel, the K rotation pass when K arrives raw, the LSE fill of a padded variable-length batch and
+    // the merge of the last round's split items
+    *dispatches = 1 + (p.rope_k ? 1 : 0) + (p.varlen ? 1 : 0) + (pl.split > 1 ? 1 : 0);
 }
 
 int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
-    int st = ensure_workspace(ctx, kWorkspaceMeta + forward_sm100_workspace_bytes(p));
+    int st = ensure_workspace(ctx, kWorkspaceMeta + forward_sm100_workspace_bytes(ctx, p));
     if (st) return st;
     const int D = p.head_dim;
+    const SplitPlan plan = plan_split(ctx->sm_count, p);
     const void *k_ptr = p.k;
     int64_t k_rs = p.kv_rs, k_hs = p.kv_hs, k_bs = p.kv_bs;
     bool k_f16 = false;
@@ -998,14 +1154,34 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
 #endif
 
     // Persistent launch: one CTA per SM walks its share of the (query block, batch, head) items.
-    kp.total_items = (long long)kp.q_blocks * p.batch * p.q_heads;
+    kp.total_items = plan.total_items;
     if (kp.total_items > 2147483647LL)
         return fail(ctx, FLAT_ERR_DISPATCH_LIMIT, "forward grid of %lld blocks is too large", kp.total_items);
-    const unsigned grid = (unsigned)std::min<long long>(kp.total_items, ctx->sm_count);
+    const unsigned grid = plan.grid;
+    kp.full_rounds = plan.full_rounds;
+    kp.rem_items = plan.rem_items;
+    kp.split = plan.split;
+    if (plan.split > 1) {
+        // partial records sit behind the rotated K in the scratch
+        char *at = scratch + (p.rope_k ? (((uint64_t)p.batch * p.kv_heads * p.kv_len * D * 2 + 255) & ~uint64_t(255)) : 0);
+        kp.part_o = reinterpret_cast<float *>(at);
+        kp.part_ml = reinterpret_cast<float2 *>(at + (uint64_t)plan.rem_items * plan.split * (2 * kTileRows) * D * sizeof(float));
+    }
     auto run = [&](auto kernel, int smem_bytes) -> int {
         FLAT_CUDA_OK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         KernelTimer timer(ctx);
         kernel<<<grid, kThreads, smem_bytes, ctx->stream>>>(kp);
+        if (plan.split > 1) {
+            const int first_lin = plan.full_rounds * (int)grid;
+            if (D == 128) {
+                if (io16) fwd_split_merge_kernel<128, true><<<plan.rem_items, 256, 0, ctx->stream>>>(kp, first_lin);
+                else fwd_split_merge_kernel<128, false><<<plan.rem_items, 256, 0, ctx->stream>>>(kp, first_lin);
+            } else {
+                if (io16) fwd_split_merge_kernel<64, true><<<plan.rem_items, 256, 0, ctx->stream>>>(kp, first_lin);
+                else fwd_split_merge_kernel<64, false><<<plan.rem_items, 256, 0, ctx->stream>>>(kp, first_lin);
+            }
+            ctx->launches += 1;
+        }
         return FLAT_OK;
     };
     kp.alibi_slopes = p.alibi_slopes;

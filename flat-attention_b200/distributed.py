@@ -66,3 +66,16 @@ def splitkv_decode(ctx, fa, dtype, slice_args: dict, rows: int, head_dim: int, o
     gathered = all_gather_partials(partial, group)
     ctx.splitkv_merge_packed(dtype, dist.get_world_size(group), rows, head_dim, gathered, out)
     return gathered
+
+
+def nccl_comm_ptr(group=None, device=None) -> int:
+    """The ncclComm_t behind a torch.distributed NCCL process group, as an integer for the C ABI
+    (flat_splitkv_decode_nccl).  The communicator exists once the group has run a collective on the device."""
+    import torch
+    import torch.distributed as dist
+    pg = group if group is not None else dist.distributed_c10d._get_default_group()
+    dev = device if device is not None else torch.device("cuda", torch.cuda.current_device())
+    backend = pg._get_backend(dev)
+    if not hasattr(backend, "_comm_ptr"):
+        raise RuntimeError("this torch build does not expose the NCCL communicator of a process group")
+    return int(backend._comm_ptr())

@@ -465,6 +465,32 @@ int32_t flat_decode_paged_batched_partial(flat_ctx *ctx, int32_t dtype, uint64_t
 int32_t flat_splitkv_merge_packed(flat_ctx *ctx, int32_t dtype, uint64_t parts, uint64_t rows,
                                   uint64_t head_dim, flat_buffer gathered, flat_buffer out_and_lse);
 
+/* The exchange step of KV-split decode over an NCCL communicator (one process per GPU, NVLink /
+ * NVSwitch underneath): `gathered` is a DEVICE buffer of world_size blocks of rows*(head_dim+1)
+ * f32 whose block `rank` already holds this rank's partial [O | LSE] (as written by
+ * flat_decode_paged_batched_partial); the blocks are all-gathered in place with ncclAllGather on
+ * the context's stream and merged into out_and_lse on every rank.  nccl_comm is the caller's
+ * ncclComm_t; NCCL is looked up in the process at the first call (the library is not linked
+ * against it), FLAT_ERR_UNAVAILABLE when it is absent.  Enqueues only; no allocation, no
+ * synchronisation.  The reference is single-device (src/wgpu_backend.rs:208-217): no counterpart. */
+int32_t flat_splitkv_merge_nccl(flat_ctx *ctx, void *nccl_comm, int32_t rank, int32_t world_size,
+                                int32_t dtype, uint64_t rows, uint64_t head_dim, flat_buffer gathered,
+                                flat_buffer out_and_lse);
+
+/* One whole KV-split decode step: this rank's partial of its cache slice (arguments as
+ * flat_decode_paged_batched_partial; a rank whose host_context_lens are all zero contributes
+ * weight zero) written into block `rank` of `gathered`, then flat_splitkv_merge_nccl.  Every rank
+ * of the communicator must make the call.  No counterpart in the reference. */
+int32_t flat_splitkv_decode_nccl(flat_ctx *ctx, void *nccl_comm, int32_t rank, int32_t world_size,
+                                 int32_t dtype, uint64_t num_seqs, uint64_t q_heads, uint64_t kv_heads,
+                                 uint64_t head_dim, uint64_t page_size, uint64_t physical_pages,
+                                 uint64_t max_pages_per_seq, const int32_t *page_tables_dev,
+                                 const int32_t *context_lens_dev, const int32_t *q_rope_positions_dev,
+                                 const int32_t *host_page_tables, const int32_t *host_context_lens,
+                                 const flat_attention_config *config, float theta, flat_buffer q,
+                                 flat_buffer k, flat_buffer v, flat_buffer gathered,
+                                 flat_buffer out_and_lse);
+
 /* The same batched split-KV decode for callers that cannot allocate device memory when the
  * call is made (a latency-critical serving loop where an allocation would stall the device, a
  * plug-in under a framework allocator that forbids side allocations, or a process whose memory

@@ -105,7 +105,8 @@ def test_config4_chunked_prefill_full_size_sampled_rows():
         c.chunked_prefill_paged(cache, Hq, chunk, fa.config(True), theta, 0, q[start:start + chunk].cuda(),
                                 k[start:start + chunk].cuda(), v[start:start + chunk].cuda(), out)
         rows = [0, 15, 16, 127, 128, chunk - 1] + [int(r) for r in rng.integers(0, chunk, 3)]
-        pairs = [(int(rng.integers(Hq)), r) for r in rows] + [(Hq - 1, chunk - 1), (0, 0)]
+        # (no pair twice: the oracle's Q rotation below is applied once per listed pair)
+        pairs = list(dict.fromkeys([(int(rng.integers(Hq)), r) for r in rows] + [(Hq - 1, chunk - 1), (0, 0)]))
         o = out[:chunk * Hq * D * 2].view(torch.bfloat16).view(chunk, Hq, D)
         l = out[chunk * Hq * D * 2:].view(torch.float32).view(Hq, chunk)
         picked.append((start, pairs, torch.stack([o[r, h] for (h, r) in pairs]).float().cpu().numpy(),

@@ -236,3 +236,41 @@ def test_random_shapes_tensor_core_path_against_f32_path():
         eo, el = run_forward("projection_rope_asymmetric", fa.F32, shp, fa.config(causal), q, k, v, rot=rot)
         check(o, l, eo, el, what)
         assert ctx().device_status() == 0, what
+
+
+@pytest.mark.parametrize("B,Hq,Hkv,Nq,Nkv,off,D,causal,rope", [
+    (1, 4, 2, 2048, 2048, 0, 128, False, False),    # 32 items on 148 SMs: every item cut into 4 KV parts
+    (1, 4, 2, 256, 4096, 3840, 128, True, True),    # 4 items, 8 parts of 4 KV tiles; the last part holds the diagonal
+    (1, 8, 8, 384, 1664, 1280, 64, True, False),    # ragged: the second Q tile of the last block lies past q_len
+    (2, 40, 8, 1024, 1024, 0, 128, True, True),     # 320 items: two whole rounds, 24 left, each cut into 6 parts
+])
+def test_last_round_items_split_along_kv(B, Hq, Hkv, Nq, Nkv, off, D, causal, rope):
+    """When the last round of the persistent forward holds few items, each is cut along KV into parts that run on
+    different CTAs and a merge kernel finishes the rows.  Sampled rows of every (batch, head) - first / last rows,
+    tile borders, random ones - against the oracle."""
+    q, k, v = randn(B * Hq * Nq * D, 1), randn(B * Hkv * Nkv * D, 2), randn(B * Hkv * Nkv * D, 3)
+    theta = 5e5
+    shp = fa.shape(B, Hq, Hkv, Nq, Nkv, D, off)
+    c = ctx()
+    launches = c.launch_count()
+    if rope:
+        o, l = run_forward("projection_rope_asymmetric", fa.BF16, shp, fa.config(causal), q, k, v, rot=fa.rotary(theta, off, 0))
+        rq = ob.rotate_rows(q, D, np.repeat(np.tile(np.arange(Nq, dtype=np.uint64) + off, B), Hq), theta)
+        rk = ob.rotate_rows(k, D, np.repeat(np.tile(np.arange(Nkv, dtype=np.uint64), B), Hkv), theta)
+        layout = ob.PROJECTION
+        o, pick = o.reshape(B, Nq, Hq, D), (lambda b, h, r: (b, r, h))
+    else:
+        o, l = run_forward("grouped_asymmetric", fa.BF16, shp, fa.config(causal), q, k, v)
+        rq, rk, layout = q, k, ob.HEAD_MAJOR
+        o, pick = o.reshape(B, Hq, Nq, D), (lambda b, h, r: (b, h, r))
+    rng = np.random.default_rng(7)
+    picks = sorted({0, 1, 127, 128, 255, 256, Nq - 1} & set(range(Nq)))
+    rows = [(b, h, r) for b in range(B) for h in range(Hq) for r in picks + [int(x) for x in rng.integers(0, Nq, 2)]]
+    eo, el = ob.forward_rows(rq, rk, v, ob._shape(B, Hq, Hkv, Nq, Nkv, D, off), layout, rows, causal, threads=8)
+    l = l.reshape(B, Hq, Nq)
+    go = np.stack([o[pick(b, h, r)] for b, h, r in rows]).reshape(-1)
+    gl = np.array([l[b, h, r] for b, h, r in rows])
+    check(go, gl, eo, el)
+    assert c.device_status() == 0
+    # the split really ran: the call launched a merge kernel besides the attention kernel (and the K rotation / tables)
+    assert c.launch_count() - launches >= 2

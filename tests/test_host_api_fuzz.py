@@ -165,6 +165,10 @@ def test_null_context_is_an_error_not_a_crash():
     assert lib.flat_decode_paged_batched_static_scratch(
         None, C.c_int32(1), C.c_uint64(1 << 62), C.c_uint64(1 << 62), C.c_uint64(1 << 62), C.c_uint64(64), C.c_uint64(16),
         C.c_uint64(1), C.c_uint64(1), None, None, None, None, None, C.byref(cfg), C.c_float(1e4), C.c_uint32(0), z, z, z, z) == 27
+    assert lib.flat_splitkv_merge_nccl(None, None, C.c_int32(0), C.c_int32(1), C.c_int32(1), C.c_uint64(1), C.c_uint64(2), z, z) == 27
+    assert lib.flat_splitkv_decode_nccl(None, None, C.c_int32(0), C.c_int32(1), C.c_int32(1), C.c_uint64(1), C.c_uint64(1),
+                                        C.c_uint64(1), C.c_uint64(2), C.c_uint64(16), C.c_uint64(1), C.c_uint64(1), None, None, None,
+                                        None, None, C.byref(cfg), C.c_float(1e4), z, z, z, z, z) == 27
     assert lib.flat_ctx_device_fingerprint(None, None) == 27 and lib.flat_ctx_device_capabilities(None, None) == 27
     assert lib.flat_benchmark_manifest_validate(None, None) == 27
     lib.flat_benchmark_manifest_canonical_json.restype = C.c_int64
