@@ -32,6 +32,7 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <type_traits>
 
 #include "common.h"
 #include "sm100_host.cuh"
@@ -96,12 +97,13 @@ struct KernelParams {
     const int32_t *page_table;
     int page_size, max_pages, physical_pages;
     int q_blocks;
-    long long total_items;  // q_blocks * batch * q_heads
-    // Work distribution: `full_rounds` rounds in which every CTA takes one whole item, then one round for the
-    // `rem_items` items that are left.  When those are few, each is cut along KV into `split` parts that run on
-    // different CTAs (a part writes its unnormalised O, running max and sum to part_o / part_ml; a merge kernel
-    // finishes the rows), so the last round keeps every SM busy instead of a fraction of them.
-    int full_rounds, rem_items, split;
+    long long total_items;  // q_blocks * batch * q_heads work items; with a split last round, its parts counted one by one
+    // Work distribution: whole rounds in which every CTA takes one item, then one round for the `rem_items` items that
+    // are left.  When those are few, each is cut along KV into `split` parts that run on different CTAs (a part
+    // writes its unnormalised O, running max and sum to part_o / part_ml; a merge kernel finishes the rows), so the
+    // last round keeps every SM busy instead of a fraction of them.  Item indices from split_first on name parts:
+    // index split_first + v is part v / rem_items of item split_first + v % rem_items.
+    int split_first, rem_items, split;  // split_first: first item index of the split round (INT_MAX when nothing is split)
     float *part_o;    // [rem_items * split][256 rows][D] f32, unnormalised
     float2 *part_ml;  // [rem_items * split][256 rows] (running max in the log2 domain, running sum)
     DeviceStatus *status;
@@ -122,7 +124,7 @@ template <int D, bool CONVK> struct Cfg {
     static constexpr int kTileBytes = kBoxes * kBoxBytes;  // one Q / K / V tile
     static constexpr int kStages = D == 128 ? 4 : 8;  // K/V ring entries
     static constexpr int kBars = 2 + 3 * kStages + 10;
-    static constexpr int kSmemBytes = (2 + kStages) * kTileBytes + kBars * 8 + 16 + 1024;
+    static constexpr int kSmemBytes = (2 + kStages) * kTileBytes + kBars * 8 + 16 + 32 + 1024;
 };
 
 __device__ __forceinline__ void record_timeout(const KernelParams &p, int where) {
@@ -144,15 +146,18 @@ struct WorkItem {
     int table_row0;        // row of the (cos, sin) table that belongs to local query row 0
 };
 
-struct ItemRef {
-    int lin;   // linear item index, -1 = none
-    int part;  // part of a split item, -1 = whole item
+// What a CTA needs to know about the part of a split item it runs in the last round; decoded once per CTA into
+// shared memory (the roles that walk the items then read five words instead of redoing the arithmetic).
+struct SplitRecord {
+    int lin;        // the item the part belongs to
+    int j0;         // first KV tile of the part
+    int n_tiles[2]; // KV tiles of the part per Q tile
+    int part_slot;  // index of its partial record
 };
 
-__device__ __forceinline__ WorkItem make_item(const KernelParams &p, ItemRef ref) {
+__device__ __forceinline__ WorkItem make_item_whole(const KernelParams &p, int lin) {
     // item index -> (query block, batch, head); late (long) query blocks first
     WorkItem it;
-    const int lin = ref.lin;
     const int total_bh = p.batch * p.q_heads;
     const int qb = p.q_blocks - 1 - lin / total_bh;
     const int bh = lin % total_bh;
@@ -183,36 +188,54 @@ __device__ __forceinline__ WorkItem make_item(const KernelParams &p, ItemRef ref
         }
         it.n_tiles[w] = first < it.q_len ? (int)((visible + kTileRows - 1) / kTileRows) : 0;
     }
-    if (ref.part >= 0) {
-        // part i of `split` takes KV tiles [i * n / split, (i + 1) * n / split) of the item's n
-        const int n = max(it.n_tiles[0], it.n_tiles[1]);
-        const int lo = (int)((long long)ref.part * n / p.split), hi = (int)((long long)(ref.part + 1) * n / p.split);
-        it.j0 = lo;
-#pragma unroll
-        for (int w = 0; w < 2; ++w) it.n_tiles[w] = max(0, min(it.n_tiles[w], hi) - lo);
-        it.part_slot = (lin - p.full_rounds * (int)gridDim.x) * p.split + ref.part;
-    }
     return it;
 }
 
-// The k-th item of this CTA.  Items are sorted longest first; CTAs take them in rounds of gridDim.x, odd rounds in
-// reverse CTA order, so that every CTA gets nearly the same number of KV tiles.  In the last, incomplete round
-// CTA position s works on item s mod rem_items, part s / rem_items.
-__device__ __forceinline__ ItemRef item_index(const KernelParams &p, int k) {
+// Item indices from split_first on name parts of the last round's items: index split_first + v is part v / rem_items of
+// item split_first + v % rem_items, and covers KV tiles [part * n / split, (part + 1) * n / split) of the item's n.
+__device__ __forceinline__ SplitRecord decode_part(const KernelParams &p, int idx) {
+    SplitRecord r;
+    const int v = idx - p.split_first;
+    const int part = v / p.rem_items;
+    r.lin = p.split_first + v % p.rem_items;
+    const WorkItem it = make_item_whole(p, r.lin);
+    const int n = max(it.n_tiles[0], it.n_tiles[1]);
+    const int lo = part * n / p.split, hi = (part + 1) * n / p.split;
+    r.j0 = lo;
+    r.n_tiles[0] = max(0, min(it.n_tiles[0], hi) - lo);
+    r.n_tiles[1] = max(0, min(it.n_tiles[1], hi) - lo);
+    r.part_slot = (r.lin - p.split_first) * p.split + part;
+    return r;
+}
+
+// SPLIT: the launch cuts the items of its last round into KV parts (a template flag, so that launches without a split
+// carry none of its bookkeeping); `rec` is the CTA's decoded part in shared memory.
+template <bool SPLIT>
+__device__ __forceinline__ WorkItem make_item(const KernelParams &p, int lin, const volatile SplitRecord *rec) {
+    if (SPLIT && lin >= p.split_first) {
+        WorkItem it = make_item_whole(p, rec->lin);
+        it.j0 = rec->j0;
+        it.n_tiles[0] = rec->n_tiles[0];
+        it.n_tiles[1] = rec->n_tiles[1];
+        it.part_slot = rec->part_slot;
+        return it;
+    }
+    return make_item_whole(p, lin);
+}
+
+// The k-th item of this CTA, or -1.  Items are sorted longest first; CTAs take them in rounds of gridDim.x,
+// odd rounds in reverse CTA order, so that every CTA gets nearly the same number of KV tiles.
+__device__ __forceinline__ int item_index(const KernelParams &p, int k) {
     const int g = (int)gridDim.x;
-    const int s = (k & 1) ? g - 1 - (int)blockIdx.x : (int)blockIdx.x;
-    if (k < p.full_rounds) return ItemRef{k * g + s, -1};
-    if (k > p.full_rounds || p.rem_items == 0) return ItemRef{-1, -1};
-    if (p.split <= 1) return ItemRef{s < p.rem_items ? k * g + s : -1, -1};
-    const int part = s / p.rem_items;
-    return ItemRef{part < p.split ? k * g + s % p.rem_items : -1, part < p.split ? part : -1};
+    const long long idx = (long long)k * g + ((k & 1) ? g - 1 - (int)blockIdx.x : (int)blockIdx.x);
+    return idx < p.total_items ? (int)idx : -1;
 }
 
 // ALIBI: the softmax warps add slope[q_head] * (key position - query position) to every scaled score
 // (src/attention_bias.rs:82-95) before the running maximum is taken.
 // F16IO: Q, K, V and O are IEEE binary16 instead of bf16 (P is then written as binary16 too, since one MMA takes A and B
 // of one format); accumulation, softmax and LSE stay f32.
-template <int D, bool CONVK, bool ALIBI, bool F16IO>
+template <int D, bool CONVK, bool ALIBI, bool F16IO, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_constant__ KernelParams p) {
     using C = Cfg<D, CONVK>;
     extern __shared__ uint8_t smem_raw[];
@@ -222,6 +245,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     uint64_t *bars = reinterpret_cast<uint64_t *>(kv_s + C::kStages * C::kTileBytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + C::kBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    volatile SplitRecord *split_rec = reinterpret_cast<volatile SplitRecord *>(tmem_slot + 2);
 
     const uint32_t bar0 = smem_u32(bars);
     auto q_full = [&](int w) { return bar0 + 8u * w; };
@@ -257,6 +281,19 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
         tma_prefetch_desc(&p.map_q);
         tma_prefetch_desc(&p.map_k);
         tma_prefetch_desc(&p.map_v);
+        if constexpr (SPLIT) {
+            // the part this CTA runs in the last round, if any: decoded once, read by every role
+            const int g = (int)gridDim.x, k_last = p.split_first / g;
+            const long long idx = (long long)k_last * g + ((k_last & 1) ? g - 1 - (int)blockIdx.x : (int)blockIdx.x);
+            if (idx < p.total_items) {
+                const SplitRecord r = decode_part(p, (int)idx);
+                split_rec->lin = r.lin;
+                split_rec->j0 = r.j0;
+                split_rec->n_tiles[0] = r.n_tiles[0];
+                split_rec->n_tiles[1] = r.n_tiles[1];
+                split_rec->part_slot = r.part_slot;
+            }
+        }
     }
     if (warp == kMmaWarp) {
         tmem_alloc(smem_u32(tmem_slot), 512);
@@ -285,9 +322,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             uint32_t ring = 0;             // K/V ring entries requested so far
             uint32_t q_loads[2] = {0, 0};  // Q tiles requested so far, per slot
             for (int k = 0; ok; ++k) {
-                const ItemRef ref = item_index(p, k);
-                if (ref.lin < 0) break;
-                const WorkItem it = make_item(p, ref);
+                const int lin = item_index(p, k);
+                if (lin < 0) break;
+                const WorkItem it = make_item<SPLIT>(p, lin, split_rec);
                 const int n_max = max(it.n_tiles[0], it.n_tiles[1]);
                 for (int w = 0; w < 2 && ok; ++w) {
                     if (it.n_tiles[w] == 0) continue;
@@ -377,9 +414,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             auto phase_of = [&](uint32_t i) { return (uint32_t)(((ring0 + i) / C::kStages) & 1); };
 
             for (int k = 0; ok; ++k) {
-                const ItemRef ref = item_index(p, k);
-                if (ref.lin < 0) break;
-                const WorkItem it = make_item(p, ref);
+                const int lin = item_index(p, k);
+                if (lin < 0) break;
+                const WorkItem it = make_item<SPLIT>(p, lin, split_rec);
                 const int n_max = max(it.n_tiles[0], it.n_tiles[1]);
                 const bool trace_item = k == 0;
                 (void)trace_item;
@@ -449,9 +486,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
         bool ok = true;
         uint32_t ring = 0;
         for (int k = 0; ok; ++k) {
-            const ItemRef ref = item_index(p, k);
-            if (ref.lin < 0) break;
-            const WorkItem it = make_item(p, ref);
+            const int lin = item_index(p, k);
+            if (lin < 0) break;
+            const WorkItem it = make_item<SPLIT>(p, lin, split_rec);
             const int n_max = max(it.n_tiles[0], it.n_tiles[1]);
             for (int j = 0; ok && j < n_max; ++j, ring += 2) {
                 const int s = ring % C::kStages;
@@ -505,7 +542,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             float m = -INFINITY, l = 0.f;
             bool run = false;
             if (k >= 0) {
-                const WorkItem it = make_item(p, item_index(p, k));
+                const WorkItem it = make_item<SPLIT>(p, item_index(p, k), split_rec);
                 run = it.n_tiles[w] > 0;
                 const int n = it.n_tiles[w];
                 int lim = it.kv_len - 1;  // last visible key of this row
@@ -515,13 +552,16 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     lim = (int)min((long long)lim, it.causal_off + first + row_in_tile);
                     lim_first = (int)min((long long)lim_first, it.causal_off + first);
                 }
+                // keys are counted from the item's first KV tile below (a part of a split item starts at tile j0)
+                lim -= it.j0 * kTileRows;
+                lim_first -= it.j0 * kTileRows;
                 // ALiBi is added to the raw score as (slope / scale) * position difference, so that the scaling of the
                 // softmax passes covers it.  Positions stay below 2^24 in magnitude (checked on the host): the float
                 // position arithmetic is exact.
                 float slope_rel = 0.f, bias_pos0 = 0.f;
                 if constexpr (ALIBI) {
                     slope_rel = __ldg(p.alibi_slopes + it.h) * p.alibi_inv_scale;
-                    bias_pos0 = (float)(p.alibi_delta - (it.r0 + w * kTileRows + row_in_tile));
+                    bias_pos0 = (float)(p.alibi_delta + it.j0 * kTileRows - (it.r0 + w * kTileRows + row_in_tile));
                 }
 
                 // Online softmax, log2 domain, one thread per row; the whole 128-column score row sits in
@@ -539,7 +579,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                         TRACE_FLUSH(w, j - 1);
                         TRACE_STAMP(0);
                     }
-                    const int key0 = (it.j0 + j) * kTileRows;
+                    const int key0 = j * kTileRows;
                     const bool tile_masked = key0 + kTileRows - 1 > lim_first;  // uniform over the Q tile
                     const int vis = min(kTileRows, lim - key0 + 1);             // visible columns of this row
                     const float c_log2 = p.scale_log2;
@@ -590,7 +630,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     // P = exp2(S*c - m) as bf16, written over S; two scores per packed f32x2 FMA
                     uint64_t c2, nm2, sum2 = 0, sum3 = 0;
                     {
-                        const float neg_m = fmaf(bias_base, c_log2, -m);
+                        // m is still -inf only while every key this row has met was masked (the first tile of a split
+                        // part may lie wholly behind the row's diagonal): all its scores are -inf and P must come out 0
+                        const float neg_m = m == -INFINITY ? 0.f : fmaf(bias_base, c_log2, -m);
                         asm("mov.b64 %0, {%1, %1};" : "=l"(nm2) : "f"(neg_m));
                         asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(c_log2));
                     }
@@ -635,10 +677,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             }
 
             if ((warp & 3) == 0 && lane == 0) TRACEB(k, w, 0);
-            const ItemRef next_ref = item_index(p, k + 1);
-            const int next_lin = next_ref.lin;
+            const int next_lin = item_index(p, k + 1);
             if (p.rope_q_table && next_lin >= 0 && ok) {
-                const WorkItem nx = make_item(p, next_ref);
+                const WorkItem nx = make_item<SPLIT>(p, next_lin, split_rec);
                 if (nx.n_tiles[w] > 0) {
                     // Rotate the Q tile in place (bf16 in, fp16 out).  A warp rotates its 32 rows; lane l
                     // takes the 16-byte chunk (l mod CH) of row (step * RPS + l / CH), so that the (cos, sin) table is
@@ -724,9 +765,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             if ((warp & 3) == 0 && lane == 0) TRACEB(k, w, 3);
             if (run && ok) {
                 tc_fence_after();
-                const WorkItem it = make_item(p, item_index(p, k));
+                const WorkItem it = make_item<SPLIT>(p, item_index(p, k), split_rec);
                 const int row = it.r0 + w * kTileRows + row_in_tile, b = it.b, h = it.h;
-                if (it.part_slot >= 0) {
+                if (SPLIT && it.part_slot >= 0) {
                     // a part of a split item: unnormalised O, running max and sum go to the partial record
                     const long long prow = (long long)it.part_slot * (2 * kTileRows) + w * kTileRows + row_in_tile;
                     float4 *po = reinterpret_cast<float4 *>(p.part_o + prow * D);
@@ -786,9 +827,9 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                 // thread's next hand-over of P: program order keeps the reads above ahead of it
                 tc_fence_before();
                 }
-            } else if (k >= 0 && ok) {
+            } else if (SPLIT && k >= 0 && ok) {
                 // a part in which this Q tile has no KV tile at all still owns a partial record: an empty one
-                const WorkItem it = make_item(p, item_index(p, k));
+                const WorkItem it = make_item<SPLIT>(p, item_index(p, k), split_rec);
                 if (it.part_slot >= 0)
                     p.part_ml[(long long)it.part_slot * (2 * kTileRows) + w * kTileRows + row_in_tile] = make_float2(-INFINITY, 0.f);
             }
@@ -833,27 +874,33 @@ __global__ void __launch_bounds__(256) fill_u32_kernel(uint32_t *__restrict__ ds
 
 // Finishes the rows of the split items of the last round: for each row the parts' unnormalised O_i, running maxima
 // m_i (log2 domain) and sums l_i combine to  M = max m_i,  L = sum 2^(m_i - M) l_i,  O = sum 2^(m_i - M) O_i / L,
-// LSE = (M + log2 L) ln 2.  One CTA per item, one warp per row at a time, a lane owns D / 32 consecutive columns.
+// LSE = (M + log2 L) ln 2.  Eight CTAs per item (32 rows each), one warp per row, a lane owns D / 32 consecutive
+// columns; the kernel is a chain of dependent global loads per row, so rows are spread wide rather than looped over.
+constexpr int kMergeCtasPerItem = 8;
 template <int D, bool F16IO>
 __global__ void __launch_bounds__(256) fwd_split_merge_kernel(const __grid_constant__ KernelParams p, int first_lin) {
     constexpr int kCols = D / 32;
+    constexpr int kRowsPerCta = 2 * kTileRows / kMergeCtasPerItem;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int lin = first_lin + blockIdx.x;
+    const int item = blockIdx.x / kMergeCtasPerItem;
+    const int lin = first_lin + item;
     const int total_bh = p.batch * p.q_heads;
     const int qb = p.q_blocks - 1 - lin / total_bh, bh = lin % total_bh;
     const int b = bh / p.q_heads, h = bh % p.q_heads;
     const int r0 = qb * 2 * kTileRows;
-    for (int rr = warp; rr < 2 * kTileRows; rr += 8) {
+#pragma unroll
+    for (int q = 0; q < kRowsPerCta / 8; ++q) {
+        const int rr = (blockIdx.x % kMergeCtasPerItem) * kRowsPerCta + q * 8 + warp;
         const int row = r0 + rr;
-        if (row >= p.q_len) break;
+        if (row >= p.q_len) continue;
+        const long long prow0 = ((long long)item * p.split) * (2 * kTileRows) + rr;
         float mx = -INFINITY;
-        for (int i = 0; i < p.split; ++i)
-            mx = fmaxf(mx, p.part_ml[((long long)blockIdx.x * p.split + i) * (2 * kTileRows) + rr].x);
+        for (int i = 0; i < p.split; ++i) mx = fmaxf(mx, p.part_ml[prow0 + (long long)i * (2 * kTileRows)].x);
         float acc[kCols], sum = 0.f;
 #pragma unroll
         for (int c = 0; c < kCols; ++c) acc[c] = 0.f;
         for (int i = 0; i < p.split; ++i) {
-            const long long prow = ((long long)blockIdx.x * p.split + i) * (2 * kTileRows) + rr;
+            const long long prow = prow0 + (long long)i * (2 * kTileRows);
             const float2 ml = p.part_ml[prow];
             if (ml.y == 0.f) continue;  // an empty part
             const float wgt = ex2(ml.x - mx);
@@ -994,6 +1041,7 @@ namespace {
 
 // Work distribution of one launch (see KernelParams): the grid, the whole rounds, what is left for the last round and
 // into how many KV parts each of those items is cut.
+constexpr int kMinPartTiles = 16;
 struct SplitPlan {
     unsigned grid;
     int full_rounds, rem_items, split;
@@ -1017,12 +1065,13 @@ SplitPlan plan_split(int sm_count, const FwdParams &p) {
     }
     if (pl.rem_items == 0) return pl;
     int split = std::min(sm_count / pl.rem_items, 8);
-    // every part should keep at least two KV tiles; the last round holds the shortest items, the shortest of all is
+    // a part costs a Q load, a rotation, an epilogue of its own and a share of the merge launch (about 10 us together):
+    // it should keep at least kMinPartTiles KV tiles.  The last round holds the shortest items, the shortest of all is
     // the first query block
     long long visible = p.kv_len;
     if (p.causal) visible = std::min<long long>(p.kv_len, p.causal_off + std::min(p.q_len, 2 * kTileRows));
     const int n_min = (int)((visible + kTileRows - 1) / kTileRows);
-    split = std::min(split, n_min / 2);
+    split = std::min(split, n_min / kMinPartTiles);
     if (split < 2) return pl;
     pl.split = split;
     if (pl.full_rounds == 0) pl.grid = (unsigned)(pl.rem_items * split);
@@ -1155,13 +1204,16 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
 
     // Persistent launch: one CTA per SM walks its share of the (query block, batch, head) items.
     kp.total_items = plan.total_items;
-    if (kp.total_items > 2147483647LL)
+    if (kp.total_items > 2147483647LL - 8 * (long long)ctx->sm_count)
         return fail(ctx, FLAT_ERR_DISPATCH_LIMIT, "forward grid of %lld blocks is too large", kp.total_items);
     const unsigned grid = plan.grid;
-    kp.full_rounds = plan.full_rounds;
+    kp.split_first = 2147483647;
     kp.rem_items = plan.rem_items;
     kp.split = plan.split;
     if (plan.split > 1) {
+        // the parts of the last round's items are dealt like items of their own
+        kp.split_first = plan.full_rounds * (int)grid;
+        kp.total_items = (long long)kp.split_first + (long long)plan.rem_items * plan.split;
         // partial records sit behind the rotated K in the scratch
         char *at = scratch + (p.rope_k ? (((uint64_t)p.batch * p.kv_heads * p.kv_len * D * 2 + 255) & ~uint64_t(255)) : 0);
         kp.part_o = reinterpret_cast<float *>(at);
@@ -1174,11 +1226,11 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
         if (plan.split > 1) {
             const int first_lin = plan.full_rounds * (int)grid;
             if (D == 128) {
-                if (io16) fwd_split_merge_kernel<128, true><<<plan.rem_items, 256, 0, ctx->stream>>>(kp, first_lin);
-                else fwd_split_merge_kernel<128, false><<<plan.rem_items, 256, 0, ctx->stream>>>(kp, first_lin);
+                if (io16) fwd_split_merge_kernel<128, true><<<plan.rem_items * kMergeCtasPerItem, 256, 0, ctx->stream>>>(kp, first_lin);
+                else fwd_split_merge_kernel<128, false><<<plan.rem_items * kMergeCtasPerItem, 256, 0, ctx->stream>>>(kp, first_lin);
             } else {
-                if (io16) fwd_split_merge_kernel<64, true><<<plan.rem_items, 256, 0, ctx->stream>>>(kp, first_lin);
-                else fwd_split_merge_kernel<64, false><<<plan.rem_items, 256, 0, ctx->stream>>>(kp, first_lin);
+                if (io16) fwd_split_merge_kernel<64, true><<<plan.rem_items * kMergeCtasPerItem, 256, 0, ctx->stream>>>(kp, first_lin);
+                else fwd_split_merge_kernel<64, false><<<plan.rem_items * kMergeCtasPerItem, 256, 0, ctx->stream>>>(kp, first_lin);
             }
             ctx->launches += 1;
         }
@@ -1187,18 +1239,24 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     kp.alibi_slopes = p.alibi_slopes;
     kp.alibi_delta = (int)(p.alibi_kv_off - p.alibi_q_off);
     kp.alibi_inv_scale = 1.0f / p.scale;
+    // <head_dim, CONVK, ALIBI, F16IO, SPLIT>
+    auto pick = [&](auto d_tag, auto convk_tag, auto alibi_tag, auto f16_tag) -> int {
+        constexpr int kD = decltype(d_tag)::value;
+        constexpr bool kConv = decltype(convk_tag)::value, kAlibi = decltype(alibi_tag)::value, kF16 = decltype(f16_tag)::value;
+        if (plan.split > 1) return run(fwd_sm100_kernel<kD, kConv, kAlibi, kF16, true>, Cfg<kD, kConv>::kSmemBytes);
+        return run(fwd_sm100_kernel<kD, kConv, kAlibi, kF16, false>, Cfg<kD, kConv>::kSmemBytes);
+    };
+    using T = std::true_type;
+    using F = std::false_type;
+    using D128 = std::integral_constant<int, 128>;
+    using D64 = std::integral_constant<int, 64>;
     if (io16) {
-        st = D == 128 ? run(fwd_sm100_kernel<128, false, false, true>, Cfg<128, false>::kSmemBytes)
-                      : run(fwd_sm100_kernel<64, false, false, true>, Cfg<64, false>::kSmemBytes);
+        st = D == 128 ? pick(D128{}, F{}, F{}, T{}) : pick(D64{}, F{}, F{}, T{});
     } else if (p.alibi_slopes) {
-        if (D == 128) st = convk ? run(fwd_sm100_kernel<128, true, true, false>, Cfg<128, true>::kSmemBytes)
-                                 : run(fwd_sm100_kernel<128, false, true, false>, Cfg<128, false>::kSmemBytes);
-        else st = convk ? run(fwd_sm100_kernel<64, true, true, false>, Cfg<64, true>::kSmemBytes)
-                        : run(fwd_sm100_kernel<64, false, true, false>, Cfg<64, false>::kSmemBytes);
-    } else if (D == 128) st = convk ? run(fwd_sm100_kernel<128, true, false, false>, Cfg<128, true>::kSmemBytes)
-                                    : run(fwd_sm100_kernel<128, false, false, false>, Cfg<128, false>::kSmemBytes);
-    else st = convk ? run(fwd_sm100_kernel<64, true, false, false>, Cfg<64, true>::kSmemBytes)
-                    : run(fwd_sm100_kernel<64, false, false, false>, Cfg<64, false>::kSmemBytes);
+        if (D == 128) st = convk ? pick(D128{}, T{}, T{}, F{}) : pick(D128{}, F{}, T{}, F{});
+        else st = convk ? pick(D64{}, T{}, T{}, F{}) : pick(D64{}, F{}, T{}, F{});
+    } else if (D == 128) st = convk ? pick(D128{}, T{}, F{}, F{}) : pick(D128{}, F{}, F{}, F{});
+    else st = convk ? pick(D64{}, T{}, F{}, F{}) : pick(D64{}, F{}, F{}, F{});
     if (st) return st;
     ctx->launches += 1;
     FLAT_CUDA_OK(ctx, cudaGetLastError());

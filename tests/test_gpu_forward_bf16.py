@@ -239,10 +239,10 @@ def test_random_shapes_tensor_core_path_against_f32_path():
 
 
 @pytest.mark.parametrize("B,Hq,Hkv,Nq,Nkv,off,D,causal,rope", [
-    (1, 4, 2, 2048, 2048, 0, 128, False, False),    # 32 items on 148 SMs: every item cut into 4 KV parts
-    (1, 4, 2, 256, 4096, 3840, 128, True, True),    # 4 items, 8 parts of 4 KV tiles; the last part holds the diagonal
-    (1, 8, 8, 384, 1664, 1280, 64, True, False),    # ragged: the second Q tile of the last block lies past q_len
-    (2, 40, 8, 1024, 1024, 0, 128, True, True),     # 320 items: two whole rounds, 24 left, each cut into 6 parts
+    (1, 4, 2, 2048, 8192, 0, 128, False, False),    # 32 items on 148 SMs: every item cut into 4 KV parts
+    (1, 4, 2, 256, 8192, 7936, 128, True, True),    # 4 items, 4 parts of 16 KV tiles; the last part holds the diagonal
+    (1, 8, 8, 384, 4736, 4352, 64, True, False),    # ragged: the second Q tile of the last block lies past q_len
+    (2, 40, 8, 1024, 5120, 4096, 128, True, True),  # 320 items: two whole rounds, 24 left, each cut into 2 parts
 ])
 def test_last_round_items_split_along_kv(B, Hq, Hkv, Nq, Nkv, off, D, causal, rope):
     """When the last round of the persistent forward holds few items, each is cut along KV into parts that run on
