@@ -555,7 +555,7 @@ def bench_prefill_variants(torch, np, fa, ctx, peaks, steps, warmup, ob=None, de
     return results
 
 
-def bench_chunked_prefill(torch, np, fa, ctx, peaks, warmup, ob=None, device_index=0, reps=3):
+def bench_chunked_prefill(torch, np, fa, ctx, peaks, warmup, ob=None, device_index=0, reps=3, shadow=True):
     """Config 4 (prefill part): one 32768-token sequence fed in 2048-token chunks into a growing paged cache."""
     Hq, Hkv, D, N, chunk, ps, theta = 64, 8, 128, 32768, 2048, 16, 500000.0
     g = torch.Generator(device="cuda").manual_seed(13)
@@ -563,6 +563,8 @@ def bench_chunked_prefill(torch, np, fa, ctx, peaks, warmup, ob=None, device_ind
     k = torch.randn(N, Hkv * D, generator=g, device="cuda").bfloat16()
     v = torch.randn(N, Hkv * D, generator=g, device="cuda").bfloat16()
     cache = fa.CudaPagedKvCache(ctx, fa.BF16, ps, N // ps + 8, Hkv, D)
+    if shadow:
+        cache.enable_prefill_shadow()
     out = ctx.empty_bytes(chunk * Hq * D * 2 + Hq * chunk * 4)
     cfg = fa.config(True)
     keep = {}
@@ -625,12 +627,14 @@ def bench_chunked_prefill(torch, np, fa, ctx, peaks, warmup, ob=None, device_ind
     return {"metric": "chunked_prefill_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_sequence": ms,
             "flop_per_sequence": flops,
             "roofline": tensor_roofline(peaks, flops, kernel_ms, loop_ms, clocks.get("reasons"),
-                                        "fwd_sm100_kernel<128,CONVK> x 16 chunks", NCU_TRAFFIC.get("chunked"),
+                                        "fwd_sm100_kernel<128,paged" + ("" if shadow else ",CONVK") + "> x 16 chunks", NCU_TRAFFIC.get("chunked"),
                                         "dram bytes read+written of the last chunk's launch scaled by flops to 16 chunks, one "
                                         "ncu capture (profiles/)" if NCU_TRAFFIC.get("chunked") else None),
             "clocks": clocks, "parity": parity,
             "workload": "C4 1 x 32768 tokens in 2048-token chunks, Hq=64 Hkv=8 D=128 causal bf16, page 16, RoPE fused "
-                        "into the cache append (K) and into the attention kernel (Q)"}
+                        "into the cache append (K) and into the attention kernel (Q)" +
+                        ("; the cache keeps a binary16 shadow of K (flat_paged_kv_cache_enable_prefill_shadow)" if shadow else
+                         "; K tiles converted to binary16 inside the kernel (no shadow)")}
 
 
 def splitkv_slice(torch, np, fd, rank, world, n, ps, Hkv, D):
@@ -839,6 +843,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU oracle legs (parity gate, cpu_baseline): for profiler runs")
     ap.add_argument("--variants-only", action="store_true", help="run only the ALiBi / binary16 prefill variants (N=1): "
                                                                 "a short command for profiler captures")
+    ap.add_argument("--no-shadow", action="store_true", help="chunked prefill without the binary16 K shadow of the paged cache")
     ap.add_argument("--chunked-only", action="store_true", help="run only the chunked prefill against the paged cache "
                                                                "(N=1; --steps = timed passes): a short command for profiler captures")
     ap.add_argument("--manifest", default=None, help="write a schema-1 canonical-JSON benchmark manifest of the headline "
@@ -882,7 +887,7 @@ def main():
             if not args.no_cpu:
                 from oracle import binding as ob_c
             print(json.dumps({"chunked_prefill": bench_chunked_prefill(torch, np, fa, ctx, peaks, args.warmup, ob_c, local_rank,
-                                                                       reps=max(1, args.steps))}), flush=True)
+                                                                       reps=max(1, args.steps), shadow=not args.no_shadow)}), flush=True)
         return
     c = C2
     B, Hq, Hkv, N, D, theta = c["B"], c["Hq"], c["Hkv"], c["N"], c["D"], c["theta"]
@@ -1017,7 +1022,8 @@ def main():
             line["decode"] = bench_decode(torch, np, fa, ctx, peaks, max(5, min(args.steps, 20)), args.warmup, ob_gate)
             line["backward"] = bench_backward(torch, np, fa, ctx, peaks, max(3, min(args.steps, 10)), args.warmup, ob_gate,
                                               device_index=local_rank)
-            line["chunked_prefill"] = bench_chunked_prefill(torch, np, fa, ctx, peaks, args.warmup, ob_gate, local_rank)
+            line["chunked_prefill"] = bench_chunked_prefill(torch, np, fa, ctx, peaks, args.warmup, ob_gate, local_rank,
+                                                            shadow=not args.no_shadow)
             line["prefill_variants"] = bench_prefill_variants(torch, np, fa, ctx, peaks, max(5, min(args.steps, 20)), args.warmup,
                                                               ob_gate, local_rank)
     if world > 1 and not args.skip_extras:

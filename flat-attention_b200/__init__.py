@@ -540,6 +540,10 @@ class CudaPagedKvCache:
                                                                  C.c_uint64(kv_position_offset), C.byref(n)))
         return n.value
 
+    def enable_prefill_shadow(self):
+        """Keep a binary16 copy of K for the tensor-core chunked prefill (bf16 caches; one more K-sized allocation)."""
+        self.ctx.check(lib().flat_paged_kv_cache_enable_prefill_shadow(self.h))
+
     def reset(self):
         self.ctx.check(lib().flat_paged_kv_cache_reset(self.h))
 

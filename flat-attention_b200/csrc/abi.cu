@@ -320,6 +320,7 @@ struct flat_paged_kv_cache {
     uint64_t kv_heads = 0, head_dim = 0;
     uint64_t tensor_bytes = 0;
     void *k = nullptr, *v = nullptr;
+    void *k_f16 = nullptr;         // optional binary16 shadow of K for the tensor-core prefill (bf16 caches)
     int32_t *dev_table = nullptr;  // device mirror of the logical -> physical map
     flat_paged_kv_table table;
 };
@@ -1110,6 +1111,7 @@ void flat_paged_kv_cache_destroy(flat_paged_kv_cache *c) {
     if (c->k) cudaFree(c->k);
     if (c->v) cudaFree(c->v);
     if (c->dev_table) cudaFree(c->dev_table);
+    if (c->k_f16) cudaFree(c->k_f16);
     delete c;
 }
 
@@ -1149,7 +1151,7 @@ static int paged_append_impl(flat_paged_kv_cache *c, flat_buffer k_source, flat_
         FLAT_CUDA_OK(ctx, cudaMemcpyAsync(c->dev_table + old_pages, fresh.data(), fresh.size() * sizeof(int32_t),
                                           cudaMemcpyHostToDevice, ctx->stream));
     }
-    st = launch_append_rows(ctx, c->dtype, k_source.ptr, v_source.ptr, c->k, c->v, (int64_t)append_len, (int)row_elems,
+    st = launch_append_rows(ctx, c->dtype, k_source.ptr, v_source.ptr, c->k, c->v, c->k_f16, (int64_t)append_len, (int)row_elems,
                             (int)c->head_dim, c->dev_table, (int)c->table.page_size, (int64_t)c->table.live_tokens, 0,
                             rotate, (int64_t)(kv_position_offset + c->table.live_tokens), inv_freq);
     if (st) return st;
@@ -1167,6 +1169,23 @@ int32_t flat_paged_kv_cache_append_rotating(flat_paged_kv_cache *cache, flat_buf
                                             uint64_t append_len, float theta, uint64_t kv_position_offset,
                                             uint64_t *new_len) {
     return paged_append_impl(cache, k_source, v_source, append_len, 1, theta, kv_position_offset, new_len);
+}
+
+int32_t flat_paged_kv_cache_enable_prefill_shadow(flat_paged_kv_cache *c) {
+    if (!c) return FLAT_ERR_NULL_POINTER;
+    flat_ctx *ctx = c->ctx;
+    if (c->dtype != FLAT_BF16)
+        return fail(ctx, FLAT_ERR_UNSUPPORTED_DTYPE, "the prefill shadow exists for bf16 caches only (an f32 cache needs none)");
+    if (c->k_f16) return FLAT_OK;
+    cudaError_t e = cudaMalloc(&c->k_f16, c->tensor_bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        c->k_f16 = nullptr;
+        return fail(ctx, FLAT_ERR_EXECUTION, "cudaMalloc of %llu bytes failed: %s", (unsigned long long)c->tensor_bytes,
+                    cudaGetErrorString(e));
+    }
+    // what the cache already holds (zeros where nothing was appended yet)
+    return launch_shadow_fill(ctx, c->k, c->k_f16, (int64_t)(c->tensor_bytes / 2));
 }
 
 int32_t flat_paged_kv_cache_reset(flat_paged_kv_cache *cache) {
@@ -1720,7 +1739,14 @@ int32_t flat_chunked_prefill_paged(flat_ctx *ctx, flat_paged_kv_cache *cache, ui
     p.page_size = (int)cache->table.page_size;
     p.max_pages = (int)cache->table.physical_pages;
     p.page_row_stride = p.kv_rs;
-    if (dtype == FLAT_BF16 && forward_sm100_supported(p)) return launch_forward_sm100(ctx, p);
+    if (dtype == FLAT_BF16 && forward_sm100_supported(p)) {
+        if (cache->k_f16) {
+            // the binary16 shadow feeds the tensor core directly: no per-tile conversion in shared memory
+            p.k = cache->k_f16;
+            p.k_f16 = 1;
+        }
+        return launch_forward_sm100(ctx, p);
+    }
     return launch_forward_simt(ctx, dtype, p);
 }
 

@@ -143,6 +143,7 @@ struct FwdParams {
     int64_t alibi_q_off, alibi_kv_off;
     float alibi_max_abs_slope;           // host-side copy of max |slope|
     int f16_io;                          // 16-bit storage is IEEE binary16 instead of bf16 (forward only)
+    int k_f16;                           // K alone is binary16 (the prefill shadow of a bf16 paged cache): no in-kernel conversion
 };
 
 // Generic SIMT forward (f32 arithmetic; T = float or __nv_bfloat16 storage).
@@ -225,8 +226,10 @@ int launch_finite_scan(flat_ctx *ctx, const FiniteScan &scan, cudaStream_t strea
 // ---- KV cache --------------------------------------------------------------------------------
 // Copies `rows` source rows of `row_elems` elements to destination rows dst_rows[i] (device
 // array of int64), optionally rotating each head_dim-wide head slice at positions pos0 + i.
+// k_shadow: optional binary16 copy of the stored K (bf16 caches), same row layout as k_dst.
+int launch_shadow_fill(flat_ctx *ctx, const void *k, void *shadow, int64_t elements);
 int launch_append_rows(flat_ctx *ctx, int dtype, const void *k_src, const void *v_src, void *k_dst,
-                       void *v_dst, int64_t rows, int row_elems, int head_dim,
+                       void *v_dst, void *k_shadow, int64_t rows, int row_elems, int head_dim,
                        const int32_t *page_table, int page_size, int64_t first_logical,
                        int64_t dst_row0, int rotate, int64_t pos0, const float *inv_freq);
 

@@ -1115,7 +1115,8 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     int64_t k_rs = p.kv_rs, k_hs = p.kv_hs, k_bs = p.kv_bs;
     bool k_f16 = false;
     const bool io16 = p.f16_io != 0;                    // binary16 storage: every operand is fp16 from the start
-    const bool convk = p.rope_q && !p.rope_k && !io16;  // Q rotated against already rotated bf16 K: K tiles become fp16 in smem
+    const bool k_shadow = p.k_f16 != 0;                 // K arrives as binary16 although V and Q are bf16 (paged cache shadow)
+    const bool convk = p.rope_q && !p.rope_k && !io16 && !k_shadow;  // Q rotated against rotated bf16 K: K tiles become fp16 in smem
     const bool q_f16 = p.rope_q || io16;
     char *scratch = scratch_ptr(ctx);
     const float2 *q_table = nullptr;
@@ -1153,7 +1154,7 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     if (p.page_table) {
         // physical layout [pages, page_size, kv_heads*D]: dims (d, token in page, head, page)
         const int64_t row = p.page_row_stride;
-        if ((st = make_map(ctx, &kp.map_k, io16, p.k, D, p.page_size, p.kv_heads, p.max_pages, row, p.kv_hs,
+        if ((st = make_map(ctx, &kp.map_k, io16 || k_shadow, p.k, D, p.page_size, p.kv_heads, p.max_pages, row, p.kv_hs,
                            row * p.page_size, p.page_size))) return st;
         if ((st = make_map(ctx, &kp.map_v, io16, p.v, D, p.page_size, p.kv_heads, p.max_pages, row, p.kv_hs,
                            row * p.page_size, p.page_size))) return st;
@@ -1170,7 +1171,7 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     kp.causal = p.causal;
     kp.causal_off = p.causal_off;
     kp.scale_log2 = p.scale * kLog2e;
-    kp.idesc_qk = make_idesc(q_f16 ? kFmtF16 : kFmtBF16, (k_f16 || convk || io16) ? kFmtF16 : kFmtBF16, 0, 0, 128, 128);
+    kp.idesc_qk = make_idesc(q_f16 ? kFmtF16 : kFmtBF16, (k_f16 || convk || io16 || k_shadow) ? kFmtF16 : kFmtBF16, 0, 0, 128, 128);
     kp.idesc_pv = io16 ? make_idesc(kFmtF16, kFmtF16, 0, 1, 128, (uint32_t)D) : make_idesc(kFmtBF16, kFmtBF16, 0, 1, 128, (uint32_t)D);
     kp.page_table = p.page_table;
     kp.page_size = p.page_size;

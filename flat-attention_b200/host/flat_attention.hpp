@@ -355,6 +355,8 @@ class CudaPagedKvCache {
         ctx_.check(flat_paged_kv_cache_append_rotating(c_, k_source, v_source, append_len, theta, kv_position_offset, &n));
         return n;
     }
+    // binary16 copy of K for the tensor-core chunked prefill (bf16 caches; allocates once)
+    void enable_prefill_shadow() { ctx_.check(flat_paged_kv_cache_enable_prefill_shadow(c_)); }
     void reset() { ctx_.check(flat_paged_kv_cache_reset(c_)); }
     uint64_t len() const { return flat_paged_kv_cache_len(c_); }
     bool is_empty() const { return len() == 0; }

@@ -358,6 +358,14 @@ int32_t flat_paged_kv_cache_append_rotating(flat_paged_kv_cache *cache, flat_buf
                                             flat_buffer v_source, uint64_t append_len,
                                             float theta, uint64_t kv_position_offset,
                                             uint64_t *new_len);
+/* Optional, bf16 caches: keep a binary16 copy of K beside the bf16 K (one more K-sized device
+ * allocation, made by this call; existing contents are converted, later appends write both).
+ * The chunked prefill rotates Q to binary16, and the tensor core takes both score operands in one
+ * format: without the copy every K tile is converted in shared memory inside the attention kernel,
+ * with it K tiles are used as they arrive.  The copy holds exactly the bf16 values of the cache
+ * (saturated beyond the binary16 range), so results do not change.  Writes made to k_buffer()
+ * behind the cache's back are not mirrored.  No counterpart in the reference (its cache is f32). */
+int32_t flat_paged_kv_cache_enable_prefill_shadow(flat_paged_kv_cache *cache);
 int32_t flat_paged_kv_cache_reset(flat_paged_kv_cache *cache);
 uint64_t flat_paged_kv_cache_len(const flat_paged_kv_cache *cache);
 uint64_t flat_paged_kv_cache_generation(const flat_paged_kv_cache *cache);

@@ -37,14 +37,34 @@ def test_chunked_prefill_equals_contiguous(B, Hq, Hkv, N, D, causal, chunk):
                                                         (fa.BF16, 8, 2, 128, 300, 128, 16), (fa.BF16, 4, 4, 64, 90, 32, 16),
                                                         # more (query block, head) items than SMs, ragged last block
                                                         (fa.BF16, 64, 8, 64, 700, 640, 16)])
-def test_chunked_prefill_into_growing_paged_cache(dtype, Hq, Hkv, D, N, chunk, ps):
+@pytest.mark.parametrize("shadow", [False, True])
+def test_chunked_prefill_into_growing_paged_cache(dtype, Hq, Hkv, D, N, chunk, ps, shadow):
     """Each chunk appends rotated K and V to the paged cache, then attends causally to the whole
-    cache.  Oracle: the cache contents as stored (pre-rotated K), Q rotation materialised."""
+    cache.  Oracle: the cache contents as stored (pre-rotated K), Q rotation materialised.  With the binary16
+    K shadow (bf16 caches) the attention kernel reads K tiles without converting them; results agree bit for bit
+    with the converting kernel's tolerance class (the shadow holds the same bf16 values)."""
     c = ctx()
     theta, off = 5e5, 3
     td = fa.torch_dtype(dtype)
     pages = (N + ps - 1) // ps + 2
     cache = fa.CudaPagedKvCache(c, dtype, ps, pages, Hkv, D)
+    if shadow:
+        if dtype != fa.BF16:
+            with pytest.raises(fa.FlatAttentionError) as e:
+                cache.enable_prefill_shadow()
+            assert e.value.kind == "UnsupportedDtype"
+            return
+        # switched on after the first chunk is in: the existing rows are converted, later appends write both copies
+        first = min(chunk, N)
+        warm = c.empty_bytes(first * Hq * D * 2 + Hq * first * 4)
+        q0 = bf16_round(ramp(N * Hq * D, 0.2).reshape(N, Hq * D))
+        k0 = bf16_round(ramp(N * Hkv * D, 0.8).reshape(N, Hkv * D))
+        v0 = bf16_round(ramp(N * Hkv * D, 1.4).reshape(N, Hkv * D))
+        c.chunked_prefill_paged(cache, Hq, first, fa.config(True), theta, off, dev(q0[:first], td), dev(k0[:first], td),
+                                dev(v0[:first], td), warm)
+        cache.enable_prefill_shadow()
+        cache.enable_prefill_shadow()  # idempotent
+        cache.reset()
     q, k, v = ramp(N * Hq * D, 0.2).reshape(N, Hq * D), ramp(N * Hkv * D, 0.8).reshape(N, Hkv * D), \
         ramp(N * Hkv * D, 1.4).reshape(N, Hkv * D)
     if dtype == fa.BF16:
@@ -98,6 +118,7 @@ def test_config4_chunked_prefill_full_size_sampled_rows():
     k = torch.randn(N, Hkv * D, generator=torch.Generator().manual_seed(32)).bfloat16()
     v = torch.randn(N, Hkv * D, generator=torch.Generator().manual_seed(33)).bfloat16()
     cache = fa.CudaPagedKvCache(c, fa.BF16, ps, N // ps + 8, Hkv, D)
+    cache.enable_prefill_shadow()  # as the benchmark runs it: K tiles reach the tensor core without conversion
     out = c.empty_bytes(chunk * Hq * D * 2 + Hq * chunk * 4)
     rng = np.random.default_rng(4)
     picked = []  # (chunk start, [(head, row)], O rows, LSE values)
