@@ -85,6 +85,8 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 
 struct KernelParams {
     CUtensorMap map_q, map_k, map_v;
+    CUtensorMap map_o;  // O as (d, row, head, batch) with boxes of 64 columns x 128 rows: the epilogue's bulk stores
+    int o_tma;          // the epilogue stores O tiles through shared memory with bulk copies (not for padded batches)
     void *o;
     float *lse;
     int64_t o_bs, o_hs, o_rs, lse_hs;
@@ -123,8 +125,10 @@ template <int D, bool CONVK> struct Cfg {
     static constexpr int kBoxBytes = kTileRows * 128;      // 128 rows x 128 B
     static constexpr int kTileBytes = kBoxes * kBoxBytes;  // one Q / K / V tile
     static constexpr int kStages = D == 128 ? 4 : 8;  // K/V ring entries
-    static constexpr int kBars = 2 + 3 * kStages + 10;
-    static constexpr int kSmemBytes = (2 + kStages) * kTileBytes + kBars * 8 + 16 + 32 + 1024;
+    static constexpr int kOutStageBytes = kTileRows * 128;  // one box of the O tile: 128 rows x 64 columns of 16 bits
+    static constexpr int kBars = 2 + 3 * kStages + 14;
+    static constexpr int kSmemBytes = (2 + kStages) * kTileBytes + 2 * kOutStageBytes + kBars * 8 + 16 + 32 + 1024;
+    static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
 };
 
 __device__ __forceinline__ void record_timeout(const KernelParams &p, int where) {
@@ -242,7 +246,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t *q_s = smem;
     uint8_t *kv_s = smem + 2 * C::kTileBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(kv_s + C::kStages * C::kTileBytes);
+    uint8_t *o_stage = kv_s + C::kStages * C::kTileBytes;  // per slot: staging of one 64-column box of the O tile
+    uint64_t *bars = reinterpret_cast<uint64_t *>(o_stage + 2 * C::kOutStageBytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + C::kBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
     volatile SplitRecord *split_rec = reinterpret_cast<volatile SplitRecord *>(tmem_slot + 2);
@@ -257,6 +262,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     auto q_ready = [&](int w) { return bar0 + 8u * (8 + 2 * C::kStages + w); };
     auto q_empty = [&](int w) { return bar0 + 8u * (10 + 2 * C::kStages + w); };
     auto k_ready = [&](int s) { return bar0 + 8u * (12 + 2 * C::kStages + s); };  // K tile converted (CONVK)
+    auto o_stage_full = [&](int w) { return bar0 + 8u * (12 + 3 * C::kStages + w); };  // a box of O is staged
+    auto o_stage_free = [&](int w) { return bar0 + 8u * (14 + 3 * C::kStages + w); };  // ... and has been read out
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -270,6 +277,8 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             mbar_init(o_final(w), 1);
             mbar_init(q_ready(w), 4);
             mbar_init(q_empty(w), 1);
+            mbar_init(o_stage_full(w), 4);
+            mbar_init(o_stage_free(w), 1);
         }
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(kv_full(s), 1);
@@ -281,6 +290,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
         tma_prefetch_desc(&p.map_q);
         tma_prefetch_desc(&p.map_k);
         tma_prefetch_desc(&p.map_v);
+        tma_prefetch_desc(&p.map_o);
         if constexpr (SPLIT) {
             // the part this CTA runs in the last round, if any: decoded once, read by every role
             const int g = (int)gridDim.x, k_last = p.split_first / g;
@@ -531,6 +541,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
         bool ok = true;
         uint32_t done = 0;     // finished items of this slot (its tile was inside q_len)
         uint32_t s_waits = 0;  // score tiles of this slot consumed so far
+        uint32_t o_boxes = 0;  // boxes of O this slot has staged so far
 
         // Iteration k runs the KV loop of item k, then rotates the Q tile of item k + 1 (its TMA was issued as soon as
         // the slot's last S MMA had completed), then stores item k: the next item's first S MMA runs during the
@@ -714,6 +725,14 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     if ((warp & 3) == 0 && lane == 0) TRACEB(k, w, 1);
                     if (ok) {
                         uint8_t *tile = q_s + w * C::kTileBytes;
+                        // all of the thread's chunks are fetched before any is written back: the loads are then in
+                        // flight together instead of each waiting behind the previous step's store
+                        uint4 raw[CH];
+#pragma unroll
+                        for (int st = 0; st < CH; ++st) {
+                            const int rt = lane_base + st * RPS + lane / CH;  // row in tile
+                            raw[st] = *reinterpret_cast<const uint4 *>(tile + (ch >> 3) * C::kBoxBytes + rt * 128 + (((ch & 7) ^ (rt & 7)) << 4));
+                        }
 #pragma unroll
                         for (int st = 0; st < CH; ++st) {
                             const int rt = lane_base + st * RPS + lane / CH;  // row in tile
@@ -727,8 +746,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                                 }
                             }
                             if (first_row + rt >= nx.q_len) continue;  // rows past q_len are not used
-                            const uint4 raw = *reinterpret_cast<const uint4 *>(tile + off);
-                            const uint32_t in[4] = {raw.x, raw.y, raw.z, raw.w};
+                            const uint32_t in[4] = {raw[st].x, raw[st].y, raw[st].z, raw[st].w};
                             uint32_t hi[4];
 #pragma unroll
                             for (int e = 0; e < 4; ++e) {
@@ -782,6 +800,56 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                                                          __uint_as_float(r[q4 * 4 + 2]), __uint_as_float(r[q4 * 4 + 3]));
                     }
                     p.part_ml[prow] = make_float2(m, l);
+                    tc_fence_before();
+                } else if (p.o_tma) {
+                    // O leaves through shared memory: every thread writes its row's 128 bytes of a 64-column box in the
+                    // swizzled box layout, the slot's first thread sends the box with one bulk store (whole lines,
+                    // rows past q_len clipped by the tensor map), instead of 32-byte stores 256 bytes apart per thread
+                    const float inv = 1.0f / l;
+                    uint8_t *stg = o_stage + w * C::kOutStageBytes;
+#pragma unroll
+                    for (int hf = 0; hf < D / 64 && ok; ++hf, ++o_boxes) {
+                        uint32_t r[64];
+                        tmem_ld32(t_o + hf * 64, r);
+                        tmem_ld32(t_o + hf * 64 + 32, r + 32);
+                        tc_wait_ld();
+                        uint32_t pk[32];
+#pragma unroll
+                        for (int i = 0; i < 64; i += 2) {
+                            if constexpr (F16IO) {
+                                __half2 h2 = __floats2half2_rn(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                                pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                            } else {
+                                __nv_bfloat162 h2 =
+                                    __floats2bfloat162_rn(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv);
+                                pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
+                            }
+                        }
+                        // the previous box has left the staging space (the first wait passes at once)
+                        if (!mbar_wait(o_stage_free(w), (o_boxes & 1) ^ 1, abort_flag)) {
+                            record_timeout(p, 320 + w);
+                            ok = false;
+                            break;
+                        }
+#pragma unroll
+                        for (int ch = 0; ch < 8; ++ch)
+                            *reinterpret_cast<uint4 *>(stg + row_in_tile * 128 + ((ch ^ (row_in_tile & 7)) << 4)) =
+                                make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
+                        fence_proxy_async();  // generic-proxy writes -> visible to the bulk copy's async proxy
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(o_stage_full(w));
+                        if ((warp & 3) == 0 && lane == 0) {
+                            if (mbar_wait(o_stage_full(w), o_boxes & 1, abort_flag)) {
+                                tma_store_4d(&p.map_o, hf * 64, it.r0 + w * kTileRows, h, b, smem_u32(stg));
+                                bulk_commit_group();
+                                bulk_wait_group_read0();
+                                mbar_arrive(o_stage_free(w));
+                            } else {
+                                record_timeout(p, 325 + w);
+                            }
+                        }
+                    }
+                    if (row < it.q_len) p.lse[((long long)b * p.q_heads + h) * p.lse_hs + row] = (m + log2f(l)) * kLn2;
                     tc_fence_before();
                 } else {
                 const float inv = 1.0f / l;
@@ -1162,6 +1230,11 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
         if ((st = make_map(ctx, &kp.map_k, k_f16 || io16, k_ptr, D, p.kv_len, p.kv_heads, p.batch, k_rs, k_hs, k_bs, kTileRows))) return st;
         if ((st = make_map(ctx, &kp.map_v, io16, p.v, D, p.kv_len, p.kv_heads, p.batch, p.kv_rs, p.kv_hs, p.kv_bs, kTileRows))) return st;
     }
+    // the epilogue's bulk stores clip at the call's q_len, not at a sequence's active length: padded batches keep the
+    // per-thread stores
+    kp.o_tma = p.varlen ? 0 : 1;
+    if (kp.o_tma && (st = make_map(ctx, &kp.map_o, io16, p.o, D, p.q_len, p.q_heads, p.batch, p.o_rs, p.o_hs, p.o_bs, kTileRows)))
+        return st;
     kp.o = p.o;
     kp.lse = p.lse;
     kp.o_bs = p.o_bs; kp.o_hs = p.o_hs; kp.o_rs = p.o_rs; kp.lse_hs = p.lse_hs;
