@@ -143,7 +143,8 @@ def lib() -> C.CDLL:
         _lib.flat_paged_kv_cache_table.restype = C.c_void_p
         _lib.flat_paged_kv_cache_table.argtypes = [C.c_void_p]
         for name in ("flat_ctx_destroy", "flat_paged_kv_table_destroy", "flat_paged_kv_cache_destroy",
-                     "flat_resident_kv_cache_destroy", "flat_resident_kv_cache_reset"):
+                     "flat_resident_kv_cache_destroy", "flat_resident_kv_cache_reset", "flat_prepared_forward_destroy",
+                     "flat_prepared_backward_destroy"):
             getattr(_lib, name).restype = None
             getattr(_lib, name).argtypes = [C.c_void_p]
     return _lib
@@ -253,6 +254,18 @@ class Context:
 
     def reserve_workspace(self, nbytes: int):
         self.check(lib().flat_ctx_reserve_workspace(self.h, C.c_uint64(nbytes)))
+
+    def reserve_rope_tables(self, rows: int, head_dim: int):
+        """Pre-size the cached (cos, sin) tables so RoPE calls with moving positions never allocate."""
+        self.check(lib().flat_ctx_reserve_rope_tables(self.h, C.c_uint64(rows), C.c_uint64(head_dim)))
+
+    def prepare_forward(self, dtype, layout, shp, cfg, rot, q, k, v, out) -> "PreparedForward":
+        """*Pipeline::prepare (src/wgpu_forward_grouped.rs:352-493): validate once, then `encode()` only enqueues."""
+        return PreparedForward(self, dtype, layout, shp, cfg, rot, q, k, v, out)
+
+    def prepare_backward(self, dtype, shp, cfg, packed_inputs, packed_grads) -> "PreparedBackward":
+        """WgpuGroupedBackwardRecomputePipeline::prepare (src/wgpu_backward_grouped.rs:231-300)."""
+        return PreparedBackward(self, dtype, shp, cfg, packed_inputs, packed_grads)
 
     def set_kernel_timing(self, enabled: bool):
         self.check(lib().flat_ctx_set_kernel_timing(self.h, C.c_int32(int(enabled))))
@@ -447,6 +460,45 @@ class Context:
     def backward_mha(self, dtype, shp, cfg, packed_inputs, packed_grads):
         self.check(lib().flat_backward_mha(self.h, C.c_int32(dtype), C.byref(shp), C.byref(cfg), buf(packed_inputs),
                                            buf(packed_grads)))
+
+
+class PreparedForward:
+    """PreparedGroupedForward (src/wgpu_forward_grouped.rs:54-91): a validated forward pass; keeps the tensors alive."""
+
+    def __init__(self, ctx: Context, dtype, layout, shp, cfg, rot, q, k, v, out):
+        self.ctx, self._keep = ctx, (q, k, v, out)
+        h = C.c_void_p()
+        ctx.check(lib().flat_forward_prepare(ctx.h, C.c_int32(dtype), C.c_int32(layout), C.byref(shp), C.byref(cfg),
+                                             C.byref(rot) if rot is not None else None, buf(q), buf(k), buf(v), buf(out),
+                                             C.byref(h)))
+        self.h = h
+
+    def encode(self):
+        self.ctx.check(lib().flat_forward_encode_prepared(self.ctx.h, self.h))
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().flat_prepared_forward_destroy(self.h)
+            self.h = None
+
+
+class PreparedBackward:
+    """PreparedGroupedBackwardRecompute (src/wgpu_backward_grouped.rs:124-129)."""
+
+    def __init__(self, ctx: Context, dtype, shp, cfg, packed_inputs, packed_grads):
+        self.ctx, self._keep = ctx, (packed_inputs, packed_grads)
+        h = C.c_void_p()
+        ctx.check(lib().flat_backward_prepare(ctx.h, C.c_int32(dtype), C.byref(shp), C.byref(cfg), buf(packed_inputs),
+                                              buf(packed_grads), C.byref(h)))
+        self.h = h
+
+    def encode(self):
+        self.ctx.check(lib().flat_backward_encode_prepared(self.ctx.h, self.h))
+
+    def __del__(self):
+        if getattr(self, "h", None):
+            lib().flat_prepared_backward_destroy(self.h)
+            self.h = None
 
 
 def _b(x) -> Buffer:

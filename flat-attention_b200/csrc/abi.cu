@@ -673,6 +673,25 @@ int32_t flat_ctx_reserve_workspace(flat_ctx *ctx, uint64_t bytes) {
     return ensure_workspace(ctx, bytes);
 }
 uint64_t flat_ctx_workspace_bytes(const flat_ctx *ctx) { return ctx ? ctx->workspace_bytes : 0; }
+
+int32_t flat_ctx_reserve_rope_tables(flat_ctx *ctx, uint64_t rows, uint64_t head_dim) {
+    if (!ctx) return FLAT_ERR_NULL_POINTER;
+    if (head_dim == 0 || head_dim % 2 != 0 || head_dim > (uint64_t)kMaxHeadDim)
+        return fail(ctx, FLAT_ERR_INVALID_ROTARY_HEAD_DIM, "rotary attention head_dim must be non-zero, even and at most %d", kMaxHeadDim);
+    if (rows == 0 || rows > ((uint64_t)1 << 31)) return fail(ctx, FLAT_ERR_INDEX_SPACE_EXCEEDED, "table rows out of range");
+    const uint64_t bytes = rows * (head_dim / 2) * 2 * sizeof(float);
+    for (auto &t : ctx->rope_tables) {
+        if (t.bytes >= bytes) continue;
+        FLAT_CUDA_OK(ctx, cudaStreamSynchronize(ctx->stream));  // kernels in flight may still read the old table
+        if (t.dev) FLAT_CUDA_OK(ctx, cudaFree(t.dev));
+        t.dev = nullptr;
+        t.bytes = 0;
+        t.rows = 0;
+        FLAT_CUDA_OK(ctx, cudaMalloc(&t.dev, bytes));
+        t.bytes = bytes;
+    }
+    return FLAT_OK;
+}
 uint64_t flat_ctx_launch_count(const flat_ctx *ctx) { return ctx ? ctx->launches : 0; }
 
 int32_t flat_ctx_device_status(flat_ctx *ctx) {
@@ -805,6 +824,44 @@ int32_t flat_forward_projection_rope_asymmetric(flat_ctx *ctx, int32_t dtype, co
     ForwardCall c{dtype, FLAT_LAYOUT_PROJECTION, true, rotary, nullptr, 0, false};
     return forward_common(ctx, c, shape, config, q, k, v, out_and_lse);
 }
+
+// ---- prepared passes (PreparedGroupedForward, src/wgpu_forward_grouped.rs:352-529) ---------------
+struct flat_prepared_forward {
+    flat_ctx *ctx;
+    int dtype;
+    FwdParams params;  // validated once; encode_prepared launches from it
+};
+
+int32_t flat_forward_prepare(flat_ctx *ctx, int32_t dtype, int32_t layout, const flat_attention_shape *shape,
+                             const flat_attention_config *config, const flat_rotary_config *rotary, flat_buffer q,
+                             flat_buffer k, flat_buffer v, flat_buffer out_and_lse, flat_prepared_forward **out) {
+    if (!ctx) return FLAT_ERR_NULL_POINTER;
+    if (!out) return fail(ctx, FLAT_ERR_NULL_POINTER, "prepared-pass output is null");
+    *out = nullptr;
+    if (layout != FLAT_LAYOUT_HEAD_MAJOR && layout != FLAT_LAYOUT_PROJECTION)
+        return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE, "unknown layout %d", layout);
+    ForwardCall c{dtype, layout, rotary != nullptr, rotary, nullptr, 0, false};
+    FwdParams p{};
+    int st = forward_common(ctx, c, shape, config, q, k, v, out_and_lse, &p);
+    if (st) return st;
+    // everything encode_prepared needs is made ready now: the scratch is sized, so encoding never allocates
+    if (storage16(dtype) && forward_sm100_supported(p) &&
+        (st = ensure_workspace(ctx, kWorkspaceMeta + forward_sm100_workspace_bytes(ctx, p))))
+        return st;
+    auto *prep = new (std::nothrow) flat_prepared_forward{ctx, dtype, p};
+    if (!prep) return fail(ctx, FLAT_ERR_EXECUTION, "out of host memory");
+    *out = prep;
+    return FLAT_OK;
+}
+
+int32_t flat_forward_encode_prepared(flat_ctx *ctx, const flat_prepared_forward *prepared) {
+    if (!ctx) return FLAT_ERR_NULL_POINTER;
+    if (!prepared) return fail(ctx, FLAT_ERR_NULL_POINTER, "prepared pass is null");
+    if (prepared->ctx != ctx) return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE, "the pass was prepared on another context");
+    return launch_forward(ctx, prepared->dtype, prepared->params);
+}
+
+void flat_prepared_forward_destroy(flat_prepared_forward *prepared) { delete prepared; }
 
 int32_t flat_forward_runtime_telemetry(flat_ctx *ctx, int32_t dtype, int32_t layout, const flat_attention_shape *shape,
                                        const flat_rotary_config *rotary, flat_dispatch_telemetry *out) {
@@ -1782,9 +1839,9 @@ int32_t flat_backward_layout_for(int32_t dtype, const flat_attention_shape *shap
     return FLAT_OK;
 }
 
-int32_t flat_backward_grouped(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
-                              const flat_attention_config *config, flat_buffer packed_inputs,
-                              flat_buffer packed_grads) {
+// validation and parameter block shared by the direct and the prepared backward entry points
+static int backward_build(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape, const flat_attention_config *config,
+                          flat_buffer packed_inputs, flat_buffer packed_grads, BwdParams *out) {
     if (!ctx) return FLAT_ERR_NULL_POINTER;
     int st;
     if ((st = check_dtype(ctx, dtype))) return st;
@@ -1808,9 +1865,57 @@ int32_t flat_backward_grouped(flat_ctx *ctx, int32_t dtype, const flat_attention
     p.seq_len = (int)shape->query_len; p.head_dim = (int)shape->head_dim; p.group = p.q_heads / p.kv_heads;
     p.causal = config->causal ? 1 : 0;
     p.scale = scale;
+    *out = p;
+    return FLAT_OK;
+}
+
+static int backward_launch(flat_ctx *ctx, int dtype, const BwdParams &p) {
     if (dtype == FLAT_BF16 && backward_sm100_supported(p)) return launch_backward_sm100(ctx, p);
     return launch_backward_simt(ctx, dtype, p);
 }
+
+int32_t flat_backward_grouped(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
+                              const flat_attention_config *config, flat_buffer packed_inputs,
+                              flat_buffer packed_grads) {
+    BwdParams p{};
+    int st = backward_build(ctx, dtype, shape, config, packed_inputs, packed_grads, &p);
+    if (st) return st;
+    return backward_launch(ctx, dtype, p);
+}
+
+// PreparedGroupedBackwardRecompute (src/wgpu_backward_grouped.rs:231-326)
+struct flat_prepared_backward {
+    flat_ctx *ctx;
+    int dtype;
+    BwdParams params;
+};
+
+int32_t flat_backward_prepare(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
+                              const flat_attention_config *config, flat_buffer packed_inputs, flat_buffer packed_grads,
+                              flat_prepared_backward **out) {
+    if (!ctx) return FLAT_ERR_NULL_POINTER;
+    if (!out) return fail(ctx, FLAT_ERR_NULL_POINTER, "prepared-pass output is null");
+    *out = nullptr;
+    BwdParams p{};
+    int st = backward_build(ctx, dtype, shape, config, packed_inputs, packed_grads, &p);
+    if (st) return st;
+    if (dtype == FLAT_BF16 && backward_sm100_supported(p) &&
+        (st = ensure_workspace(ctx, kWorkspaceMeta + backward_sm100_workspace_bytes(p))))
+        return st;
+    auto *prep = new (std::nothrow) flat_prepared_backward{ctx, dtype, p};
+    if (!prep) return fail(ctx, FLAT_ERR_EXECUTION, "out of host memory");
+    *out = prep;
+    return FLAT_OK;
+}
+
+int32_t flat_backward_encode_prepared(flat_ctx *ctx, const flat_prepared_backward *prepared) {
+    if (!ctx) return FLAT_ERR_NULL_POINTER;
+    if (!prepared) return fail(ctx, FLAT_ERR_NULL_POINTER, "prepared pass is null");
+    if (prepared->ctx != ctx) return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE, "the pass was prepared on another context");
+    return backward_launch(ctx, prepared->dtype, prepared->params);
+}
+
+void flat_prepared_backward_destroy(flat_prepared_backward *prepared) { delete prepared; }
 
 int32_t flat_backward_mha(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
                           const flat_attention_config *config, flat_buffer packed_inputs, flat_buffer packed_grads) {

@@ -164,6 +164,28 @@ class CudaGroupedForwardPipeline {
                                         pass.out_and_lse));
         return forward_layout(dtype_, pass.shape);
     }
+    // PreparedGroupedForward (src/wgpu_forward_grouped.rs:54-91): validated once by prepare, then only enqueued
+    class Prepared {
+      public:
+        Prepared(const Context &ctx, flat_prepared_forward *h) : ctx_(ctx), h_(h) {}
+        ~Prepared() { flat_prepared_forward_destroy(h_); }
+        Prepared(const Prepared &) = delete;
+        Prepared &operator=(const Prepared &) = delete;
+        Prepared(Prepared &&o) noexcept : ctx_(o.ctx_), h_(o.h_) { o.h_ = nullptr; }
+        const flat_prepared_forward *raw() const { return h_; }
+
+      private:
+        const Context &ctx_;
+        flat_prepared_forward *h_;
+    };
+    Prepared prepare(const ForwardPass &pass) const {
+        auto cfg = pass.config.raw();
+        flat_prepared_forward *h = nullptr;
+        ctx_.check(flat_forward_prepare(ctx_.raw(), static_cast<int32_t>(dtype_), FLAT_LAYOUT_HEAD_MAJOR, &pass.shape, &cfg, nullptr,
+                                        pass.q, pass.k, pass.v, pass.out_and_lse, &h));
+        return Prepared(ctx_, h);
+    }
+    void encode_prepared(const Prepared &prepared) const { ctx_.check(flat_forward_encode_prepared(ctx_.raw(), prepared.raw())); }
 
   private:
     const Context &ctx_;

@@ -196,6 +196,12 @@ const char *flat_last_error_detail(const flat_ctx *ctx);
  * backward accumulators) so later encode calls do not allocate. */
 int32_t flat_ctx_reserve_workspace(flat_ctx *ctx, uint64_t bytes);
 uint64_t flat_ctx_workspace_bytes(const flat_ctx *ctx);
+/* Pre-size the context's two cached (cos, sin) tables for calls of up to `rows` positions at
+ * `head_dim`, so that RoPE entry points whose positions change from call to call (chunked
+ * prefill) recompute into memory that exists instead of freeing and allocating.  Together with
+ * flat_ctx_reserve_workspace this makes the encode-style entry points allocation-free, the
+ * contract of the reference's encode functions (src/wgpu_decode.rs:1-8). */
+int32_t flat_ctx_reserve_rope_tables(flat_ctx *ctx, uint64_t rows, uint64_t head_dim);
 /* Number of kernel launches this context has enqueued since creation. */
 uint64_t flat_ctx_launch_count(const flat_ctx *ctx);
 /* Reads the device status word written by kernels: FLAT_OK, FLAT_ERR_DEVICE_WAIT_TIMEOUT (a
@@ -301,6 +307,22 @@ int32_t flat_forward_projection_rope_varlen(flat_ctx *ctx, int32_t dtype,
                                             uint64_t sequence_count, flat_buffer q,
                                             flat_buffer k, flat_buffer v,
                                             flat_buffer out_and_lse);
+
+/* WgpuGroupedForwardPipeline::prepare / encode_prepared (src/wgpu_forward_grouped.rs:352-529;
+ * PreparedGroupedForward :54-91): validate a forward pass once - shape, configuration, rotary
+ * (NULL = none), buffer sizes - size the scratch it needs, and keep the launch parameters; later
+ * flat_forward_encode_prepared calls only enqueue (no validation, no allocation, no
+ * synchronisation) on the context's current stream, for as long as the four buffers stay where
+ * they were.  `layout` selects head-major or projection tensors; rectangular shapes and
+ * pre-rotated K (rotary->rotate_k = 0) are accepted like in the direct entry points.  The handle
+ * belongs to the context it was prepared on. */
+typedef struct flat_prepared_forward flat_prepared_forward;
+int32_t flat_forward_prepare(flat_ctx *ctx, int32_t dtype, int32_t layout, const flat_attention_shape *shape,
+                             const flat_attention_config *config, const flat_rotary_config *rotary,
+                             flat_buffer q, flat_buffer k, flat_buffer v, flat_buffer out_and_lse,
+                             flat_prepared_forward **out);
+int32_t flat_forward_encode_prepared(flat_ctx *ctx, const flat_prepared_forward *prepared);
+void flat_prepared_forward_destroy(flat_prepared_forward *prepared);
 
 /* WgpuFlatAttention::forward / WgpuGroupedAttention::forward / WgpuRotaryGroupedAttention::forward
  * (src/wgpu_backend.rs:445-463, src/wgpu_grouped_backend.rs:126-146,
@@ -581,6 +603,16 @@ int32_t flat_backward_grouped(flat_ctx *ctx, int32_t dtype, const flat_attention
 int32_t flat_backward_mha(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
                           const flat_attention_config *config, flat_buffer packed_inputs,
                           flat_buffer packed_grads);
+
+/* WgpuGroupedBackwardRecomputePipeline::prepare / encode_prepared and
+ * PreparedGroupedBackwardRecompute (src/wgpu_backward_grouped.rs:231-326): the backward pass
+ * validated once, its scratch sized, the launch parameters kept; encode_prepared only enqueues. */
+typedef struct flat_prepared_backward flat_prepared_backward;
+int32_t flat_backward_prepare(flat_ctx *ctx, int32_t dtype, const flat_attention_shape *shape,
+                              const flat_attention_config *config, flat_buffer packed_inputs,
+                              flat_buffer packed_grads, flat_prepared_backward **out);
+int32_t flat_backward_encode_prepared(flat_ctx *ctx, const flat_prepared_backward *prepared);
+void flat_prepared_backward_destroy(flat_prepared_backward *prepared);
 
 /* ---- precision routing and numerical modes -------------------------------------------- */
 

@@ -274,3 +274,56 @@ def test_last_round_items_split_along_kv(B, Hq, Hkv, Nq, Nkv, off, D, causal, ro
     assert c.device_status() == 0
     # the split really ran: the call launched a merge kernel besides the attention kernel (and the K rotation / tables)
     assert c.launch_count() - launches >= 2
+
+
+def test_prepared_forward_and_backward_only_enqueue():
+    """prepare validates once and sizes the scratch; encode_prepared gives the same bits as the direct entry point
+    and neither allocates nor re-validates (src/wgpu_forward_grouped.rs:352-529, src/wgpu_backward_grouped.rs:231-326)."""
+    c = fa.Context(0)
+    B, Hq, Hkv, N, D, theta = 1, 8, 2, 384, 128, 5e5
+    g = torch.Generator().manual_seed(41)
+    q, do = (torch.randn(B, Hq, N, D, generator=g).bfloat16().cuda() for _ in range(2))
+    k, v = (torch.randn(B, Hkv, N, D, generator=g).bfloat16().cuda() for _ in range(2))
+    shp, cfg, rot = fa.shape(B, Hq, Hkv, N, N, D), fa.config(True), fa.rotary(theta, 3)
+    direct, out = c.create_output_buffer(fa.BF16, shp), c.create_output_buffer(fa.BF16, shp)
+    c.forward_grouped_rope(fa.BF16, shp, cfg, rot, q, k, v, direct)
+    c.reserve_rope_tables(N, D)
+    prep = c.prepare_forward(fa.BF16, fa.HEAD_MAJOR, shp, cfg, rot, q, k, v, out)
+    ws, launches = c.workspace_bytes(), c.launch_count()
+    for _ in range(3):
+        out.fill_(0x7f)
+        prep.encode()
+    c.synchronize()
+    assert torch.equal(out, direct) and c.workspace_bytes() == ws and c.launch_count() - launches == 6  # K rotation + attention
+    # errors surface at prepare time, with the direct entry point's variants
+    with pytest.raises(fa.FlatAttentionError) as e:
+        c.prepare_forward(fa.BF16, fa.HEAD_MAJOR, shp, cfg, rot, q, k, v, out[:-8])
+    assert e.value.kind == "BufferTooSmall"
+    with pytest.raises(fa.FlatAttentionError) as e:
+        c.prepare_forward(fa.BF16, fa.HEAD_MAJOR, fa.shape(B, Hq, 3, N, N, D), cfg, rot, q, k, v, out)
+    assert e.value.kind == "InvalidHeadGrouping"
+    other = fa.Context(0)
+    st = fa.lib().flat_forward_encode_prepared(other.h, prep.h)
+    assert fa.STATUS[st] == "UnsupportedShape"
+    # backward
+    fwd = c.create_output_buffer(fa.BF16, shp)
+    c.forward_grouped(fa.BF16, shp, cfg, q, k, v, fwd)
+    FL, L = fa.forward_layout(fa.BF16, shp), fa.backward_layout(fa.BF16, shp)
+    packed = c.empty_bytes(L.input_bytes)
+    for off, t in ((L.q_offset, q), (L.k_offset, k), (L.v_offset, v), (L.d_out_offset, do)):
+        packed[off:off + t.numel() * 2] = t.view(torch.uint8).reshape(-1)
+    packed[L.out_offset:L.out_offset + FL.q_bytes] = fwd[:FL.q_bytes]
+    packed[L.lse_offset:L.lse_offset + 4 * FL.lse_elements] = fwd[FL.lse_byte_offset:FL.lse_byte_offset + 4 * FL.lse_elements]
+    g_direct, g_prep = c.empty_bytes(L.output_bytes), c.empty_bytes(L.output_bytes)
+    c.backward_grouped(fa.BF16, shp, cfg, packed, g_direct)
+    bprep = c.prepare_backward(fa.BF16, shp, cfg, packed, g_prep)
+    ws = c.workspace_bytes()
+    for _ in range(2):
+        g_prep.fill_(0x7f)
+        bprep.encode()
+    c.synchronize()
+    assert torch.equal(g_prep, g_direct) and c.workspace_bytes() == ws
+    with pytest.raises(fa.FlatAttentionError) as e:
+        c.prepare_backward(fa.BF16, shp, cfg, packed[:-4], g_prep)
+    assert e.value.kind == "BufferTooSmall"
+    assert c.device_status() == 0
