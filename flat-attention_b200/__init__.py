@@ -255,6 +255,10 @@ class Context:
     def reserve_workspace(self, nbytes: int):
         self.check(lib().flat_ctx_reserve_workspace(self.h, C.c_uint64(nbytes)))
 
+    def set_backward_scratch_budget(self, nbytes: int):
+        """Bytes the bf16 backward may use to keep its dS tiles (O(N^2)) instead of recomputing the scores for dQ; 0 = never."""
+        self.check(lib().flat_ctx_set_backward_scratch_budget(self.h, C.c_uint64(nbytes)))
+
     def reserve_rope_tables(self, rows: int, head_dim: int):
         """Pre-size the cached (cos, sin) tables so RoPE calls with moving positions never allocate."""
         self.check(lib().flat_ctx_reserve_rope_tables(self.h, C.c_uint64(rows), C.c_uint64(head_dim)))

@@ -674,6 +674,12 @@ int32_t flat_ctx_reserve_workspace(flat_ctx *ctx, uint64_t bytes) {
 }
 uint64_t flat_ctx_workspace_bytes(const flat_ctx *ctx) { return ctx ? ctx->workspace_bytes : 0; }
 
+int32_t flat_ctx_set_backward_scratch_budget(flat_ctx *ctx, uint64_t bytes) {
+    if (!ctx) return FLAT_ERR_NULL_POINTER;
+    ctx->backward_scratch_budget = bytes;
+    return FLAT_OK;
+}
+
 int32_t flat_ctx_reserve_rope_tables(flat_ctx *ctx, uint64_t rows, uint64_t head_dim) {
     if (!ctx) return FLAT_ERR_NULL_POINTER;
     if (head_dim == 0 || head_dim % 2 != 0 || head_dim > (uint64_t)kMaxHeadDim)
@@ -1900,7 +1906,7 @@ int32_t flat_backward_prepare(flat_ctx *ctx, int32_t dtype, const flat_attention
     int st = backward_build(ctx, dtype, shape, config, packed_inputs, packed_grads, &p);
     if (st) return st;
     if (dtype == FLAT_BF16 && backward_sm100_supported(p) &&
-        (st = ensure_workspace(ctx, kWorkspaceMeta + backward_sm100_workspace_bytes(p))))
+        (st = ensure_workspace(ctx, kWorkspaceMeta + backward_sm100_workspace_bytes(ctx, p))))
         return st;
     auto *prep = new (std::nothrow) flat_prepared_backward{ctx, dtype, p};
     if (!prep) return fail(ctx, FLAT_ERR_EXECUTION, "out of host memory");

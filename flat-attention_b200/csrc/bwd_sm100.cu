@@ -18,6 +18,13 @@
 //
 // The score recompute is done twice (7 GEMM units instead of 5); in exchange nothing is accumulated
 // through global memory.  A prologue kernel writes delta and -LSE*log2(e) to context scratch.
+//
+// When the context's backward scratch budget allows it (flat_ctx_set_backward_scratch_budget), the recompute is
+// spent once only: the KV-stationary kernel also writes every bf16 dS^T tile it forms to scratch (SPILL; one 32 KiB
+// bulk store per streamed tile, issued by an otherwise idle thread), and dQ comes from a third kernel that only
+// streams those tiles and the K tiles through the tensor core, dQ_i = sum_j dS_ij K_j (5 GEMM units executed, no
+// elementwise work, HBM-bound).  The scratch holds one tile per visible (key tile, query tile) pair: O(N^2) bytes,
+// which is why a budget decides.
 // Gradients are written in f32: the accumulators are f32, and a bf16 rounding of a gradient above 4
 // (ulp 2^-5) would by itself use up the 2e-2 absolute error bound.
 #include <cuda.h>
@@ -56,12 +63,14 @@ struct BwdKernelParams {
     CUtensorMap map_q, map_k, map_v, map_do;
     const float *neg_lse2;  // -LSE * log2(e), [B, Hq, N]
     const float *delta;     // dO . O, [B, Hq, N]
-    void *out0, *out1;      // f32 outputs.  KV-stationary kernel: dV, dK; dQ kernel: dQ, null
+    void *out0, *out1;      // f32 outputs.  KV-stationary kernel: dV, dK; dQ kernels: dQ, null
+    uint8_t *ds_spill;      // SPILL: bf16 dS^T tiles, 32 KiB each, tile (key tile j, query tile i) of (batch, q head) at
+                            // ((batch * q_heads + head) * tiles_per_head + (causal ? i (i + 1) / 2 + j : i * n_tiles + j))
     int batch, q_heads, kv_heads, seq_len, group, n_tiles;
     int seq_pad;            // seq_len rounded up to whole tiles: row stride of neg_lse2 / delta
     int causal;
     float scale, scale_log2;
-    uint32_t idesc_k, idesc_mn;
+    uint32_t idesc_k, idesc_mn, idesc_dq;
     DeviceStatus *status;
     long long *trace;
 };
@@ -72,19 +81,31 @@ template <int D> struct BCfg {
     static constexpr int kTileBytes = kBoxes * kBoxBytes;
     static constexpr int kStageBytes = 2 * kTileBytes + 1024;  // two tiles + 128 f32 lse + 128 f32 delta
     static constexpr int kStages = D == 128 ? 2 : 4;
-    static constexpr int kBars = 2 * kStages + 10;  // enough for either kernel's barrier set
+    static constexpr int kBars = 2 * kStages + 12;  // enough for either kernel's barrier set
 #ifdef FLAT_TRACE
     static constexpr int kTraceBytes = 32 * 8 * 4;
 #else
     static constexpr int kTraceBytes = 0;
 #endif
-    static constexpr int kSmemBytes = 2 * kTileBytes + kStages * kStageBytes + kBars * 8 + 16 + kTraceBytes + 1024;
+    static constexpr int kDsBytes = 2 * kBoxBytes;  // SPILL: the dS^T tile (128 keys x 128 queries, bf16) staged for its bulk store
+    // the dynamic shared array is declared 1024-byte aligned (the 128-byte swizzle needs it): no slack is added
+    static constexpr int kSmemBytes = 2 * kTileBytes + kStages * kStageBytes + kDsBytes + kBars * 8 + 16 + kTraceBytes;
+    static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
 };
+
+__device__ __forceinline__ long long ds_tile_index(const BwdKernelParams &p, int b, int head, int j, int i) {
+    const long long per_head = p.causal ? (long long)p.n_tiles * (p.n_tiles + 1) / 2 : (long long)p.n_tiles * p.n_tiles;
+    return ((long long)b * p.q_heads + head) * per_head + (p.causal ? (long long)i * (i + 1) / 2 + j : (long long)i * p.n_tiles + j);
+}
 
 __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
                  "l"(src), "r"(bytes), "r"(bar)
                  : "memory");
+}
+
+__device__ __forceinline__ void bulk_copy_s2g(void *dst, uint32_t src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(src), "r"(bytes) : "memory");
 }
 
 __device__ __forceinline__ void timeout(const BwdKernelParams &p, int where) {
@@ -100,15 +121,15 @@ __device__ __forceinline__ void timeout(const BwdKernelParams &p, int where) {
 //   dP^T = V dO_i^T (runs under phase 1)
 //   dV += P^T dO_i, S^T of tile i + 1  -> phase 2: dS^T = P^T (dP^T - delta) as bf16 over dP^T
 //   dK += dS^T Q_i, dP^T of tile i + 1
-template <int D>
+template <int D, bool SPILL>
 __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_constant__ BwdKernelParams p) {
     using C = BCfg<D>;
-    extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint8_t *st0 = smem;                    // K tile
     uint8_t *st1 = smem + C::kTileBytes;    // V tile
     uint8_t *ring = smem + 2 * C::kTileBytes;
-    uint64_t *bars = reinterpret_cast<uint64_t *>(ring + C::kStages * C::kStageBytes);
+    uint8_t *ds_s = ring + C::kStages * C::kStageBytes;  // SPILL: dS^T tile, two 64-query boxes of 128 key rows x 128 B, swizzled
+    uint64_t *bars = reinterpret_cast<uint64_t *>(ds_s + C::kDsBytes);
     uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + C::kBars);
     volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 #ifdef FLAT_TRACE
@@ -127,6 +148,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
     const uint32_t p_ready = bar0 + 8u * (3 + 2 * C::kStages);    // bf16 P^T written
     const uint32_t ds_ready = bar0 + 8u * (4 + 2 * C::kStages);   // bf16 dS^T written
     const uint32_t acc_final = bar0 + 8u * (5 + 2 * C::kStages);
+    const uint32_t ds_staged = bar0 + 8u * (6 + 2 * C::kStages);  // SPILL: the dS^T tile is complete in shared memory
+    const uint32_t ds_free = bar0 + 8u * (7 + 2 * C::kStages);    // SPILL: ... and its bulk store has read it
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
@@ -142,7 +165,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
     const int n_iter = per_head * p.group;
 
     if (threadIdx.x == 0) {
-        *abort_flag = 0;
+        *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;  // a misplaced shared window would break the swizzle: refuse to run
+        if (*abort_flag) timeout(p, 90);
         mbar_init(st_full, 1);
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(rg_full(s), 1);
@@ -153,6 +177,8 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
         mbar_init(p_ready, 8);
         mbar_init(ds_ready, 8);
         mbar_init(acc_final, 1);
+        mbar_init(ds_staged, 8);
+        mbar_init(ds_free, 1);
         mbar_fence_init();
         fence_proxy_async();
     }
@@ -266,6 +292,23 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                 if (it < 16) TRS(it, 4);
             }
             if (ok) tc_commit(acc_final);
+        } else if (SPILL && warp == kMmaWarp + 1 && lane == 0) {
+            // ================= dS^T spill =================
+            // One bulk store of the staged 32 KiB tile per streamed tile; the elementwise warps may refill the staging
+            // space once the store has read it.  The latency of the stores is spent here, not in the warps that compute.
+            for (int it = 0; it < n_iter; ++it) {
+                if (!mbar_wait(ds_staged, it & 1, abort_flag)) {
+                    timeout(p, 400);
+                    break;
+                }
+                const int t = first + it % per_head;
+                const int hs = h * p.group + it / per_head;
+                bulk_copy_s2g(p.ds_spill + ds_tile_index(p, b, hs, t_own, t) * C::kDsBytes, smem_u32(ds_s), C::kDsBytes);
+                asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                mbar_arrive(ds_free);
+            }
+            asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // the tiles are in memory before the CTA retires
         }
     } else {
         // ================= elementwise warps + epilogue =================
@@ -366,12 +409,36 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_sm100_kernel(const __grid_con
                     ds[i >> 1] = *reinterpret_cast<const uint32_t *>(&dsb);
                 }
                 if (warp == 0 && lane == 0 && it < 16) TRS(16 + it, 5);
+                if constexpr (SPILL) {
+                    // a zero-filled key row past seq_len must reach the dQ kernel as zeros (it scores 0, which against a
+                    // very negative LSE could give a huge P)
+                    if (t_own * kTile + row_local >= p.seq_len) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i) ds[i] = 0u;
+                    }
+                }
                 tmem_st32(t_y, ds);  // bf16 dS^T over dP^T
+                if constexpr (SPILL) {
+                    // ... and into the staging tile of the spill: row = key, this warp group's 64 queries = 128 bytes of box
+                    // `half`, 16-byte chunks swizzled by the row (the layout the dQ kernel's MMAs read it back in)
+                    if (!mbar_wait(ds_free, (it & 1) ^ 1, abort_flag)) {  // the previous tile's store has read the space
+                        timeout(p, 317);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t *row_s = ds_s + half * C::kBoxBytes + row_local * 128;
+#pragma unroll
+                    for (int ch = 0; ch < 8; ++ch)
+                        *reinterpret_cast<uint4 *>(row_s + ((ch ^ (row_local & 7)) << 4)) =
+                            make_uint4(ds[ch * 4], ds[ch * 4 + 1], ds[ch * 4 + 2], ds[ch * 4 + 3]);
+                    fence_proxy_async();  // generic-proxy writes -> visible to the bulk store's async proxy
+                }
                 tc_wait_st();
             }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(ds_ready);
+            if (SPILL && lane == 0) mbar_arrive(ds_staged);
             if (warp == 0 && lane == 0 && it < 16) TRS(it, 7);
         }
         if (ok && !mbar_wait(acc_final, 0, abort_flag)) {
@@ -743,6 +810,136 @@ __global__ void __launch_bounds__(kThreads, 1) bwd_dq_sm100_kernel(const __grid_
 }
 #undef TRS
 
+// dQ from spilled dS^T tiles: one CTA owns 128 queries of one (batch, q_head) and streams, per visible key tile j, the
+// 32 KiB dS^T tile (one contiguous bulk copy: the tile sits in scratch in the swizzled layout it was staged in) and
+// the K_j tile; dQ += dS_ij K_j is eight SS MMAs (A = the dS^T tile read M-major, B = K_j read N-major).  No
+// elementwise work; the kernel is bound by the stream of dS^T tiles from HBM.  Warps 0-3 epilogue, 4 producer, 5 MMA.
+template <int D> struct DqSpillCfg {
+    static constexpr int kBoxes = D / 64;
+    static constexpr int kBoxBytes = kTile * 128;
+    static constexpr int kTileBytes = kBoxes * kBoxBytes;
+    static constexpr int kDsBytes = 2 * kBoxBytes;
+    static constexpr int kStageBytes = kDsBytes + kTileBytes;
+    static constexpr int kStages = 3;
+    static constexpr int kBars = 2 * kStages + 1;
+    static constexpr int kThreadsDq = 192;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kBars * 8 + 16;
+};
+
+template <int D>
+__global__ void __launch_bounds__(DqSpillCfg<D>::kThreadsDq, 1) bwd_dq_spill_kernel(const __grid_constant__ BwdKernelParams p) {
+    using C = DqSpillCfg<D>;
+    extern __shared__ __align__(1024) uint8_t smem[];
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem + C::kStages * C::kStageBytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bars + C::kBars);
+    volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+    const uint32_t bar0 = smem_u32(bars);
+    auto rg_full = [&](int s) { return bar0 + 8u * s; };
+    auto rg_empty = [&](int s) { return bar0 + 8u * (C::kStages + s); };
+    const uint32_t acc_final = bar0 + 8u * (2 * C::kStages);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    // block -> (query tile, head, batch); late query tiles see the most keys and go first
+    const int lin = blockIdx.x;
+    const int tile_rank = lin / (p.q_heads * p.batch);
+    const int bh = lin % (p.q_heads * p.batch);
+    const int b = bh / p.q_heads, h = bh % p.q_heads;
+    const int t_own = p.causal ? p.n_tiles - 1 - tile_rank : tile_rank;
+    const int n_iter = p.causal ? t_own + 1 : p.n_tiles;
+    constexpr uint32_t kTmemCols = D;  // 64 or 128: a power of two >= 32
+
+    if (threadIdx.x == 0) {
+        *abort_flag = (smem_u32(smem) & 1023u) ? 1 : 0;
+        if (*abort_flag) timeout(p, 91);
+        for (int s = 0; s < C::kStages; ++s) {
+            mbar_init(rg_full(s), 1);
+            mbar_init(rg_empty(s), 1);
+        }
+        mbar_init(acc_final, 1);
+        mbar_fence_init();
+        fence_proxy_async();
+    }
+    if (warp == 5) {
+        tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 4 && lane == 0 && !*abort_flag) {
+        // ================= producer =================
+        const int kvh = h / p.group;
+        for (int it = 0; it < n_iter; ++it) {
+            const int s = it % C::kStages;
+            if (!mbar_wait(rg_empty(s), ((it / C::kStages) & 1) ^ 1, abort_flag)) {
+                timeout(p, 100 + s);
+                break;
+            }
+            uint8_t *stage = smem + s * C::kStageBytes;
+            mbar_expect_tx(rg_full(s), C::kStageBytes);
+            bulk_copy_g2s(smem_u32(stage), p.ds_spill + ds_tile_index(p, b, h, it, t_own) * C::kDsBytes, C::kDsBytes, rg_full(s));
+            for (int kb = 0; kb < C::kBoxes; ++kb)
+                tma_load_4d(smem_u32(stage + C::kDsBytes + kb * C::kBoxBytes), &p.map_k, kb * 64, it * kTile, kvh, b, rg_full(s));
+        }
+    } else if (warp == 5 && lane == 0 && !*abort_flag) {
+        // ================= MMA issuer =================
+        bool ok = true;
+        for (int it = 0; ok && it < n_iter; ++it) {
+            const int s = it % C::kStages;
+            if (!mbar_wait(rg_full(s), (it / C::kStages) & 1, abort_flag)) {
+                timeout(p, 210);
+                ok = false;
+                break;
+            }
+            tc_fence_after();
+            const uint8_t *stage = smem + s * C::kStageBytes;
+            const uint64_t a_desc = make_smem_desc(smem_u32(stage), C::kBoxBytes, 1024);                // dS^T, M-major
+            const uint64_t b_desc = make_smem_desc(smem_u32(stage + C::kDsBytes), C::kBoxBytes, 1024);  // K_j, N-major
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk)
+                mma_ss_off(tmem_base, a_desc, b_desc, kk * (16 * 128 >> 4), p.idesc_dq, (it > 0 || kk > 0));
+            tc_commit(rg_empty(s));
+        }
+        if (ok) tc_commit(acc_final);
+    } else if (warp < 4) {
+        // ================= epilogue =================
+        const int row_local = warp * 32 + lane;  // TMEM lane = query row
+        if (mbar_wait(acc_final, 0, abort_flag)) {
+            tc_fence_after();
+            const long long out_row = ((long long)b * p.q_heads + h) * p.seq_len + (long long)t_own * kTile + row_local;
+            float *op = reinterpret_cast<float *>(p.out0) + out_row * D;
+            const bool store = t_own * kTile + row_local < p.seq_len;
+            const uint32_t t_acc = tmem_base + (static_cast<uint32_t>(warp * 32) << 16);
+#pragma unroll
+            for (int c = 0; c < D / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(t_acc + c * 32, r);
+                tc_wait_ld();
+                if (!store) continue;
+                float4 *dst = reinterpret_cast<float4 *>(op + c * 32);
+#pragma unroll
+                for (int q4 = 0; q4 < 8; ++q4)
+                    dst[q4] = make_float4(__uint_as_float(r[q4 * 4]) * p.scale, __uint_as_float(r[q4 * 4 + 1]) * p.scale,
+                                          __uint_as_float(r[q4 * 4 + 2]) * p.scale, __uint_as_float(r[q4 * 4 + 3]) * p.scale);
+            }
+        } else {
+            timeout(p, 320);
+        }
+    }
+
+    if (*abort_flag) {
+        for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 5) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
 // delta = dO . O and -LSE*log2(e).  A thread takes 8 elements (16 bytes) of a row of each tensor, head_dim / 8
 // neighbouring lanes share a row, so a warp covers 256 / head_dim rows with full-width loads.
 __global__ void __launch_bounds__(256) bwd_prep_kernel(const __nv_bfloat16 *__restrict__ d_out,
@@ -784,15 +981,29 @@ bool backward_sm100_supported(const BwdParams &p) {
     return true;
 }
 
-uint64_t backward_sm100_workspace_bytes(const BwdParams &p) {
+namespace {
+// bytes of the dS^T spill: one 32 KiB tile per visible (key tile, query tile) pair of every (batch, q head)
+uint64_t spill_bytes(const BwdParams &p) {
+    const uint64_t n = ((uint64_t)p.seq_len + kTile - 1) / kTile;
+    const uint64_t per_head = p.causal ? n * (n + 1) / 2 : n * n;
+    return (uint64_t)p.batch * p.q_heads * per_head * (2 * kTile * 128);
+}
+uint64_t small_scratch_bytes(const BwdParams &p) {
     const uint64_t seq_pad = ((uint64_t)p.seq_len + kTile - 1) / kTile * kTile;
-    return 2 * (uint64_t)p.batch * p.q_heads * seq_pad * sizeof(float);
+    return (2 * (uint64_t)p.batch * p.q_heads * seq_pad * sizeof(float) + 1023) & ~uint64_t(1023);
+}
+bool use_spill(const flat_ctx *ctx, const BwdParams &p) { return spill_bytes(p) <= ctx->backward_scratch_budget; }
+}  // namespace
+
+uint64_t backward_sm100_workspace_bytes(const flat_ctx *ctx, const BwdParams &p) {
+    return small_scratch_bytes(p) + (use_spill(ctx, p) ? spill_bytes(p) : 0);
 }
 
 int launch_backward_sm100(flat_ctx *ctx, const BwdParams &p) {
-    int st = ensure_workspace(ctx, kWorkspaceMeta + backward_sm100_workspace_bytes(p));
+    int st = ensure_workspace(ctx, kWorkspaceMeta + backward_sm100_workspace_bytes(ctx, p));
     if (st) return st;
     const int D = p.head_dim, N = p.seq_len;
+    const bool spill = use_spill(ctx, p);
     const int64_t rows = (int64_t)p.batch * p.q_heads * N;
     const int seq_pad = (N + kTile - 1) / kTile * kTile;
     const int64_t rows_pad = (int64_t)p.batch * p.q_heads * seq_pad;
@@ -822,28 +1033,36 @@ int launch_backward_sm100(flat_ctx *ctx, const BwdParams &p) {
     kp.scale_log2 = p.scale * kLog2e;
     kp.idesc_k = make_idesc(kFmtBF16, kFmtBF16, 0, 0, 128, 128);
     kp.idesc_mn = make_idesc(kFmtBF16, kFmtBF16, 0, 1, 128, (uint32_t)D);
+    kp.idesc_dq = make_idesc(kFmtBF16, kFmtBF16, 1, 1, 128, (uint32_t)D);
+    kp.ds_spill = spill ? reinterpret_cast<uint8_t *>(scratch_ptr(ctx)) + small_scratch_bytes(p) : nullptr;
     kp.status = ctx->dev_status;
     kp.trace = nullptr;
 #ifdef FLAT_TRACE
     if (const char *tp = getenv("FLAT_TRACE_PTR")) kp.trace = reinterpret_cast<long long *>(strtoull(tp, nullptr, 0));
 #endif
 
-    auto run = [&](auto kernel, int smem_bytes, long long grid) -> int {
+    auto run = [&](auto kernel, int smem_bytes, long long grid, int threads = kThreads) -> int {
         FLAT_CUDA_OK(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         KernelTimer timer(ctx);
-        kernel<<<(unsigned)grid, kThreads, smem_bytes, ctx->stream>>>(kp);
+        kernel<<<(unsigned)grid, threads, smem_bytes, ctx->stream>>>(kp);
         return FLAT_OK;
     };
     const long long grid_kv = (long long)kp.n_tiles * p.kv_heads * p.batch;
     const long long grid_q = (long long)kp.n_tiles * p.q_heads * p.batch;
     kp.out0 = p.dv;
     kp.out1 = p.dk;
-    if (D == 128) st = run(bwd_sm100_kernel<128>, BCfg<128>::kSmemBytes, grid_kv);
-    else st = run(bwd_sm100_kernel<64>, BCfg<64>::kSmemBytes, grid_kv);
+    if (spill) {
+        if (D == 128) st = run(bwd_sm100_kernel<128, true>, BCfg<128>::kSmemBytes, grid_kv);
+        else st = run(bwd_sm100_kernel<64, true>, BCfg<64>::kSmemBytes, grid_kv);
+    } else if (D == 128) st = run(bwd_sm100_kernel<128, false>, BCfg<128>::kSmemBytes, grid_kv);
+    else st = run(bwd_sm100_kernel<64, false>, BCfg<64>::kSmemBytes, grid_kv);
     if (st) return st;
     kp.out0 = p.dq;
     kp.out1 = nullptr;
-    if (D == 128) st = run(bwd_dq_sm100_kernel<128>, DqCfg<128>::kSmemBytes, grid_q);
+    if (spill) {
+        if (D == 128) st = run(bwd_dq_spill_kernel<128>, DqSpillCfg<128>::kSmemBytes, grid_q, DqSpillCfg<128>::kThreadsDq);
+        else st = run(bwd_dq_spill_kernel<64>, DqSpillCfg<64>::kSmemBytes, grid_q, DqSpillCfg<64>::kThreadsDq);
+    } else if (D == 128) st = run(bwd_dq_sm100_kernel<128>, DqCfg<128>::kSmemBytes, grid_q);
     else st = run(bwd_dq_sm100_kernel<64>, DqCfg<64>::kSmemBytes, grid_q);
     if (st) return st;
     ctx->launches += 2;

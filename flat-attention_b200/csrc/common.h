@@ -57,6 +57,9 @@ struct flat_ctx {
     };
     RopeTable rope_tables[2];
     uint64_t rope_clock = 0;
+    // The tensor-core backward may keep every bf16 dS^T tile in scratch (O(N^2) bytes) so that dQ needs no second score
+    // recompute; it does so while that spill fits this budget (flat_ctx_set_backward_scratch_budget).
+    uint64_t backward_scratch_budget = 8ull << 30;
     cudaEvent_t stream_switch = nullptr;  // orders the old and the new stream in flat_ctx_set_stream
     // sequence offsets of the last balanced decode plan and where they were uploaded (skips identical re-uploads)
     std::vector<int32_t> plan_offsets;
@@ -244,7 +247,7 @@ struct BwdParams {
 };
 int launch_backward_simt(flat_ctx *ctx, int dtype, const BwdParams &p);
 bool backward_sm100_supported(const BwdParams &p);
-uint64_t backward_sm100_workspace_bytes(const BwdParams &p);
+uint64_t backward_sm100_workspace_bytes(const flat_ctx *ctx, const BwdParams &p);
 int launch_backward_sm100(flat_ctx *ctx, const BwdParams &p);
 
 }  // namespace flat

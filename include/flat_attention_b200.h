@@ -196,6 +196,13 @@ const char *flat_last_error_detail(const flat_ctx *ctx);
  * backward accumulators) so later encode calls do not allocate. */
 int32_t flat_ctx_reserve_workspace(flat_ctx *ctx, uint64_t bytes);
 uint64_t flat_ctx_workspace_bytes(const flat_ctx *ctx);
+/* The bf16 tensor-core backward has two routes to dQ.  With scratch to spare it keeps every bf16
+ * dS tile of the dK/dV kernel (32 KiB per visible 128 x 128 (key, query) tile pair:
+ * batch * q_heads * N^2 bytes for a causal call, twice that otherwise) and forms dQ from the tiles
+ * with one more GEMM, five GEMM units in all; otherwise it recomputes the scores in a second
+ * kernel, seven GEMM units and no O(N^2) scratch.  The spill route is taken while its scratch fits
+ * `bytes` (default 8 GiB; 0 = never).  Results are bitwise repeatable on either route. */
+int32_t flat_ctx_set_backward_scratch_budget(flat_ctx *ctx, uint64_t bytes);
 /* Pre-size the context's two cached (cos, sin) tables for calls of up to `rows` positions at
  * `head_dim`, so that RoPE entry points whose positions change from call to call (chunked
  * prefill) recompute into memory that exists instead of freeing and allocating.  Together with

@@ -17,11 +17,20 @@ def randn(n, seed):
     return bf16_round(torch.randn(n, generator=torch.Generator().manual_seed(seed)).numpy())
 
 
+@pytest.fixture(params=["spill", "recompute"])
+def dq_route(request):
+    """Both routes of the tensor-core backward to dQ: from the dS tiles kept in scratch (the default while they fit the
+    context's budget) and by recomputing the scores in a second kernel (budget 0)."""
+    ctx().set_backward_scratch_budget(0 if request.param == "recompute" else 8 << 30)
+    yield request.param
+    ctx().set_backward_scratch_budget(8 << 30)
+
+
 @pytest.mark.parametrize("B,Hq,Hkv,N,D", [(1, 4, 2, 256, 128), (2, 2, 2, 128, 64), (1, 8, 1, 384, 128), (1, 2, 1, 512, 64),
                                           # sequence lengths that are not whole 128-row tiles
                                           (2, 4, 2, 200, 128), (1, 4, 1, 333, 64), (1, 2, 2, 40, 128)])
 @pytest.mark.parametrize("causal", [True, False])
-def test_backward_bf16_small(B, Hq, Hkv, N, D, causal):
+def test_backward_bf16_small(B, Hq, Hkv, N, D, causal, dq_route):
     q, k, v, do = randn(B * Hq * N * D, 1), randn(B * Hkv * N * D, 2), randn(B * Hkv * N * D, 3), randn(B * Hq * N * D, 4)
     fo, fl = ob.forward_reference_grouped(q, k, v, B, Hq, Hkv, N, D, causal)
     fo = bf16_round(fo)
@@ -35,7 +44,7 @@ def test_backward_bf16_small(B, Hq, Hkv, N, D, causal):
     assert ctx().device_status() == 0
 
 
-def test_random_shapes_tensor_core_backward_against_f32_path():
+def test_random_shapes_tensor_core_backward_against_f32_path(dq_route):
     """Differential sweep: the tcgen05 backward (bf16) against the generic f32 backward (pinned to the oracle at 1e-4)
     on the same bf16-rounded inputs and the same forward results, over seeded random shapes (ragged lengths, both
     head dims, GQA groups, causal and not)."""
@@ -61,7 +70,7 @@ def test_random_shapes_tensor_core_backward_against_f32_path():
         assert ctx().device_status() == 0, what
 
 
-def test_config5_grouped_backward_sampled_rows():
+def test_config5_grouped_backward_sampled_rows(dq_route):
     """B=2, Hq=32, Hkv=8, N=8192, D=128, causal: forward on the device, backward on the device, oracle
     on sampled dQ rows and dK/dV rows (first/last rows, tile boundaries, random)."""
     B, Hq, Hkv, N, D = 2, 32, 8, 8192, 128
