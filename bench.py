@@ -38,11 +38,13 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 NCU_TRAFFIC = {
     "forward": 304_634_112 + 102_786_304,  # fwd_sm100_kernel<128,false>, C2
     "decode": 1_110_867_000 + 4_535_296,  # decode_mma_kernel<128>, C3
-    "backward": 1_229_615_000 + 110_039_296 + 643_880_000 + 235_303_936,  # dK/dV kernel + dQ kernel, C5
+    # dK/dV kernel (reads, dS writes) + dQ kernel (dS reads, writes), captured on one eighth of C5 and scaled by 8
+    "backward": 8 * (60_724_736 + 507_990_528 + 554_259_712 + 22_141_696),
 }
 sys.path.insert(0, ROOT)
-BACKWARD_KERNELS = "bwd_sm100_kernel<128> + bwd_dq_sm100_kernel<128>"
-BACKWARD_NOTE = "7 GEMM units are executed for 5 algorithmic ones (scores recomputed in both kernels)"
+BACKWARD_KERNELS = "bwd_sm100_kernel<128,spill> + bwd_dq_spill_kernel<128>"
+BACKWARD_NOTE = ("5 GEMM units, the algorithmic count: the dK/dV kernel writes its bf16 dS tiles to scratch (causal C5: "
+                 "4.3 GB) and the dQ kernel streams them back against K, so that kernel is HBM-bound, not tensor-bound")
 
 C2 = dict(B=4, Hq=32, Hkv=8, N=4096, D=128, theta=500000.0)
 C3 = dict(S=64, Hq=32, Hkv=8, D=128, page=16, lo=512, hi=8192, theta=500000.0)
@@ -447,12 +449,12 @@ def bench_backward(torch, np, fa, ctx, peaks, steps, warmup, ob=None, dims=None,
     ctx.set_kernel_timing(False)
     flops = 10 * B * Hq * N * N * D // 2
     kernel_ms = kms / steps  # the tensor-core kernels of one call
-    traffic = NCU_TRAFFIC["backward"] if not dims else None
+    traffic = NCU_TRAFFIC.get("backward") if not dims else None
     return {"metric": "grouped_backward_tflops", "value": flops / (ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms,
             "flop_per_step": flops, "workload": "C5 B=%d Hq=%d Hkv=%d N=8192 D=128 causal bf16, f32 gradients" % (B, Hq, Hkv),
             "roofline": tensor_roofline(peaks, flops, kernel_ms, loop_ms, clocks.get("reasons"), BACKWARD_KERNELS,
-                                        traffic, "dram bytes read+written, all kernels of one call, one ncu capture of this "
-                                                 "workload (profiles/)" if traffic else None, BACKWARD_NOTE),
+                                        traffic, "dram bytes read+written, both kernels of one call: 8 x one ncu capture of "
+                                                 "one eighth of this workload (profiles/)" if traffic else None, BACKWARD_NOTE),
             "clocks": clocks, "parity": parity}
 
 
@@ -893,6 +895,9 @@ def main():
     ap.add_argument("--no-shadow", action="store_true", help="chunked prefill without the binary16 K shadow of the paged cache")
     ap.add_argument("--chunked-only", action="store_true", help="run only the chunked prefill against the paged cache "
                                                                "(N=1; --steps = timed passes): a short command for profiler captures")
+    ap.add_argument("--backward-only", default=None, metavar="B,HQ,HKV", help="run only the grouped backward of config 5 with this "
+                    "batch and head counts (N=8192, D=128 as in config 5; '2,32,8' is config 5 itself): a short command "
+                    "for profiler captures, which want a scratch of a few hundred MB rather than config 5's 4.3 GB")
     ap.add_argument("--manifest", default=None, help="write a schema-1 canonical-JSON benchmark manifest of the headline "
                                                      "workload to this path (rank 0)")
     ap.add_argument("--commit-sha", default=None, help="40-hex source revision recorded in the manifest "
@@ -926,6 +931,16 @@ def main():
     if args.variants_only:
         if rank == 0:
             print(json.dumps({"prefill_variants": bench_prefill_variants(torch, np, fa, ctx, peaks, max(1, args.steps), args.warmup)}),
+                  flush=True)
+        return
+    if args.backward_only:
+        if rank == 0:
+            dims = tuple(int(x) for x in args.backward_only.split(","))
+            ob_b = None
+            if not args.no_cpu:
+                from oracle import binding as ob_b
+            print(json.dumps({"backward": bench_backward(torch, np, fa, ctx, peaks, max(1, args.steps), args.warmup, ob_b,
+                                                         None if dims == (C5["B"], C5["Hq"], C5["Hkv"]) else dims, local_rank)}),
                   flush=True)
         return
     if args.chunked_only:

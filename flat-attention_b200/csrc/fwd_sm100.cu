@@ -53,6 +53,9 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 
 // Debug timeline (compiled in with -DFLAT_TRACE): clock64 stamps of CTA FLAT_TRACE_BLOCK (default 0), written to the buffer whose
 // address is given in the environment variable FLAT_TRACE_PTR.  Layout [role 0..2][iteration 0..63][slot 0..7].
+#ifndef FLAT_TRACE_ITEM
+#define FLAT_TRACE_ITEM 0  // the item of the CTA whose KV loop is stamped
+#endif
 #ifdef FLAT_TRACE
 #ifndef FLAT_TRACE_BLOCK
 #define FLAT_TRACE_BLOCK 0
@@ -83,6 +86,27 @@ constexpr float kRescaleThreshold = 8.0f;  // log2 domain
 #define TRACEB(k, role, slot) do { } while (0)
 #endif
 
+// Division of a non-negative int by a divisor fixed for the launch, as a multiply-high and a shift (the work-item
+// arithmetic below runs on the critical path of every item boundary, where an emulated 32-bit division costs about a
+// hundred cycles).  mul = ceil(2^(31 + ceil(log2 d)) / d), shr = ceil(log2 d) - 1; exact for 0 <= n < 2^31.
+struct FastDiv {
+    uint32_t mul, shr, one;  // one: the divisor is 1 (the quotient is n itself)
+};
+inline FastDiv make_fastdiv(int d) {
+    FastDiv f{0, 0, d == 1 ? 1u : 0u};
+    if (d > 1) {
+        int l = 0;
+        while ((1ll << l) < d) ++l;  // ceil(log2 d)
+        const int p = 31 + l;
+        f.mul = (uint32_t)(((1ull << p) + (unsigned long long)d - 1) / (unsigned long long)d);
+        f.shr = (uint32_t)(p - 32);
+    }
+    return f;
+}
+__device__ __forceinline__ int fast_div(int n, const FastDiv &f) {
+    return f.one ? n : (int)(__umulhi((uint32_t)n, f.mul) >> f.shr);
+}
+
 struct KernelParams {
     CUtensorMap map_q, map_k, map_v;
     CUtensorMap map_o;  // O as (d, row, head, batch) with boxes of 64 columns x 128 rows: the epilogue's bulk stores
@@ -92,6 +116,7 @@ struct KernelParams {
     int64_t o_bs, o_hs, o_rs, lse_hs;
     int o_align32;  // every O row starts on a 32-byte boundary: 256-bit stores may be used
     int batch, q_heads, kv_heads, q_len, kv_len, group;
+    FastDiv div_bh, div_heads, div_group;  // by batch * q_heads, by q_heads, by group
     int causal;
     long long causal_off;
     float scale_log2;
@@ -163,11 +188,12 @@ __device__ __forceinline__ WorkItem make_item_whole(const KernelParams &p, int l
     // item index -> (query block, batch, head); late (long) query blocks first
     WorkItem it;
     const int total_bh = p.batch * p.q_heads;
-    const int qb = p.q_blocks - 1 - lin / total_bh;
-    const int bh = lin % total_bh;
-    it.b = bh / p.q_heads;
-    it.h = bh % p.q_heads;
-    it.kvh = it.h / p.group;
+    const int q_lin = fast_div(lin, p.div_bh);
+    const int qb = p.q_blocks - 1 - q_lin;
+    const int bh = lin - q_lin * total_bh;
+    it.b = fast_div(bh, p.div_heads);
+    it.h = bh - it.b * p.q_heads;
+    it.kvh = fast_div(it.h, p.div_group);
     it.r0 = qb * 2 * kTileRows;
     it.q_len = p.q_len;
     it.kv_len = p.kv_len;
@@ -428,7 +454,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                 if (lin < 0) break;
                 const WorkItem it = make_item<SPLIT>(p, lin, split_rec);
                 const int n_max = max(it.n_tiles[0], it.n_tiles[1]);
-                const bool trace_item = k == 0;
+                const bool trace_item = k == FLAT_TRACE_ITEM;
                 (void)trace_item;
                 TRACEB(k, 2, 0);
                 // prologue: S_w(0) as soon as the slot's Q tile is ready (the other slot may still be finishing the
@@ -542,13 +568,14 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
         uint32_t done = 0;     // finished items of this slot (its tile was inside q_len)
         uint32_t s_waits = 0;  // score tiles of this slot consumed so far
         uint32_t o_boxes = 0;  // boxes of O this slot has staged so far
+        bool store_pending = false;  // (the slot's first thread) a bulk store of the staging space has not been waited for
 
         // Iteration k runs the KV loop of item k, then rotates the Q tile of item k + 1 (its TMA was issued as soon as
         // the slot's last S MMA had completed), then stores item k: the next item's first S MMA runs during the
         // epilogue.  k = -1 only rotates the first tile.
         for (int k = -1; ok; ++k) {
             // (item indices are recomputed where they are needed rather than kept in registers across the KV loop)
-            const bool trace_item = k == 0;
+            const bool trace_item = k == FLAT_TRACE_ITEM;
             (void)trace_item;
             float m = -INFINITY, l = 0.f;
             bool run = false;
@@ -825,7 +852,14 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                                 pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                             }
                         }
-                        // the previous box has left the staging space (the first wait passes at once)
+                        // The previous box has left the staging space (the first wait passes at once).  The thread that
+                        // sent it does not wait for the bulk store's read right after issuing it, but here, after the
+                        // next box has been fetched and converted (or an item later): by then the read is long done.
+                        if (store_pending) {
+                            bulk_wait_group_read0();
+                            mbar_arrive(o_stage_free(w));
+                            store_pending = false;
+                        }
                         if (!mbar_wait(o_stage_free(w), (o_boxes & 1) ^ 1, abort_flag)) {
                             record_timeout(p, 320 + w);
                             ok = false;
@@ -842,8 +876,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                             if (mbar_wait(o_stage_full(w), o_boxes & 1, abort_flag)) {
                                 tma_store_4d(&p.map_o, hf * 64, it.r0 + w * kTileRows, h, b, smem_u32(stg));
                                 bulk_commit_group();
-                                bulk_wait_group_read0();
-                                mbar_arrive(o_stage_free(w));
+                                store_pending = true;
                             } else {
                                 record_timeout(p, 325 + w);
                             }
@@ -904,6 +937,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             if ((warp & 3) == 0 && lane == 0) TRACEB(k, w, 4);
             if (next_lin < 0) break;
         }
+        if (store_pending) bulk_wait_group_read0();  // the staging space must outlive the last store's read
     }
 
     if (*abort_flag) {
@@ -1241,6 +1275,9 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     kp.o_align32 = (reinterpret_cast<uintptr_t>(p.o) % 32 == 0 && p.o_bs % 16 == 0 && p.o_hs % 16 == 0 && p.o_rs % 16 == 0) ? 1 : 0;
     kp.batch = p.batch; kp.q_heads = p.q_heads; kp.kv_heads = p.kv_heads; kp.q_len = p.q_len; kp.kv_len = p.kv_len;
     kp.group = p.group;
+    kp.div_bh = make_fastdiv(p.batch * p.q_heads);
+    kp.div_heads = make_fastdiv(p.q_heads);
+    kp.div_group = make_fastdiv(p.group);
     kp.causal = p.causal;
     kp.causal_off = p.causal_off;
     kp.scale_log2 = p.scale * kLog2e;
