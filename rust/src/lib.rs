@@ -175,6 +175,73 @@ impl<'a> CudaGroupedForwardPipeline<'a> {
     }
 }
 
+/// `GroupedBackwardRecomputePass` (src/wgpu_backward_grouped.rs:104-112): one packed input buffer
+/// `[Q | K | V | dO | O | LSE]` and one packed f32 gradient buffer `[dQ | dK | dV]`, offsets from `layout`.
+#[derive(Clone, Copy, Debug)]
+pub struct CudaGroupedBackwardRecomputePass {
+    pub packed_inputs: DeviceBuffer,
+    pub packed_grads: DeviceBuffer,
+    pub shape: GroupedAttentionShape,
+    pub config: FlatAttentionConfig,
+}
+
+/// `WgpuGroupedBackwardRecomputePipeline` (src/wgpu_backward_grouped.rs:181-326): `layout` / `encode` /
+/// `prepare` / `encode_prepared`; gradients are bitwise repeatable.
+pub struct CudaGroupedBackwardRecomputePipeline<'a> {
+    ctx: &'a CudaContext,
+    dtype: DType,
+}
+
+/// `PreparedGroupedBackwardRecompute` (src/wgpu_backward_grouped.rs:231-326): a validated pass with its scratch
+/// sized; `encode_prepared` only enqueues.
+pub struct CudaPreparedGroupedBackwardRecompute {
+    raw: *mut FlatPreparedBackward,
+}
+impl Drop for CudaPreparedGroupedBackwardRecompute {
+    fn drop(&mut self) {
+        unsafe { cuda_ffi::flat_prepared_backward_destroy(self.raw) }
+    }
+}
+
+impl<'a> CudaGroupedBackwardRecomputePipeline<'a> {
+    pub fn new(ctx: &'a CudaContext, dtype: DType) -> Self {
+        Self { ctx, dtype }
+    }
+    pub fn layout(dtype: DType, shape: GroupedAttentionShape) -> Result<FlatBackwardLayout, CudaError> {
+        let mut out = FlatBackwardLayout::default();
+        let code = unsafe { cuda_ffi::flat_backward_layout_for(dtype as i32, &raw_grouped(shape), &mut out) };
+        if code != 0 {
+            return Err(CudaError { code, detail: String::new() });
+        }
+        Ok(out)
+    }
+    /// Records the two kernels on the context's stream; never synchronises.
+    pub fn encode(&self, pass: CudaGroupedBackwardRecomputePass) -> Result<FlatBackwardLayout, CudaError> {
+        let (shape, cfg) = (raw_grouped(pass.shape), raw_config(pass.config));
+        self.ctx.check(unsafe {
+            cuda_ffi::flat_backward_grouped(self.ctx.raw, self.dtype as i32, &shape, &cfg, pass.packed_inputs.raw(),
+                                            pass.packed_grads.raw())
+        })?;
+        Self::layout(self.dtype, pass.shape)
+    }
+    pub fn prepare(&self, pass: CudaGroupedBackwardRecomputePass) -> Result<CudaPreparedGroupedBackwardRecompute, CudaError> {
+        let (shape, cfg) = (raw_grouped(pass.shape), raw_config(pass.config));
+        let mut raw = core::ptr::null_mut();
+        self.ctx.check(unsafe {
+            cuda_ffi::flat_backward_prepare(self.ctx.raw, self.dtype as i32, &shape, &cfg, pass.packed_inputs.raw(),
+                                            pass.packed_grads.raw(), &mut raw)
+        })?;
+        Ok(CudaPreparedGroupedBackwardRecompute { raw })
+    }
+    pub fn encode_prepared(&self, prepared: &CudaPreparedGroupedBackwardRecompute) -> Result<(), CudaError> {
+        self.ctx.check(unsafe { cuda_ffi::flat_backward_encode_prepared(self.ctx.raw, prepared.raw) })
+    }
+    /// Bound of the dS scratch between the two kernels; 0 selects the recompute route.
+    pub fn set_scratch_budget(&self, bytes: u64) -> Result<(), CudaError> {
+        self.ctx.check(unsafe { cuda_ffi::flat_ctx_set_backward_scratch_budget(self.ctx.raw, bytes) })
+    }
+}
+
 /// `WgpuPagedKvCache` (src/wgpu_paged_kv_cache.rs:76-279): owns K and V `[pages * page_size, kv_heads * head_dim]`.
 pub struct CudaPagedKvCache<'a> {
     ctx: &'a CudaContext,
