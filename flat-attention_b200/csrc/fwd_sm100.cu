@@ -109,7 +109,7 @@ __device__ __forceinline__ int fast_div(int n, const FastDiv &f) {
 
 struct KernelParams {
     CUtensorMap map_q, map_k, map_v;
-    CUtensorMap map_o;  // O as (d, row, head, batch) with boxes of 64 columns x 128 rows: the epilogue's bulk stores
+    CUtensorMap map_o;  // O as (d, row, head, batch) with boxes of 64 columns x 32 rows: the epilogue's bulk stores, one per warp
     int o_tma;          // the epilogue stores O tiles through shared memory with bulk copies (not for padded batches)
     void *o;
     float *lse;
@@ -151,7 +151,7 @@ template <int D, bool CONVK> struct Cfg {
     static constexpr int kTileBytes = kBoxes * kBoxBytes;  // one Q / K / V tile
     static constexpr int kStages = D == 128 ? 4 : 8;  // K/V ring entries
     static constexpr int kOutStageBytes = kTileRows * 128;  // one box of the O tile: 128 rows x 64 columns of 16 bits
-    static constexpr int kBars = 2 + 3 * kStages + 14;
+    static constexpr int kBars = 2 + 3 * kStages + 10;
     static constexpr int kSmemBytes = (2 + kStages) * kTileBytes + 2 * kOutStageBytes + kBars * 8 + 16 + 32 + 1024;
     static_assert(kSmemBytes <= 232448, "shared memory of one CTA");
 };
@@ -288,8 +288,6 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
     auto q_ready = [&](int w) { return bar0 + 8u * (8 + 2 * C::kStages + w); };
     auto q_empty = [&](int w) { return bar0 + 8u * (10 + 2 * C::kStages + w); };
     auto k_ready = [&](int s) { return bar0 + 8u * (12 + 2 * C::kStages + s); };  // K tile converted (CONVK)
-    auto o_stage_full = [&](int w) { return bar0 + 8u * (12 + 3 * C::kStages + w); };  // a box of O is staged
-    auto o_stage_free = [&](int w) { return bar0 + 8u * (14 + 3 * C::kStages + w); };  // ... and has been read out
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -303,8 +301,6 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
             mbar_init(o_final(w), 1);
             mbar_init(q_ready(w), 4);
             mbar_init(q_empty(w), 1);
-            mbar_init(o_stage_full(w), 4);
-            mbar_init(o_stage_free(w), 1);
         }
         for (int s = 0; s < C::kStages; ++s) {
             mbar_init(kv_full(s), 1);
@@ -567,8 +563,7 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
         bool ok = true;
         uint32_t done = 0;     // finished items of this slot (its tile was inside q_len)
         uint32_t s_waits = 0;  // score tiles of this slot consumed so far
-        uint32_t o_boxes = 0;  // boxes of O this slot has staged so far
-        bool store_pending = false;  // (the slot's first thread) a bulk store of the staging space has not been waited for
+        bool store_pending = false;  // (lane 0) a bulk store of this warp's staging rows has not been waited for
 
         // Iteration k runs the KV loop of item k, then rotates the Q tile of item k + 1 (its TMA was issued as soon as
         // the slot's last S MMA had completed), then stores item k: the next item's first S MMA runs during the
@@ -830,12 +825,12 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     tc_fence_before();
                 } else if (p.o_tma) {
                     // O leaves through shared memory: every thread writes its row's 128 bytes of a 64-column box in the
-                    // swizzled box layout, the slot's first thread sends the box with one bulk store (whole lines,
-                    // rows past q_len clipped by the tensor map), instead of 32-byte stores 256 bytes apart per thread
+                    // swizzled box layout and each warp sends its 32 rows with one bulk store (whole lines), instead of
+                    // 32-byte stores 256 bytes apart per thread
                     const float inv = 1.0f / l;
                     uint8_t *stg = o_stage + w * C::kOutStageBytes;
 #pragma unroll
-                    for (int hf = 0; hf < D / 64 && ok; ++hf, ++o_boxes) {
+                    for (int hf = 0; hf < D / 64; ++hf) {
                         uint32_t r[64];
                         tmem_ld32(t_o + hf * 64, r);
                         tmem_ld32(t_o + hf * 64 + 32, r + 32);
@@ -852,34 +847,26 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                                 pk[i >> 1] = *reinterpret_cast<uint32_t *>(&h2);
                             }
                         }
-                        // The previous box has left the staging space (the first wait passes at once).  The thread that
-                        // sent it does not wait for the bulk store's read right after issuing it, but here, after the
-                        // next box has been fetched and converted (or an item later): by then the read is long done.
-                        if (store_pending) {
+                        // A warp stages and sends its own 32 rows, so the four warps of the slot never wait for one
+                        // another here.  The staging rows are reused by the next box: the lane that sent the previous one
+                        // waits for that bulk store's read only now, after the next box has been fetched and converted
+                        // (or an item later), when it is long done.
+                        if (lane == 0 && store_pending) {
                             bulk_wait_group_read0();
-                            mbar_arrive(o_stage_free(w));
                             store_pending = false;
                         }
-                        if (!mbar_wait(o_stage_free(w), (o_boxes & 1) ^ 1, abort_flag)) {
-                            record_timeout(p, 320 + w);
-                            ok = false;
-                            break;
-                        }
+                        __syncwarp();
 #pragma unroll
                         for (int ch = 0; ch < 8; ++ch)
                             *reinterpret_cast<uint4 *>(stg + row_in_tile * 128 + ((ch ^ (row_in_tile & 7)) << 4)) =
                                 make_uint4(pk[ch * 4], pk[ch * 4 + 1], pk[ch * 4 + 2], pk[ch * 4 + 3]);
                         fence_proxy_async();  // generic-proxy writes -> visible to the bulk copy's async proxy
                         __syncwarp();
-                        if (lane == 0) mbar_arrive(o_stage_full(w));
-                        if ((warp & 3) == 0 && lane == 0) {
-                            if (mbar_wait(o_stage_full(w), o_boxes & 1, abort_flag)) {
-                                tma_store_4d(&p.map_o, hf * 64, it.r0 + w * kTileRows, h, b, smem_u32(stg));
-                                bulk_commit_group();
-                                store_pending = true;
-                            } else {
-                                record_timeout(p, 325 + w);
-                            }
+                        // (rows past q_len are clipped by the tensor map; a box that starts past it is not sent at all)
+                        if (lane == 0 && it.r0 + w * kTileRows + lane_base < it.q_len) {
+                            tma_store_4d(&p.map_o, hf * 64, it.r0 + w * kTileRows + lane_base, h, b, smem_u32(stg + lane_base * 128));
+                            bulk_commit_group();
+                            store_pending = true;
                         }
                     }
                     if (row < it.q_len) p.lse[((long long)b * p.q_heads + h) * p.lse_hs + row] = (m + log2f(l)) * kLn2;
@@ -1267,7 +1254,7 @@ int launch_forward_sm100(flat_ctx *ctx, const FwdParams &p) {
     // the epilogue's bulk stores clip at the call's q_len, not at a sequence's active length: padded batches keep the
     // per-thread stores
     kp.o_tma = p.varlen ? 0 : 1;
-    if (kp.o_tma && (st = make_map(ctx, &kp.map_o, io16, p.o, D, p.q_len, p.q_heads, p.batch, p.o_rs, p.o_hs, p.o_bs, kTileRows)))
+    if (kp.o_tma && (st = make_map(ctx, &kp.map_o, io16, p.o, D, p.q_len, p.q_heads, p.batch, p.o_rs, p.o_hs, p.o_bs, 32)))
         return st;
     kp.o = p.o;
     kp.lse = p.lse;
