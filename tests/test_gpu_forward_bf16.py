@@ -238,6 +238,20 @@ def test_random_shapes_tensor_core_path_against_f32_path():
         assert ctx().device_status() == 0, what
 
 
+@pytest.mark.parametrize("B,Hq,Hkv,N,D", [(3, 6, 3, 300, 128), (5, 12, 4, 260, 64), (7, 9, 9, 130, 128), (1, 15, 5, 513, 128)])
+def test_head_and_batch_counts_that_are_not_powers_of_two(B, Hq, Hkv, N, D):
+    """The persistent kernel turns a work-item index into (query block, batch, head, kv head) with multiply-high
+    constants made on the host instead of divisions: batch * heads, heads and group sizes that are not powers of two,
+    against the generic f32 kernel on the same bf16-rounded inputs."""
+    q, k, v = randn(B * N * Hq * D, 41), randn(B * N * Hkv * D, 42), randn(B * N * Hkv * D, 43)
+    shp = fa.shape(B, Hq, Hkv, N, N, D)
+    rot = fa.rotary(5e5, 0)
+    o, l = run_forward("projection_rope", fa.BF16, shp, fa.config(True), q, k, v, rot=rot)
+    eo, el = run_forward("projection_rope", fa.F32, shp, fa.config(True), q, k, v, rot=rot)
+    check(o, l, eo, el, f"B={B} Hq={Hq} Hkv={Hkv} N={N} D={D}")
+    assert ctx().device_status() == 0
+
+
 @pytest.mark.parametrize("B,Hq,Hkv,Nq,Nkv,off,D,causal,rope", [
     (1, 4, 2, 2048, 8192, 0, 128, False, False),    # 32 items on 148 SMs: every item cut into 4 KV parts
     (1, 4, 2, 256, 8192, 7936, 128, True, True),    # 4 items, 4 parts of 16 KV tiles; the last part holds the diagonal
