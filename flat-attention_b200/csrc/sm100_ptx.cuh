@@ -75,22 +75,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     }
 }
 
-// The same bounded wait for a warp that is in no hurry and shares its scheduler with busy warps: it sleeps `ns`
-// nanoseconds between looks instead of polling, at the price of that much reaction time.
-__device__ __forceinline__ bool mbar_wait_sleepy(uint32_t bar, uint32_t parity, volatile int *abort_flag, uint32_t ns) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const uint32_t start = (uint32_t)clock();
-    for (;;) {
-        __nanosleep(ns);
-        if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag != 0) return false;
-        if ((uint32_t)clock() - start > kWaitCycles) {
-            *abort_flag = 1;
-            return false;
-        }
-    }
-}
-
 // ---- TMA -------------------------------------------------------------------------------------
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -201,12 +185,6 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *r) {
           "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
         : "r"(taddr)
         : "memory");
-}
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t *r) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-                 : "r"(taddr)
-                 : "memory");
 }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t *r) {
     asm volatile(
