@@ -808,16 +808,61 @@ def bench_splitkv_128k(torch, np, dist, fa, ctx, peaks, rank, world, steps, warm
         finally:
             world = world_saved
         one_gpu["graph_ms_per_step"], one_gpu["graph_error"] = g1_ms, g1_err
-    t = torch.tensor([tot / steps, tot_merge / steps, kms / max(kn, 1), g_ms if g_ms is not None else -1.0], device="cuda",
-                     dtype=torch.float64)
+    # The same step over NVLink peer memory (flat_splitkv_decode_peer): the partial, then ONE kernel that stores it into
+    # every rank's buffer, waits for the others' flags and merges.  Same bits as the NCCL route (checked).
+    peer = {}
+    xchg = None
+    try:
+        xchg = fd.connect_peer_exchange(fa.SplitKvPeerExchange(ctx, rank, world, Hq, D))
+    except Exception as e:  # raised on every rank or on none
+        peer["error"] = repr(e)[:300]
+    p_ms = pg_ms = -1.0
+    if xchg is not None:
+        out_p = ctx.create_decode_output_buffer(fa.BF16, 1, Hq, D)
+
+        def step_peer():
+            ctx.splitkv_decode_peer(xchg, fa.BF16, cfg=args["cfg"], theta=theta, q=Q, k=K, v=V, out=out_p, **abi)
+        for _ in range(warmup):
+            step_peer()
+        tot_p = 0.0
+        for _ in range(steps):
+            flush.zero_()
+            torch.cuda.synchronize()
+            dist.barrier()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            step_peer()
+            b.record()
+            torch.cuda.synchronize()
+            tot_p += a.elapsed_time(b)
+        p_ms = tot_p / steps
+        peer["same_bits_as_nccl_route"] = bool(torch.equal(out_p, out)) and ctx.device_status() == 0
+        pg, peer["graph_error"] = graph_ms(step_peer, steps)
+        pg_ms = pg if pg is not None else -1.0
+        torch.cuda.synchronize()
+        dist.barrier()  # nobody unmaps a buffer a peer may still store into
+        xchg.close()
+    t = torch.tensor([tot / steps, tot_merge / steps, kms / max(kn, 1), g_ms if g_ms is not None else -1.0, p_ms, pg_ms],
+                     device="cuda", dtype=torch.float64)
     dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, ms_merge, kernel_ms = float(t[0]), float(t[1]), float(t[2])
     graph_step_ms = float(t[3]) if g_ms is not None else None
+    if xchg is not None:
+        same = torch.tensor([1 if peer["same_bits_as_nccl_route"] else 0], device="cuda")
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        peer.update(ms_per_step=float(t[4]), graph_ms_per_step=float(t[5]) if float(t[5]) > 0 else None,
+                    same_bits_as_nccl_route=bool(int(same.item())),
+                    what="flat_splitkv_decode_peer: partial decode, then one kernel: 16-byte peer stores of the 33 KB block "
+                         "into every rank's buffer, flag, bounded wait for the others' flags, merge")
+        if one_gpu:
+            peer["speedup_vs_one_gpu"] = one_gpu["ms_per_step"] / peer["ms_per_step"]
+            if one_gpu.get("graph_ms_per_step") and peer["graph_ms_per_step"]:
+                peer["graph_speedup_vs_one_gpu"] = one_gpu["graph_ms_per_step"] / peer["graph_ms_per_step"]
     kv_bytes = n * Hkv * D * 2 * 2
     per_gpu_gbs = kv_bytes / world / (kernel_ms * 1e-3) / 1e9
     return {"metric": "splitkv_decode_128k", "ms_per_step": ms, "gather_merge_ms": ms_merge,
             "partial_kernel_ms": kernel_ms, "one_gpu": one_gpu,
-            "graph_ms_per_step": graph_step_ms, "graph_error": g_err,
+            "graph_ms_per_step": graph_step_ms, "graph_error": g_err, "peer": peer,
             "speedup_vs_one_gpu": (one_gpu["ms_per_step"] / ms) if one_gpu else None,
             "graph_speedup_vs_one_gpu": (one_gpu["graph_ms_per_step"] / graph_step_ms)
             if one_gpu and one_gpu.get("graph_ms_per_step") and graph_step_ms else None,

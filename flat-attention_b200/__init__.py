@@ -144,7 +144,7 @@ def lib() -> C.CDLL:
         _lib.flat_paged_kv_cache_table.argtypes = [C.c_void_p]
         for name in ("flat_ctx_destroy", "flat_paged_kv_table_destroy", "flat_paged_kv_cache_destroy",
                      "flat_resident_kv_cache_destroy", "flat_resident_kv_cache_reset", "flat_prepared_forward_destroy",
-                     "flat_prepared_backward_destroy"):
+                     "flat_prepared_backward_destroy", "flat_splitkv_exchange_destroy"):
             getattr(_lib, name).restype = None
             getattr(_lib, name).argtypes = [C.c_void_p]
     return _lib
@@ -434,6 +434,20 @@ class Context:
             C.c_void_p(q_rope_positions_dev.data_ptr()), ip(host_page_tables), ip(host_context_lens), C.byref(cfg),
             C.c_float(theta), buf(q), _b(k), _b(v), buf(gathered), buf(out)))
 
+    def splitkv_decode_peer(self, exchange: "SplitKvPeerExchange", dtype, num_seqs, q_heads, kv_heads, head_dim, page_size,
+                            physical_pages, max_pages_per_seq, page_tables_dev, context_lens_dev, q_rope_positions_dev,
+                            host_page_tables, host_context_lens, cfg, theta, q, k, v, out):
+        """One KV-split decode step over NVLink peer memory: partial of this rank's slice, then one kernel that
+        stores it into every rank's buffer, waits for theirs and merges.  Enqueues only; every rank must call."""
+        def ip(a):
+            return None if a is None else a.ctypes.data_as(C.POINTER(C.c_int32))
+        self.check(lib().flat_splitkv_decode_peer(
+            self.h, exchange.h, C.c_int32(dtype), C.c_uint64(num_seqs), C.c_uint64(q_heads), C.c_uint64(kv_heads),
+            C.c_uint64(head_dim), C.c_uint64(page_size), C.c_uint64(physical_pages), C.c_uint64(max_pages_per_seq),
+            C.c_void_p(page_tables_dev.data_ptr()), C.c_void_p(context_lens_dev.data_ptr()),
+            C.c_void_p(q_rope_positions_dev.data_ptr()), ip(host_page_tables), ip(host_context_lens), C.byref(cfg),
+            C.c_float(theta), buf(q), _b(k), _b(v), buf(out)))
+
     def splitkv_merge_nccl(self, comm_ptr: int, rank: int, world: int, dtype, rows, head_dim, gathered, out):
         self.check(lib().flat_splitkv_merge_nccl(self.h, C.c_void_p(comm_ptr), C.c_int32(rank), C.c_int32(world),
                                                  C.c_int32(dtype), C.c_uint64(rows), C.c_uint64(head_dim), buf(gathered),
@@ -464,6 +478,36 @@ class Context:
     def backward_mha(self, dtype, shp, cfg, packed_inputs, packed_grads):
         self.check(lib().flat_backward_mha(self.h, C.c_int32(dtype), C.byref(shp), C.byref(cfg), buf(packed_inputs),
                                            buf(packed_grads)))
+
+
+class SplitKvPeerExchange:
+    """The peer-memory exchange object of KV-split decode (flat_splitkv_exchange_*): one device allocation per rank
+    that the other ranks of the box map through CUDA IPC.  `handle()` is what a rank gives the others;
+    `connect(all_handles)` maps theirs (see `distributed.connect_peer_exchange`)."""
+
+    def __init__(self, ctx: "Context", rank: int, world: int, rows: int, head_dim: int):
+        self.ctx = ctx
+        h = C.c_void_p()
+        ctx.check(lib().flat_splitkv_exchange_create(ctx.h, C.c_int32(rank), C.c_int32(world), C.c_uint64(rows),
+                                                     C.c_uint64(head_dim), C.byref(h)))
+        self.h, self.world = h, world
+
+    def handle(self) -> bytes:
+        out = (C.c_uint8 * 64)()
+        self.ctx.check(lib().flat_splitkv_exchange_handle(self.h, out))
+        return bytes(out)
+
+    def connect(self, handles: bytes):
+        arr = (C.c_uint8 * len(handles)).from_buffer_copy(handles)
+        self.ctx.check(lib().flat_splitkv_exchange_connect(self.h, arr, C.c_uint64(len(handles))))
+
+    def close(self):
+        if getattr(self, "h", None):
+            lib().flat_splitkv_exchange_destroy(self.h)
+            self.h = None
+
+    def __del__(self):
+        self.close()
 
 
 class PreparedForward:

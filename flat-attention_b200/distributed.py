@@ -79,3 +79,26 @@ def nccl_comm_ptr(group=None, device=None) -> int:
     if not hasattr(backend, "_comm_ptr"):
         raise RuntimeError("this torch build does not expose the NCCL communicator of a process group")
     return int(backend._comm_ptr())
+
+
+def connect_peer_exchange(exchange, group=None):
+    """Hands every rank's IPC handle of a `SplitKvPeerExchange` to every other rank (one all-gather of 64 bytes per
+    rank through torch.distributed, any backend) and maps them: after this the exchange can run
+    `Context.splitkv_decode_peer`.  Every rank of the group must make the call; when a rank cannot map a peer, every
+    rank raises (nobody is left waiting in a collective)."""
+    import torch
+    import torch.distributed as dist
+    world = dist.get_world_size(group)
+    handles = [None] * world
+    dist.all_gather_object(handles, exchange.handle(), group=group)
+    error = None
+    try:
+        exchange.connect(b"".join(handles))
+    except Exception as e:  # reported after the ranks have agreed on the outcome
+        error = e
+    device = "cuda" if dist.get_backend(group) == "nccl" else "cpu"
+    ok = torch.tensor([0 if error else 1], device=device)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=group)  # also: every rank has mapped every buffer before any store
+    if int(ok.item()) == 0:
+        raise RuntimeError("peer exchange could not be connected on every rank: %r" % (error,))
+    return exchange

@@ -528,6 +528,44 @@ int32_t flat_splitkv_decode_nccl(flat_ctx *ctx, void *nccl_comm, int32_t rank, i
                                  flat_buffer k, flat_buffer v, flat_buffer gathered,
                                  flat_buffer out_and_lse);
 
+/* The same KV-split decode step without a collective library: exchange and merge in ONE kernel over
+ * NVLink peer memory.  Each rank owns an exchange object (one device allocation: a staging block,
+ * two receive buffers of world_size blocks of rows*(head_dim+1) f32, flags and a step counter) that
+ * the other ranks of the box map through CUDA IPC:
+ *   flat_splitkv_exchange_create   allocates it for `rows` = num_seqs*q_heads rows of head_dim;
+ *   flat_splitkv_exchange_handle   gives the 64-byte handle the host passes to the other ranks by
+ *                                  whatever channel it has (a torch.distributed all-gather, MPI, a file);
+ *   flat_splitkv_exchange_connect  takes all ranks' handles (world_size * 64 bytes, in rank order; the
+ *                                  own entry is ignored) and maps them; FLAT_ERR_UNAVAILABLE when a
+ *                                  peer cannot be mapped (no peer access between the two GPUs);
+ *   flat_splitkv_decode_peer       one step: this rank's partial into the staging block, then a kernel
+ *                                  that stores the block into every rank's receive buffer with plain peer
+ *                                  stores, raises this rank's flag there, waits until all ranks' flags
+ *                                  of this step have arrived here and merges (same arithmetic and the
+ *                                  same bits as flat_splitkv_merge_packed).  Every rank must make the
+ *                                  call, once per step, in the same order.  Enqueues only, can be
+ *                                  captured in a CUDA graph and replayed (the step counter is on the
+ *                                  device).  A rank that waits longer than about a second gives up:
+ *                                  flat_ctx_device_status then reports FLAT_ERR_DEVICE_WAIT_TIMEOUT,
+ *                                  the output of that step is unspecified and the context stays usable;
+ *   flat_splitkv_exchange_destroy  synchronises the context's stream, unmaps and frees.
+ * At most 16 ranks.  No counterpart in the reference (single-device, src/wgpu_backend.rs:208-217). */
+typedef struct flat_splitkv_exchange flat_splitkv_exchange;
+int32_t flat_splitkv_exchange_create(flat_ctx *ctx, int32_t rank, int32_t world_size, uint64_t rows,
+                                     uint64_t head_dim, flat_splitkv_exchange **out);
+int32_t flat_splitkv_exchange_handle(const flat_splitkv_exchange *exchange, uint8_t out[64]);
+int32_t flat_splitkv_exchange_connect(flat_splitkv_exchange *exchange, const uint8_t *handles,
+                                      uint64_t handle_bytes);
+void flat_splitkv_exchange_destroy(flat_splitkv_exchange *exchange);
+int32_t flat_splitkv_decode_peer(flat_ctx *ctx, flat_splitkv_exchange *exchange, int32_t dtype,
+                                 uint64_t num_seqs, uint64_t q_heads, uint64_t kv_heads,
+                                 uint64_t head_dim, uint64_t page_size, uint64_t physical_pages,
+                                 uint64_t max_pages_per_seq, const int32_t *page_tables_dev,
+                                 const int32_t *context_lens_dev, const int32_t *q_rope_positions_dev,
+                                 const int32_t *host_page_tables, const int32_t *host_context_lens,
+                                 const flat_attention_config *config, float theta, flat_buffer q,
+                                 flat_buffer k, flat_buffer v, flat_buffer out_and_lse);
+
 /* The same batched split-KV decode for callers that cannot allocate device memory when the
  * call is made (a latency-critical serving loop where an allocation would stall the device, a
  * plug-in under a framework allocator that forbids side allocations, or a process whose memory

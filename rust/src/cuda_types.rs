@@ -5,7 +5,8 @@ use core::ffi::{c_char, c_void};
 macro_rules! opaque {
     ($($name:ident),*) => { $(#[repr(C)] pub struct $name { _private: [u8; 0] })* };
 }
-opaque!(FlatCtx, FlatPagedKvTable, FlatPagedKvCache, FlatResidentKvCache, FlatPreparedForward, FlatPreparedBackward);
+opaque!(FlatCtx, FlatPagedKvTable, FlatPagedKvCache, FlatResidentKvCache, FlatPreparedForward, FlatPreparedBackward,
+        FlatSplitKvExchange);
 
 pub const FLAT_F32: i32 = 0;
 pub const FLAT_BF16: i32 = 1;

@@ -1,6 +1,8 @@
 """KV-split decode over a real NCCL communicator through the C ABI (flat_splitkv_decode_nccl): two ranks, one GPU
 each, every rank holding half of one sequence's pages.  The merged result on both ranks equals the CPU oracle on the
-whole sequence and the single-GPU decode.  Needs two GPUs; the plumbing around it (sharding, merge formula) is covered
+whole sequence and the single-GPU decode.  The peer-memory route (flat_splitkv_decode_peer: one kernel that stores the
+partial into both ranks' buffers, waits for the other's flag and merges) runs on the same ranks and must give the
+same bits as the NCCL route, step after step (both receive buffers and their reuse).  Needs two GPUs; the plumbing around it (sharding, merge formula) is covered
 on CPU with gloo in test_distributed_cpu.py."""
 import os
 import sys
@@ -63,6 +65,21 @@ def _rank_main(rank, world, port, result):
         both = [torch.empty_like(out) for _ in range(world)]
         dist.all_gather(both, out)
         result["same_%d" % rank] = bool(torch.equal(both[0], both[1]))
+        # the same step over peer memory: five steps, so both receive buffers are used and reused
+        xchg = fd.connect_peer_exchange(fa.SplitKvPeerExchange(ctx, rank, world, Hq, D))
+        out_peer = ctx.create_decode_output_buffer(fa.BF16, 1, Hq, D)
+        peer_same = True
+        for step in range(5):
+            out_peer.zero_()
+            ctx.splitkv_decode_peer(xchg, fa.BF16, 1, Hq, Hkv, D, ps, pool, pages, torch.from_numpy(tab).cuda(),
+                                    torch.from_numpy(lens).cuda(), torch.from_numpy(qpos).cuda(), tab, lens, fa.config(True),
+                                    theta, Q.cuda(), Kc.cuda(), Vc.cuda(), out_peer)
+            ctx.synchronize()
+            peer_same = peer_same and bool(torch.equal(out_peer, out))
+        result["peer_same_%d" % rank] = peer_same
+        result["peer_status_%d" % rank] = ctx.device_status()
+        dist.barrier()  # nobody unmaps a buffer a peer may still store into
+        xchg.close()
     finally:
         dist.destroy_process_group()
 
@@ -78,3 +95,5 @@ def test_splitkv_decode_over_nccl_two_ranks():
     mp.spawn(_rank_main, args=(2, port, result), nprocs=2, join=True)
     assert result["o"] <= 2e-2 and result["l"] <= 2e-3, dict(result)
     assert result["same_0"] and result["same_1"]
+    assert result["peer_status_0"] == 0 and result["peer_status_1"] == 0, dict(result)
+    assert result["peer_same_0"] and result["peer_same_1"], dict(result)
