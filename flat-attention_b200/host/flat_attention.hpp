@@ -10,6 +10,7 @@
 
 #include <cstdint>
 #include <optional>
+#include <array>
 #include <stdexcept>
 #include <string>
 #include <utility>
@@ -507,6 +508,47 @@ class CudaGroupedBackwardRecomputePipeline {
   private:
     const Context &ctx_;
     DType dtype_;
+};
+
+// KV-split decode of one long sequence across the GPUs of a box (no counterpart in the reference, which is
+// single-device): the peer-memory exchange object.  handle() is what a rank gives the other ranks, connect() maps
+// theirs; decode() is one step (flat_splitkv_decode_peer: the rank's partial, then one kernel that stores it into every
+// rank's buffer, waits for the others' flags and merges).
+struct SplitKvSlicePass {
+    uint64_t num_seqs, q_heads, kv_heads, head_dim, page_size, physical_pages, max_pages_per_seq;
+    const int32_t *page_tables_dev, *context_lens_dev, *q_rope_positions_dev;
+    const int32_t *host_page_tables, *host_context_lens;  // optional (validation; all-zero lengths = an empty slice)
+    FlatAttentionConfig config;
+    float theta;
+    DeviceBuffer q, k, v, out_and_lse;
+};
+class CudaSplitKvPeerExchange {
+  public:
+    CudaSplitKvPeerExchange(const Context &ctx, int rank, int world, uint64_t rows, uint64_t head_dim) : ctx_(ctx) {
+        ctx_.check(flat_splitkv_exchange_create(ctx_.raw(), rank, world, rows, head_dim, &raw_));
+    }
+    ~CudaSplitKvPeerExchange() { flat_splitkv_exchange_destroy(raw_); }
+    CudaSplitKvPeerExchange(const CudaSplitKvPeerExchange &) = delete;
+    CudaSplitKvPeerExchange &operator=(const CudaSplitKvPeerExchange &) = delete;
+    std::array<uint8_t, 64> handle() const {
+        std::array<uint8_t, 64> h{};
+        ctx_.check(flat_splitkv_exchange_handle(raw_, h.data()));
+        return h;
+    }
+    void connect(const std::vector<uint8_t> &all_handles) {
+        ctx_.check(flat_splitkv_exchange_connect(raw_, all_handles.data(), all_handles.size()));
+    }
+    void decode(DType dtype, const SplitKvSlicePass &p) const {
+        auto cfg = p.config.raw();
+        ctx_.check(flat_splitkv_decode_peer(ctx_.raw(), raw_, static_cast<int32_t>(dtype), p.num_seqs, p.q_heads, p.kv_heads,
+                                            p.head_dim, p.page_size, p.physical_pages, p.max_pages_per_seq, p.page_tables_dev,
+                                            p.context_lens_dev, p.q_rope_positions_dev, p.host_page_tables, p.host_context_lens,
+                                            &cfg, p.theta, p.q, p.k, p.v, p.out_and_lse));
+    }
+
+  private:
+    const Context &ctx_;
+    flat_splitkv_exchange *raw_ = nullptr;
 };
 
 }  // namespace flat

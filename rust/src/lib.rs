@@ -341,3 +341,38 @@ impl<'a> CudaPagedDecodePipeline<'a> {
         Self::layout(self.dtype, pass.q_heads, pass.head_dim)
     }
 }
+
+/// The peer-memory exchange of KV-split decode (no counterpart in the reference, which is single-device): one device
+/// allocation per rank that the other ranks of the box map through CUDA IPC.  `handle` is what a rank gives the
+/// others, `connect` maps theirs; `flat_splitkv_decode_peer` then runs a step (the rank's partial, then one kernel that
+/// stores it into every rank's buffer, waits for the others' flags and merges).
+pub struct CudaSplitKvPeerExchange<'a> {
+    ctx: &'a CudaContext,
+    raw: *mut FlatSplitKvExchange,
+}
+
+impl<'a> CudaSplitKvPeerExchange<'a> {
+    pub fn new(ctx: &'a CudaContext, rank: i32, world: i32, rows: u64, head_dim: u64) -> Result<Self, CudaError> {
+        let mut raw = core::ptr::null_mut();
+        ctx.check(unsafe { cuda_ffi::flat_splitkv_exchange_create(ctx.raw, rank, world, rows, head_dim, &mut raw) })?;
+        Ok(Self { ctx, raw })
+    }
+    pub fn handle(&self) -> Result<[u8; 64], CudaError> {
+        let mut out = [0u8; 64];
+        self.ctx.check(unsafe { cuda_ffi::flat_splitkv_exchange_handle(self.raw, out.as_mut_ptr()) })?;
+        Ok(out)
+    }
+    /// `all_handles`: every rank's handle in rank order (the own entry is ignored).
+    pub fn connect(&mut self, all_handles: &[u8]) -> Result<(), CudaError> {
+        self.ctx.check(unsafe { cuda_ffi::flat_splitkv_exchange_connect(self.raw, all_handles.as_ptr(), all_handles.len() as u64) })
+    }
+    pub fn raw(&self) -> *mut FlatSplitKvExchange {
+        self.raw
+    }
+}
+
+impl Drop for CudaSplitKvPeerExchange<'_> {
+    fn drop(&mut self) {
+        unsafe { cuda_ffi::flat_splitkv_exchange_destroy(self.raw) }
+    }
+}

@@ -169,6 +169,12 @@ def test_null_context_is_an_error_not_a_crash():
     assert lib.flat_splitkv_decode_nccl(None, None, C.c_int32(0), C.c_int32(1), C.c_int32(1), C.c_uint64(1), C.c_uint64(1),
                                         C.c_uint64(1), C.c_uint64(2), C.c_uint64(16), C.c_uint64(1), C.c_uint64(1), None, None, None,
                                         None, None, C.byref(cfg), C.c_float(1e4), z, z, z, z, z) == 27
+    assert lib.flat_splitkv_exchange_create(None, C.c_int32(0), C.c_int32(2), C.c_uint64(64), C.c_uint64(128), None) == 27
+    assert lib.flat_splitkv_exchange_handle(None, None) == 27 and lib.flat_splitkv_exchange_connect(None, None, C.c_uint64(0)) == 27
+    lib.flat_splitkv_exchange_destroy(None)
+    assert lib.flat_splitkv_decode_peer(None, None, C.c_int32(1), C.c_uint64(1), C.c_uint64(1), C.c_uint64(1), C.c_uint64(2),
+                                        C.c_uint64(16), C.c_uint64(1), C.c_uint64(1), None, None, None, None, None,
+                                        C.byref(cfg), C.c_float(1e4), z, z, z, z) == 27
     assert lib.flat_forward_prepare(None, C.c_int32(1), C.c_int32(0), C.byref(shp), C.byref(cfg), None, z, z, z, z, None) == 27
     assert lib.flat_forward_encode_prepared(None, None) == 27 and lib.flat_backward_encode_prepared(None, None) == 27
     assert lib.flat_backward_prepare(None, C.c_int32(1), C.byref(shp), C.byref(cfg), z, z, None) == 27
