@@ -252,9 +252,15 @@ __global__ void __launch_bounds__(256) decode_kernel(const __grid_constant__ Dec
 // over the parts with the weights staged in shared memory (coalesced rows, several loads in flight).
 // Fixed-chunk mode: only ceil(ctx/chunk) parts of a row are live.  Balanced mode: one slot per CTA that
 // touched the sequence; a single slot was already written as the final result.
-constexpr int kMergeThreads = 128;
-constexpr int kMergeBatch = 512;  // weights staged per pass
+constexpr int kMergeDims = 128;    // threads along the head dimension (kMaxHeadDim)
+constexpr int kMergeGroups = 4;    // groups of such threads; group g takes the parts g, g + 4, ... of a batch
+constexpr int kMergeThreads = kMergeDims * kMergeGroups;
+constexpr int kMergeBatch = 512;   // weights staged per pass
 
+// Merge of the split-KV partials of one row: LSE = log sum exp(LSE_i), O = sum exp(LSE_i - LSE) O_i.  A long context
+// cut into short spans gives a row hundreds of parts and a batch only a few rows, so the parts are spread over four
+// thread groups with eight independent loads in flight each (the loop is a chain of L2 round trips otherwise); the
+// groups' sums are added in group order, which keeps the result a fixed function of the inputs.
 template <typename T>
 __global__ void __launch_bounds__(kMergeThreads) merge_kernel(int parts, int64_t rows, int head_dim,
                                                               const float *__restrict__ partial_o,
@@ -265,7 +271,9 @@ __global__ void __launch_bounds__(kMergeThreads) merge_kernel(int parts, int64_t
                                                               int64_t stride_lse) {
     __shared__ float w_s[kMergeBatch];
     __shared__ float red[kMergeThreads / 32];
+    __shared__ float acc_s[kMergeGroups][kMergeDims];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int dim = tid % kMergeDims, group = tid / kMergeDims;
     const int64_t row = blockIdx.x;
     int live = parts;
     if (seq_offsets) {
@@ -302,23 +310,27 @@ __global__ void __launch_bounds__(kMergeThreads) merge_kernel(int parts, int64_t
         __syncthreads();
         for (int i = tid; i < n; i += kMergeThreads) w_s[i] = expf(partial_lse[(int64_t)(base + i) * stride_lse + row] - total);
         __syncthreads();
-        if (tid < head_dim) {
-            const float *src = partial_o + (int64_t)base * stride_o + row * head_dim + tid;
-            int i = 0;
-            for (; i + 4 <= n; i += 4) {
-                const float a0 = src[(int64_t)(i + 0) * stride_o], a1 = src[(int64_t)(i + 1) * stride_o];
-                const float a2 = src[(int64_t)(i + 2) * stride_o], a3 = src[(int64_t)(i + 3) * stride_o];
-                acc = fmaf(w_s[i], a0, acc);
-                acc = fmaf(w_s[i + 1], a1, acc);
-                acc = fmaf(w_s[i + 2], a2, acc);
-                acc = fmaf(w_s[i + 3], a3, acc);
+        if (dim < head_dim) {
+            const float *src = partial_o + (int64_t)base * stride_o + row * head_dim + dim;
+            int i = group;
+            for (; i + 7 * kMergeGroups < n; i += 8 * kMergeGroups) {
+                float a[8];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) a[u] = src[(int64_t)(i + u * kMergeGroups) * stride_o];
+#pragma unroll
+                for (int u = 0; u < 8; ++u) acc = fmaf(w_s[i + u * kMergeGroups], a[u], acc);
             }
-            for (; i < n; ++i) acc = fmaf(w_s[i], src[(int64_t)i * stride_o], acc);
+            for (; i < n; i += kMergeGroups) acc = fmaf(w_s[i], src[(int64_t)i * stride_o], acc);
         }
     }
-    if (tid < head_dim) {
-        if constexpr (sizeof(T) == 4) o[row * head_dim + tid] = acc;
-        else o[row * head_dim + tid] = __float2bfloat16_rn(acc);
+    acc_s[group][dim] = acc;
+    __syncthreads();
+    if (group == 0 && dim < head_dim) {
+        float r = acc_s[0][dim];
+#pragma unroll
+        for (int g = 1; g < kMergeGroups; ++g) r += acc_s[g][dim];
+        if constexpr (sizeof(T) == 4) o[row * head_dim + dim] = r;
+        else o[row * head_dim + dim] = __float2bfloat16_rn(r);
     }
     if (tid == 0) lse[row] = total;
 }
