@@ -253,22 +253,25 @@ __global__ void __launch_bounds__(256) decode_kernel(const __grid_constant__ Dec
 // Fixed-chunk mode: only ceil(ctx/chunk) parts of a row are live.  Balanced mode: one slot per CTA that
 // touched the sequence; a single slot was already written as the final result.
 constexpr int kMergeDims = 128;    // threads along the head dimension (kMaxHeadDim)
-constexpr int kMergeGroups = 4;    // groups of such threads; group g takes the parts g, g + 4, ... of a batch
-constexpr int kMergeThreads = kMergeDims * kMergeGroups;
+constexpr int kMergeGroupsWide = 4;  // thread groups of the wide variant; group g takes the parts g, g + 4, ... of a batch
+constexpr int kMergeWideFrom = 17;   // rows with this many parts or more are merged by the wide variant
 constexpr int kMergeBatch = 512;   // weights staged per pass
 
-// Merge of the split-KV partials of one row: LSE = log sum exp(LSE_i), O = sum exp(LSE_i - LSE) O_i.  A long context
-// cut into short spans gives a row hundreds of parts and a batch only a few rows, so the parts are spread over four
-// thread groups with eight independent loads in flight each (the loop is a chain of L2 round trips otherwise); the
-// groups' sums are added in group order, which keeps the result a fixed function of the inputs.
-template <typename T>
-__global__ void __launch_bounds__(kMergeThreads) merge_kernel(int parts, int64_t rows, int head_dim,
+// Merge of the split-KV partials of one row: LSE = log sum exp(LSE_i), O = sum exp(LSE_i - LSE) O_i.  GROUPS = 1: 128
+// threads, the parts are added in order (a batch of many short sequences: few parts per row, thousands of rows).
+// GROUPS = 4: a long context cut into short spans gives a row hundreds of parts and a batch only a few rows, so the
+// parts are spread over four thread groups (the loop is a chain of L2 round trips otherwise) and the groups' sums are
+// added in group order.  Either way eight independent loads are in flight per thread and the result is a fixed
+// function of the inputs and of the part count.
+template <typename T, int GROUPS>
+__global__ void __launch_bounds__(kMergeDims * GROUPS) merge_kernel(int parts, int64_t rows, int head_dim,
                                                               const float *__restrict__ partial_o,
                                                               const float *__restrict__ partial_lse, T *__restrict__ o,
                                                               float *__restrict__ lse, const int32_t *context_lens,
                                                               int uniform_len, int chunk_tokens, int rows_per_seq,
                                                               const int32_t *seq_offsets, int span_tokens, int64_t stride_o,
                                                               int64_t stride_lse) {
+    constexpr int kMergeGroups = GROUPS, kMergeThreads = kMergeDims * GROUPS;
     __shared__ float w_s[kMergeBatch];
     __shared__ float red[kMergeThreads / 32];
     __shared__ float acc_s[kMergeGroups][kMergeDims];
@@ -340,10 +343,14 @@ int merge_chunks(flat_ctx *ctx, const DecodeParams &p) {
     if (p.kv_splits <= 1) return FLAT_OK;
     int64_t rows = (int64_t)p.num_seqs * p.q_heads;
     int blocks = (int)rows;
-    merge_kernel<T><<<blocks, kMergeThreads, 0, ctx->stream>>>(p.kv_splits, rows, p.head_dim, p.partial_o, p.partial_lse, (T *)p.o,
-                                                      p.lse, p.context_lens, p.uniform_len, p.chunk_tokens, p.q_heads,
-                                                      p.balanced ? p.seq_offsets : nullptr, p.span_tokens,
-                                                      rows * p.head_dim, rows);
+    if (p.kv_splits >= kMergeWideFrom)
+        merge_kernel<T, kMergeGroupsWide><<<blocks, kMergeDims * kMergeGroupsWide, 0, ctx->stream>>>(
+            p.kv_splits, rows, p.head_dim, p.partial_o, p.partial_lse, (T *)p.o, p.lse, p.context_lens, p.uniform_len,
+            p.chunk_tokens, p.q_heads, p.balanced ? p.seq_offsets : nullptr, p.span_tokens, rows * p.head_dim, rows);
+    else
+        merge_kernel<T, 1><<<blocks, kMergeDims, 0, ctx->stream>>>(
+            p.kv_splits, rows, p.head_dim, p.partial_o, p.partial_lse, (T *)p.o, p.lse, p.context_lens, p.uniform_len,
+            p.chunk_tokens, p.q_heads, p.balanced ? p.seq_offsets : nullptr, p.span_tokens, rows * p.head_dim, rows);
     ctx->launches += 1;
     FLAT_CUDA_OK(ctx, cudaGetLastError());
     return FLAT_OK;
@@ -416,13 +423,18 @@ int launch_decode(flat_ctx *ctx, int dtype, const DecodeParams &p) {
 int launch_splitkv_merge(flat_ctx *ctx, int dtype, int parts, int64_t rows, int head_dim, const float *partial_o,
                          const float *partial_lse, int64_t part_stride_o, int64_t part_stride_lse, void *o, float *lse) {
     int blocks = (int)rows;
-    if (dtype == FLAT_BF16)
-        merge_kernel<__nv_bfloat16><<<blocks, kMergeThreads, 0, ctx->stream>>>(parts, rows, head_dim, partial_o, partial_lse,
-                                                                      (__nv_bfloat16 *)o, lse, nullptr, 0, 0, 1, nullptr, 0, part_stride_o,
-                                                                      part_stride_lse);
-    else
-        merge_kernel<float><<<blocks, kMergeThreads, 0, ctx->stream>>>(parts, rows, head_dim, partial_o, partial_lse, (float *)o,
-                                                             lse, nullptr, 0, 0, 1, nullptr, 0, part_stride_o, part_stride_lse);
+    auto launch = [&](auto kernel, int threads, auto *out) {
+        kernel<<<blocks, threads, 0, ctx->stream>>>(parts, rows, head_dim, partial_o, partial_lse, out, lse, nullptr, 0, 0, 1, nullptr,
+                                                   0, part_stride_o, part_stride_lse);
+    };
+    const bool wide = parts >= kMergeWideFrom;
+    if (dtype == FLAT_BF16) {
+        if (wide) launch(merge_kernel<__nv_bfloat16, kMergeGroupsWide>, kMergeDims * kMergeGroupsWide, (__nv_bfloat16 *)o);
+        else launch(merge_kernel<__nv_bfloat16, 1>, kMergeDims, (__nv_bfloat16 *)o);
+    } else {
+        if (wide) launch(merge_kernel<float, kMergeGroupsWide>, kMergeDims * kMergeGroupsWide, (float *)o);
+        else launch(merge_kernel<float, 1>, kMergeDims, (float *)o);
+    }
     ctx->launches += 1;
     FLAT_CUDA_OK(ctx, cudaGetLastError());
     return FLAT_OK;

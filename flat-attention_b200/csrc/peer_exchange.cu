@@ -121,34 +121,23 @@ __global__ void __launch_bounds__(kXchgThreads) peer_exchange_merge_kernel(const
             for (int sft = 16; sft >= 1; sft >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, sft);
             const float total = mx + logf(sum);
             const float w_mine = lane < p.world ? expf(mine - total) : 0.f;
-            // (the merge kernel adds parts g, g + 4, ... in four running sums and then the four sums in order)
-            constexpr int kGroups = 4;
-            float acc[kMaxHeadDim / 32][kGroups];
+            // (at most 16 ranks: the merge kernel of the all-gather route adds so few parts in order)
+            float acc[kMaxHeadDim / 32];
 #pragma unroll
-            for (int i = 0; i < kMaxHeadDim / 32; ++i)
+            for (int i = 0; i < kMaxHeadDim / 32; ++i) acc[i] = 0.f;
+            for (int r = 0; r < p.world; ++r) {
+                const float w = __shfl_sync(0xffffffffu, w_mine, r);
+                const float *blk = reinterpret_cast<const float *>(data + r * p.block_bytes) + (size_t)row * D;
 #pragma unroll
-                for (int g = 0; g < kGroups; ++g) acc[i][g] = 0.f;
-            for (int r0 = 0; r0 < p.world; r0 += kGroups) {
-#pragma unroll
-                for (int g = 0; g < kGroups; ++g) {
-                    const int r = r0 + g;
-                    if (r >= p.world) break;
-                    const float w = __shfl_sync(0xffffffffu, w_mine, r);
-                    const float *blk = reinterpret_cast<const float *>(data + r * p.block_bytes) + (size_t)row * D;
-#pragma unroll
-                    for (int i = 0; i < kMaxHeadDim / 32; ++i)
-                        if (lane + 32 * i < D) acc[i][g] = fmaf(w, __ldcg(blk + lane + 32 * i), acc[i][g]);
-                }
+                for (int i = 0; i < kMaxHeadDim / 32; ++i)
+                    if (lane + 32 * i < D) acc[i] = fmaf(w, __ldcg(blk + lane + 32 * i), acc[i]);
             }
 #pragma unroll
             for (int i = 0; i < kMaxHeadDim / 32; ++i) {
                 const int d = lane + 32 * i;
                 if (d >= D) continue;
-                float v = acc[i][0];
-#pragma unroll
-                for (int g = 1; g < kGroups; ++g) v += acc[i][g];
-                if constexpr (sizeof(T) == 4) reinterpret_cast<float *>(p.o)[(size_t)row * D + d] = v;
-                else reinterpret_cast<__nv_bfloat16 *>(p.o)[(size_t)row * D + d] = __float2bfloat16_rn(v);
+                if constexpr (sizeof(T) == 4) reinterpret_cast<float *>(p.o)[(size_t)row * D + d] = acc[i];
+                else reinterpret_cast<__nv_bfloat16 *>(p.o)[(size_t)row * D + d] = __float2bfloat16_rn(acc[i]);
             }
             if (lane == 0) p.lse[row] = total;
         }
