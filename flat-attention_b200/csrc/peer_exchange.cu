@@ -231,13 +231,19 @@ int32_t flat_splitkv_exchange_connect(flat_splitkv_exchange *x, const uint8_t *h
         if (r == x->rank) continue;
         cudaIpcMemHandle_t h;
         std::memcpy(&h, handles + (uint64_t)r * 64, 64);
+        if (std::memcmp(&h, &x->handle, 64) == 0) {
+            // this process's own buffer named for another rank (a single-process harness): IPC cannot open a handle in
+            // the process that made it, and need not
+            x->peers[r] = x->local;
+            continue;
+        }
         void *ptr = nullptr;
         const cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
         if (e != cudaSuccess) {
             cudaGetLastError();
             for (int q = 0; q < r; ++q)
                 if (q != x->rank && x->peers[q]) {
-                    cudaIpcCloseMemHandle(x->peers[q]);
+                    if (x->peers[q] != x->local) cudaIpcCloseMemHandle(x->peers[q]);
                     x->peers[q] = nullptr;
                 }
             return fail(ctx, FLAT_ERR_UNAVAILABLE, "rank %d's exchange buffer cannot be mapped: %s", r, cudaGetErrorString(e));
@@ -252,7 +258,7 @@ void flat_splitkv_exchange_destroy(flat_splitkv_exchange *x) {
     if (!x) return;
     cudaStreamSynchronize(x->ctx->stream);
     for (int r = 0; r < x->world; ++r)
-        if (r != x->rank && x->peers[r]) cudaIpcCloseMemHandle(x->peers[r]);
+        if (r != x->rank && x->peers[r] && x->peers[r] != x->local) cudaIpcCloseMemHandle(x->peers[r]);
     if (x->local) cudaFree(x->local);
     delete x;
 }

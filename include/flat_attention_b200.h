@@ -537,7 +537,9 @@ int32_t flat_splitkv_decode_nccl(flat_ctx *ctx, void *nccl_comm, int32_t rank, i
  *                                  whatever channel it has (a torch.distributed all-gather, MPI, a file);
  *   flat_splitkv_exchange_connect  takes all ranks' handles (world_size * 64 bytes, in rank order; the
  *                                  own entry is ignored) and maps them; FLAT_ERR_UNAVAILABLE when a
- *                                  peer cannot be mapped (no peer access between the two GPUs);
+ *                                  peer cannot be mapped (no peer access between the two GPUs); an entry
+ *                                  equal to the own handle stands for this process's own buffer (a
+ *                                  single-process harness in which a rank is absent);
  *   flat_splitkv_decode_peer       one step: this rank's partial into the staging block, then a kernel
  *                                  that stores the block into every rank's receive buffer with plain peer
  *                                  stores, raises this rank's flag there, waits until all ranks' flags

@@ -385,3 +385,68 @@ def test_kv_split_across_ranks_emulated_on_one_gpu(parts):
     mo, ml = fd.merge_partials_reference(po, pl)
     assert_close("merge O", o, mo.numpy(), 8e-3, 0.0)
     assert_close("merge LSE", l, ml.numpy(), 1e-5, 0.0)
+
+
+def _one_sequence_slice(n, Hq=32, Hkv=8, D=128, ps=16, seed=21):
+    g = torch.Generator().manual_seed(seed)
+    K = torch.randn(n, Hkv * D, generator=g).bfloat16()
+    V = torch.randn(n, Hkv * D, generator=g).bfloat16()
+    Q = torch.randn(1, Hq * D, generator=g).bfloat16()
+    pages = (n + ps - 1) // ps
+    pool = pages + 2
+    perm = np.random.default_rng(seed).permutation(pool).astype(np.int32)[:pages]
+    Kc, Vc = torch.zeros(pool * ps, Hkv * D, dtype=torch.bfloat16), torch.zeros(pool * ps, Hkv * D, dtype=torch.bfloat16)
+    for i in range(pages):
+        lo, hi = i * ps, min(n, (i + 1) * ps)
+        Kc[perm[i] * ps:perm[i] * ps + hi - lo] = K[lo:hi]
+        Vc[perm[i] * ps:perm[i] * ps + hi - lo] = V[lo:hi]
+    tab, lens, qpos = perm.reshape(1, pages), np.array([n], np.int32), np.array([n - 1], np.int32)
+    args = (1, Hq, Hkv, D, ps, pool, pages, torch.from_numpy(tab).cuda(), torch.from_numpy(lens).cuda(),
+            torch.from_numpy(qpos).cuda(), tab, lens, fa.config(True), 5e5, Q.cuda(), Kc.cuda(), Vc.cuda())
+    return args, Hq, D
+
+
+def test_peer_exchange_with_one_rank_equals_partial_plus_merge():
+    """flat_splitkv_decode_peer on a one-rank exchange (no peer to map): the exchange kernel stores the partial into
+    the rank's own buffer, sees its own flag and merges one part.  Same bits as the partial followed by
+    flat_splitkv_merge_packed, step after step (both receive buffers and the device-side step counter)."""
+    c = ctx()
+    args, Hq, D = _one_sequence_slice(16 * 133 + 3)
+    part = torch.empty(Hq * (D + 1), dtype=torch.float32, device="cuda")
+    c.decode_paged_batched_partial(fa.BF16, *args, part)
+    want = c.create_decode_output_buffer(fa.BF16, 1, Hq, D)
+    c.splitkv_merge_packed(fa.BF16, 1, Hq, D, part, want)
+    x = fa.SplitKvPeerExchange(c, 0, 1, Hq, D)
+    try:
+        for step in range(4):
+            got = c.create_decode_output_buffer(fa.BF16, 1, Hq, D)
+            got.zero_()
+            c.splitkv_decode_peer(x, fa.BF16, *args, got)
+            c.synchronize()
+            assert torch.equal(got, want), f"step {step}"
+        assert c.device_status() == 0
+    finally:
+        x.close()
+
+
+def test_peer_exchange_wait_gives_up_when_a_rank_never_arrives():
+    """The exchange kernel's wait for the other ranks' flags is bounded: a two-rank exchange whose second rank does
+    not exist (its handle slot names this process's own buffer, so the stores have a place to go) runs into the limit
+    after about a second, the status word reports FLAT_ERR_DEVICE_WAIT_TIMEOUT with the absent rank, and the context
+    goes on working."""
+    c = ctx()
+    args, Hq, D = _one_sequence_slice(16 * 40)
+    x = fa.SplitKvPeerExchange(c, 0, 2, Hq, D)
+    try:
+        x.connect(x.handle() * 2)
+        out = c.create_decode_output_buffer(fa.BF16, 1, Hq, D)
+        c.splitkv_decode_peer(x, fa.BF16, *args, out)
+        c.synchronize()
+        assert c.device_status() == 60  # FLAT_ERR_DEVICE_WAIT_TIMEOUT, cleared by the read
+    finally:
+        x.close()
+    # the context still decodes
+    part = torch.empty(Hq * (D + 1), dtype=torch.float32, device="cuda")
+    c.decode_paged_batched_partial(fa.BF16, *args, part)
+    c.synchronize()
+    assert c.device_status() == 0 and bool(torch.isfinite(part).all())
