@@ -507,7 +507,10 @@ class SplitKvPeerExchange:
             self.h = None
 
     def __del__(self):
-        self.close()
+        try:
+            self.close()
+        except Exception:  # interpreter shutdown: the module's globals may be gone already
+            pass
 
 
 class PreparedForward:
@@ -526,7 +529,10 @@ class PreparedForward:
 
     def __del__(self):
         if getattr(self, "h", None):
-            lib().flat_prepared_forward_destroy(self.h)
+            try:
+                lib().flat_prepared_forward_destroy(self.h)
+            except Exception:  # interpreter shutdown: the module's globals may be gone already
+                pass
             self.h = None
 
 
@@ -545,7 +551,10 @@ class PreparedBackward:
 
     def __del__(self):
         if getattr(self, "h", None):
-            lib().flat_prepared_backward_destroy(self.h)
+            try:
+                lib().flat_prepared_backward_destroy(self.h)
+            except Exception:  # interpreter shutdown: the module's globals may be gone already
+                pass
             self.h = None
 
 
@@ -568,7 +577,10 @@ class PagedKvTable:
 
     def __del__(self):
         if getattr(self, "_owned", False) and getattr(self, "h", None):
-            lib().flat_paged_kv_table_destroy(self.h)
+            try:
+                lib().flat_paged_kv_table_destroy(self.h)
+            except Exception:  # interpreter shutdown: the module's globals may be gone already
+                pass
             self.h = None
 
     def append(self, tokens: int):
@@ -624,7 +636,10 @@ class CudaPagedKvCache:
 
     def __del__(self):
         if getattr(self, "h", None) and getattr(self.ctx, "h", None):
-            lib().flat_paged_kv_cache_destroy(self.h)
+            try:
+                lib().flat_paged_kv_cache_destroy(self.h)
+            except Exception:  # interpreter shutdown: the module's globals may be gone already
+                pass
             self.h = None
 
     def record_append(self, k_source, v_source, append_len: int) -> int:
@@ -690,7 +705,10 @@ class CudaResidentKvCache:
 
     def __del__(self):
         if getattr(self, "h", None) and getattr(self.ctx, "h", None):
-            lib().flat_resident_kv_cache_destroy(self.h)
+            try:
+                lib().flat_resident_kv_cache_destroy(self.h)
+            except Exception:  # interpreter shutdown: the module's globals may be gone already
+                pass
             self.h = None
 
     def record_append(self, k_source, v_source, append_len: int) -> int:
