@@ -621,24 +621,39 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     for (int c = 0; c < 4; ++c) tmem_ld32(t_s + c * 32, r + c * 32);
                     tc_wait_ld();
                     if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(1);
-                    float bias_base = 0.f;  // tile-constant part of the bias, folded into the max and the exponent below
-                    if constexpr (ALIBI) {
-                        // r[i] <- s_i + (slope / c) * i: one FFMA with an immediate per score.  The rest of the bias,
-                        // (slope / c) * (position difference of column 0), is the same for the whole tile row.
-#pragma unroll
-                        for (int i = 0; i < 128; ++i) r[i] = __float_as_uint(fmaf(slope_rel, (float)i, __uint_as_float(r[i])));
-                        bias_base = slope_rel * (bias_pos0 + (float)key0);
-                    }
+                    // ALiBi: the bias of column i is (slope / c) * i on top of a part that is the same for the whole tile
+                    // row (bias_base).  It is never added to the scores in a pass of its own: the exponent pass below
+                    // folds it into the addend of its FMA (a running pair that advances by two columns per step), and
+                    // the maximum is taken per 32-column chunk of raw scores plus the chunk's largest bias, which bounds
+                    // the true maximum from above by at most 31 columns' worth of slope (any reference point at or above
+                    // the maximum serves the online softmax: P only gets smaller, O and the row sum with it).
+                    float bias_base = 0.f;
+                    if constexpr (ALIBI) bias_base = slope_rel * (bias_pos0 + (float)key0);
                     if (tile_masked) {
 #pragma unroll
                         for (int i = 0; i < 128; ++i)
                             if (i >= vis) r[i] = 0xff800000u;  // -inf: exp2 gives exactly 0
                     }
                     float mx = -INFINITY, mx1 = -INFINITY;  // two chains for instruction-level parallelism
+                    if constexpr (ALIBI) {
 #pragma unroll
-                    for (int i = 0; i < 128; i += 4) {
-                        asm("max.f32 %0, %0, %1, %2;" : "+f"(mx) : "f"(__uint_as_float(r[i])), "f"(__uint_as_float(r[i + 1])));
-                        asm("max.f32 %0, %0, %1, %2;" : "+f"(mx1) : "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3])));
+                        for (int c = 0; c < 4; ++c) {
+                            float a = -INFINITY, b = -INFINITY;
+#pragma unroll
+                            for (int i = 32 * c; i < 32 * c + 32; i += 4) {
+                                asm("max.f32 %0, %0, %1, %2;" : "+f"(a) : "f"(__uint_as_float(r[i])), "f"(__uint_as_float(r[i + 1])));
+                                asm("max.f32 %0, %0, %1, %2;" : "+f"(b) : "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3])));
+                            }
+                            // the chunk's largest bias sits at its last column for a positive slope, at its first otherwise
+                            const float edge = slope_rel >= 0.f ? (float)(32 * c + 31) : (float)(32 * c);
+                            mx = fmaxf(mx, fmaf(slope_rel, edge, fmaxf(a, b)));
+                        }
+                    } else {
+#pragma unroll
+                        for (int i = 0; i < 128; i += 4) {
+                            asm("max.f32 %0, %0, %1, %2;" : "+f"(mx) : "f"(__uint_as_float(r[i])), "f"(__uint_as_float(r[i + 1])));
+                            asm("max.f32 %0, %0, %1, %2;" : "+f"(mx1) : "f"(__uint_as_float(r[i + 2])), "f"(__uint_as_float(r[i + 3])));
+                        }
                     }
                     const float m_cand = fmaxf(m, (fmaxf(mx, mx1) + bias_base) * c_log2);
                     const bool grow = (m_cand - m) > kRescaleThreshold;
@@ -662,21 +677,31 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     if ((warp & 3) == 0 && lane == 0) TRACE_STAMP(2);
                     // P = exp2(S*c - m) as bf16, written over S; two scores per packed f32x2 FMA
                     uint64_t c2, nm2, sum2 = 0, sum3 = 0;
-                    {
-                        // m is still -inf only while every key this row has met was masked (the first tile of a split
-                        // part may lie wholly behind the row's diagonal): all its scores are -inf and P must come out 0
-                        const float neg_m = m == -INFINITY ? 0.f : fmaf(bias_base, c_log2, -m);
-                        asm("mov.b64 %0, {%1, %1};" : "=l"(nm2) : "f"(neg_m));
-                        asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(c_log2));
+                    // m is still -inf only while every key this row has met was masked (the first tile of a split
+                    // part may lie wholly behind the row's diagonal): all its scores are -inf and P must come out 0
+                    const float neg_m0 = m == -INFINITY ? 0.f : fmaf(bias_base, c_log2, -m);
+                    asm("mov.b64 %0, {%1, %1};" : "=l"(nm2) : "f"(neg_m0));
+                    asm("mov.b64 %0, {%1, %1};" : "=l"(c2) : "f"(c_log2));
+                    [[maybe_unused]] uint64_t step2 = 0;  // ALiBi: the addend's advance per pair of columns
+                    [[maybe_unused]] float cs = 0.f;
+                    if constexpr (ALIBI) {
+                        cs = slope_rel * c_log2;
+                        asm("mov.b64 %0, {%1, %1};" : "=l"(step2) : "f"(2.f * cs));
                     }
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         uint32_t pk[16];
+                        if constexpr (ALIBI) {
+                            // the addend of the chunk's first pair, exact; the running sum then covers 16 steps only
+                            const float a0 = fmaf(cs, (float)(32 * c), neg_m0), a1 = fmaf(cs, (float)(32 * c + 1), neg_m0);
+                            asm("mov.b64 %0, {%1, %2};" : "=l"(nm2) : "f"(a0), "f"(a1));
+                        }
 #pragma unroll
                         for (int i = 0; i < 32; i += 2) {
                             uint64_t s2, t2, p2;
                             asm("mov.b64 %0, {%1, %2};" : "=l"(s2) : "r"(r[c * 32 + i]), "r"(r[c * 32 + i + 1]));
                             asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(t2) : "l"(s2), "l"(c2), "l"(nm2));
+                            if constexpr (ALIBI) asm("add.rn.f32x2 %0, %0, %1;" : "+l"(nm2) : "l"(step2));
                             float t0, t1;
                             asm("mov.b64 {%0, %1}, %2;" : "=f"(t0), "=f"(t1) : "l"(t2));
                             const float p0 = ex2(t0), p1 = ex2(t1);
