@@ -226,6 +226,7 @@ int32_t flat_splitkv_exchange_connect(flat_splitkv_exchange *x, const uint8_t *h
     if (handle_bytes < (uint64_t)x->world * 64)
         return fail(ctx, FLAT_ERR_BUFFER_TOO_SMALL, "peer handles have %llu bytes, requires %llu", (unsigned long long)handle_bytes,
                     (unsigned long long)((uint64_t)x->world * 64));
+    if (x->world == 1) return FLAT_OK;  // nothing to map
     if (x->connected) return fail(ctx, FLAT_ERR_UNSUPPORTED_SHAPE, "the exchange is already connected");
     for (int r = 0; r < x->world; ++r) {
         if (r == x->rank) continue;
