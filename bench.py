@@ -813,9 +813,23 @@ def bench_splitkv_128k(torch, np, dist, fa, ctx, peaks, rank, world, steps, warm
     peer = {}
     xchg = None
     try:
-        xchg = fd.connect_peer_exchange(fa.SplitKvPeerExchange(ctx, rank, world, Hq, D))
-    except Exception as e:  # raised on every rank or on none
+        xchg = fa.SplitKvPeerExchange(ctx, rank, world, Hq, D)
+    except Exception as e:
         peer["error"] = repr(e)[:300]
+    made = torch.tensor([1 if xchg is not None else 0], device="cuda")
+    dist.all_reduce(made, op=dist.ReduceOp.MIN)  # the ranks agree before anyone enters the handle exchange
+    if int(made.item()) == 0:
+        if xchg is not None:
+            xchg.close()
+        xchg = None
+        peer.setdefault("error", "another rank could not create its exchange buffer")
+    else:
+        try:
+            fd.connect_peer_exchange(xchg)
+        except Exception as e:  # raised on every rank or on none
+            peer["error"] = repr(e)[:300]
+            xchg.close()
+            xchg = None
     p_ms = pg_ms = -1.0
     if xchg is not None:
         out_p = ctx.create_decode_output_buffer(fa.BF16, 1, Hq, D)
