@@ -854,12 +854,13 @@ __global__ void __launch_bounds__(kThreads, 1) fwd_sm100_kernel(const __grid_con
                     // 32-byte stores 256 bytes apart per thread
                     const float inv = 1.0f / l;
                     uint8_t *stg = o_stage + w * C::kOutStageBytes;
+                    uint32_t ro[D];  // the whole row of O: all loads in flight, one wait
+#pragma unroll
+                    for (int c = 0; c < D / 32; ++c) tmem_ld32(t_o + c * 32, ro + c * 32);
+                    tc_wait_ld();
 #pragma unroll
                     for (int hf = 0; hf < D / 64; ++hf) {
-                        uint32_t r[64];
-                        tmem_ld32(t_o + hf * 64, r);
-                        tmem_ld32(t_o + hf * 64 + 32, r + 32);
-                        tc_wait_ld();
+                        const uint32_t *r = ro + hf * 64;
                         uint32_t pk[32];
 #pragma unroll
                         for (int i = 0; i < 64; i += 2) {
