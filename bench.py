@@ -38,6 +38,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 NCU_TRAFFIC = {
     "forward": 311_873_792 + 111_970_304,  # fwd_sm100_kernel<128>, C2
     "decode": 1_110_817_000 + 3_957_504,  # decode_mma_kernel<128>, C3
+    # the 16 launches of fwd_sm100_kernel<128,paged,shadow> of one C4 sequence, summed (one ncu pass over a whole sequence)
+    "chunked": 4196745216 + 500366592,
     # dK/dV kernel (reads, dS writes) + dQ kernel (dS reads, writes), captured on one eighth of C5 and scaled by 8
     "backward": 8 * (60_724_736 + 507_990_528 + 554_259_712 + 22_141_696),
 }
